@@ -1,0 +1,95 @@
+/* libevoattn -- EvoAttention (pair-bias + residue-mask attention) forward and
+ * backward for NVIDIA B200 (sm_100a).  Plain C ABI: device pointers, sizes and
+ * a CUDA stream; no framework types.  All tensors are caller-owned, contiguous
+ * and 16-byte aligned.  Every call is asynchronous on `stream` and returns 0
+ * (EVO_OK) or a negative error code; nothing throws, blocks or exits.
+ *
+ * Shapes (B batch, S MSA/triangle rows, N residues, H heads, D head dim):
+ *   q,k,v,o,d_o,dq,dk,dv  bf16 [B][S][N][H][D]     (the caller layout of
+ *                         evo_h100/tk_evo_attention_layer.py:5-11 -- no
+ *                         transpose, no padding of D)
+ *   pair_bias             bf16 [B][H][N][N]        (layer.py:91)
+ *   res_mask              bf16 [B][S][N] additive  (layer.py:94)
+ *   lse                   fp32 [B][S][H][N]  natural-log log-sum-exp
+ *                         (evo_h100/tk_evoattention.cu:330-334)
+ *   dbias                 fp32 [B][H][N][N]        (tk_evoattention.cu:1113)
+ * Supported: D in {32, 64}; N a multiple of 8 (any N >= 8, the last tile may be
+ * ragged); N*H*D*S*B*2 bytes < 2^40.
+ */
+#ifndef EVOATTN_H_
+#define EVOATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct EvoDims {
+    int32_t B, S, N, H, D;
+} EvoDims;
+
+enum {
+    EVO_OK = 0,
+    EVO_ERR_BAD_DIMS = -1,      /* unsupported D / N / non-positive extent        */
+    EVO_ERR_NULL_PTR = -2,
+    EVO_ERR_ALIGNMENT = -3,     /* a pointer is not 16-byte aligned               */
+    EVO_ERR_WORKSPACE = -4,     /* workspace smaller than evo_bwd_workspace_bytes */
+    EVO_ERR_NO_DRIVER = -5,     /* CUDA driver / tensor-map encoder unavailable   */
+    EVO_ERR_TENSOR_MAP = -6,    /* cuTensorMapEncodeTiled refused the layout      */
+    EVO_ERR_CUDA = -7,          /* a CUDA runtime call failed (see evo_last_cuda_error) */
+    EVO_ERR_DEVICE_WAIT = -8,   /* a kernel's bounded wait ran out (evo_device_status) */
+    EVO_ERR_TOO_LARGE = -9      /* problem exceeds a fixed-capacity entry point   */
+};
+
+/* Library ABI version (major*100 + minor). */
+int evo_version(void);
+const char* evo_strerror(int code);
+/* cudaError_t of the most recent failing runtime call on this thread (0 if none). */
+int evo_last_cuda_error(void);
+
+/* Forward.  Replaces evoattention_forward (evo_h100/tk_evoattention.cu:911-1043):
+ * O = softmax(q k^T * scale + pair_bias + res_mask) v, LSE saved for backward.
+ * scale <= 0 means 1/sqrt(D) (tk_evoattention.cu:988-990).  Unlike the
+ * reference it does not allocate outputs and does not synchronise the stream
+ * (tk_evoattention.cu:977-978, :1040). */
+int evo_fwd(const EvoDims* dims, const void* q, const void* k, const void* v,
+            const void* pair_bias, const void* res_mask, void* o, float* lse, float scale,
+            void* stream);
+
+/* Bytes of scratch evo_bwd needs for these dims (delta rows + fp32 dQ accumulator). */
+size_t evo_bwd_workspace_bytes(const EvoDims* dims);
+
+/* Backward.  Replaces evoattention_backward (tk_evoattention.cu:1051-1197):
+ * recomputes P from LSE; dq = scale * dS k, dk = scale * dS^T q, dv = P^T d_o,
+ * dbias = sum over S of dS (unscaled, tk_evoattention.cu:824-833), dS = P o (dP - delta).
+ * dq/dk/dv are written as bf16 in the caller layout (the reference returns
+ * padded fp32, tk_evoattention.cu:1109-1112); dbias (fp32) is overwritten, not
+ * accumulated into.  `workspace` is scratch of at least
+ * evo_bwd_workspace_bytes(dims), 256-byte aligned; its contents are undefined
+ * afterwards. */
+int evo_bwd(const EvoDims* dims, const void* q, const void* k, const void* v,
+            const void* pair_bias, const void* res_mask, const void* o, const float* lse,
+            const void* d_o, void* dq, void* dk, void* dv, float* dbias, void* workspace,
+            size_t workspace_bytes, float scale, void* stream);
+
+/* Reads (and clears) the device status word that kernels set when a bounded
+ * wait gives up.  Synchronises the device.  Returns EVO_OK, EVO_ERR_DEVICE_WAIT
+ * (raw word in *raw if non-NULL) or EVO_ERR_CUDA.  The reference has no
+ * counterpart: its kernels wait without bound. */
+int evo_device_status(uint32_t* raw);
+
+/* Unit check of the tensor-core operand conventions used by the kernels (no
+ * counterpart in the reference).  x: bf16 [128][128], y, z: bf16 [128][D].
+ *   out_yzt [128][128] = y z^T      (both operands K-major row tiles)
+ *   out_xy  [128][D]   = x y        (A K-major square tile, B MN-major row tile)
+ *   out_xty [128][D]   = x^T y      (A MN-major square tile, B MN-major row tile)
+ * all fp32. */
+int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
+                     float* out_xy, float* out_xty, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EVOATTN_H_ */

@@ -1,0 +1,114 @@
+"""ctypes binding of libevoattn.so (the C ABI declared in include/evoattn.h).
+
+There is no fallback: if the library is missing or a call fails, this module
+raises.  Build the library with `python megakernel-exploration_b200/build.py`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libevoattn.so")
+
+ABI_VERSION = 100
+
+
+class EvoDims(C.Structure):
+    _fields_ = [("B", C.c_int32), ("S", C.c_int32), ("N", C.c_int32),
+                ("H", C.c_int32), ("D", C.c_int32)]
+
+
+class EvoAttnError(RuntimeError):
+    def __init__(self, code: int, what: str, detail: str = ""):
+        self.code = code
+        super().__init__(f"libevoattn: {what} failed with {code}: {detail}")
+
+
+# name -> (restype, argtypes); every symbol include/evoattn.h declares
+SYMBOLS = {
+    "evo_version": (C.c_int, []),
+    "evo_strerror": (C.c_char_p, [C.c_int]),
+    "evo_last_cuda_error": (C.c_int, []),
+    "evo_fwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 7 + [C.c_float, C.c_void_p]),
+    "evo_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
+    "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 13 + [C.c_size_t, C.c_float, C.c_void_p]),
+    "evo_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
+    "evo_selftest_mma": (C.c_int, [C.c_int] + [C.c_void_p] * 7),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib() -> C.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise ImportError(
+                    f"{LIB_PATH} not found: build it with "
+                    f"`python {os.path.join(HERE, 'build.py')}` (needs nvcc, sm_100a)")
+            h = C.CDLL(LIB_PATH)
+            for name, (res, args) in SYMBOLS.items():
+                fn = getattr(h, name)   # AttributeError if the symbol is not exported
+                fn.restype = res
+                fn.argtypes = args
+            v = h.evo_version()
+            if v // 100 != ABI_VERSION // 100:
+                raise ImportError(f"libevoattn ABI {v} does not match binding {ABI_VERSION}")
+            _lib = h
+    return _lib
+
+
+def strerror(code: int) -> str:
+    return lib().evo_strerror(code).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        detail = strerror(code)
+        if code == -7:
+            detail += f" (cudaError {lib().evo_last_cuda_error()})"
+        raise EvoAttnError(code, what, detail)
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def fwd(dims: EvoDims, q, k, v, bias, mask, o, lse, scale: float, stream: int) -> None:
+    check(lib().evo_fwd(C.byref(dims), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
+                        _ptr(o), _ptr(lse), float(scale), stream), "evo_fwd")
+
+
+def bwd_workspace_bytes(dims: EvoDims) -> int:
+    return int(lib().evo_bwd_workspace_bytes(C.byref(dims)))
+
+
+def bwd(dims: EvoDims, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, workspace,
+        scale: float, stream: int) -> None:
+    check(lib().evo_bwd(C.byref(dims), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
+                        _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv),
+                        _ptr(dbias), _ptr(workspace),
+                        workspace.numel() * workspace.element_size(), float(scale), stream),
+          "evo_bwd")
+
+
+def device_status() -> int:
+    """Synchronises the device; raises if a kernel reported a timed-out wait."""
+    raw = C.c_uint32(0)
+    code = lib().evo_device_status(C.byref(raw))
+    if code != 0:
+        raise EvoAttnError(code, "evo_device_status",
+                           f"{strerror(code)} (status word 0x{raw.value:08x})")
+    return 0
+
+
+def selftest_mma(D: int, x, y, z, out_yzt, out_xy, out_xty, stream: int) -> None:
+    check(lib().evo_selftest_mma(int(D), _ptr(x), _ptr(y), _ptr(z), _ptr(out_yzt), _ptr(out_xy),
+                                 _ptr(out_xty), stream), "evo_selftest_mma")

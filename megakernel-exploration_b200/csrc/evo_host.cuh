@@ -1,0 +1,52 @@
+// Host-side helpers shared by the launchers: error codes, the driver entry
+// point for tensor-map encoding (resolved at run time so the library has no
+// link-time dependency on libcuda), and tensor-map builders for the layouts
+// this library reads and writes.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/evoattn.h"
+
+namespace evo {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Returns nullptr when no CUDA driver is present.
+EncodeTiledFn encode_tiled_fn();
+
+struct TmapDim {
+    uint64_t extent;       // elements
+    uint64_t stride_bytes; // ignored for dim 0 (contiguous)
+    uint32_t box;          // elements
+};
+
+// rank <= 5; dims[0] is the contiguous one.  Returns EVO_OK or an error code.
+int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int rank,
+              const TmapDim* dims, CUtensorMapSwizzle swz);
+
+inline CUtensorMapSwizzle row_swizzle(int D) {
+    return D == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+}
+
+// bf16 [BS][N][H][D] (contiguous) viewed as (D, H, N, BS); box = one head's
+// [rows x D] tile, swizzled by row.
+int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows);
+// fp32 [BS][N][H][D] viewed the same way; box [rows x 32 floats] (128 B, 128B swizzle).
+int make_tmap_qkv_f32(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows);
+// bf16 [B][H][N][N] viewed as (N, N, H, B); box [128 rows x 64 cols], 128B swizzle.
+int make_tmap_bias(CUtensorMap* out, const void* base, int B, int H, int N);
+// fp32 [B][H][N][N] viewed as (N, N, H, B); box [128 rows x 32 cols], 128B swizzle.
+int make_tmap_dbias(CUtensorMap* out, const void* base, int B, int H, int N);
+
+int check_dims(const EvoDims* d);
+// Device address of this device's status word (nullptr on failure).
+unsigned int* status_word();
+int cuda_err(cudaError_t e);
+
+}  // namespace evo

@@ -1,0 +1,130 @@
+// Unit check of the UMMA operand conventions (descriptor builders in
+// evo_tiles.cuh) that the attention kernels rely on: one CTA multiplies small
+// tiles through exactly the descriptors the real kernels use, and the host
+// compares against a CPU GEMM.
+#include "evo_host.cuh"
+#include "evo_tiles.cuh"
+
+namespace evo {
+
+template <int DH>
+__global__ void __launch_bounds__(128, 1)
+selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_z,
+                    const __nv_bfloat16* __restrict__ x, float* __restrict__ out_yzt,
+                    float* __restrict__ out_xy, float* __restrict__ out_xty, unsigned int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sX = smem;                                // 32 KB square tile
+    uint8_t* sY = sX + SQ_BYTES;                       // row tile
+    uint8_t* sZ = sY + RowTile<DH>::BYTES;             // row tile
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sZ + RowTile<DH>::BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    WaitCtx wc{abort_flag, status};
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        fence_mbar_init();
+        fence_async_smem();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, 256);
+        tmem_relinquish();
+    }
+    // X: row `tid`, sixteen 16-byte chunks, into the swizzled square tile.
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(x + tid * 128);
+#pragma unroll
+        for (int cc = 0; cc < 16; ++cc) {
+            *reinterpret_cast<uint4*>(sX + sq_chunk_off(tid, cc)) = src[cc];
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (tid == 0) {
+        mbar_arrive_expect_tx(&bars[0], 2 * RowTile<DH>::BYTES);
+        tma_load_4d(sY, &tm_y, &bars[0], 0, 0, 0, 0);
+        tma_load_4d(sZ, &tm_z, &bars[0], 0, 0, 0, 0);
+        if (mbar_wait(&bars[0], 0, wc, 1)) {
+            tc_fence_after();
+            const uint32_t aX = smem_u32(sX), aY = smem_u32(sY), aZ = smem_u32(sZ);
+#pragma unroll
+            for (int kb = 0; kb < RowTile<DH>::KBLOCKS; ++kb)
+                umma_ss(tmem + 0, RowTile<DH>::kmajor(aY, kb), RowTile<DH>::kmajor(aZ, kb),
+                        make_idesc_bf16(128, 128, 0, 0), kb > 0);
+#pragma unroll
+            for (int kb = 0; kb < 8; ++kb)
+                umma_ss(tmem + 128, sq_kmajor(aX, kb), RowTile<DH>::mnmajor(aY, kb),
+                        make_idesc_bf16(128, DH, 0, 1), kb > 0);
+#pragma unroll
+            for (int kb = 0; kb < 8; ++kb)
+                umma_ss(tmem + 128 + DH, sq_mnmajor(aX, kb), RowTile<DH>::mnmajor(aY, kb),
+                        make_idesc_bf16(128, DH, 1, 1), kb > 0);
+            umma_commit(&bars[1]);
+        }
+    }
+    __syncwarp();
+    if (warp_all(mbar_wait(&bars[1], 0, wc, 2))) {
+        tc_fence_after();
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            tmem_ld32(lane_base + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out_yzt[tid * 128 + c * 32 + i] = __uint_as_float(r[i]);
+        }
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+            tmem_ld32(lane_base + 128 + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out_xy[tid * DH + c * 32 + i] = __uint_as_float(r[i]);
+            tmem_ld32(lane_base + 128 + DH + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out_xty[tid * DH + c * 32 + i] = __uint_as_float(r[i]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+template <int DH>
+static int launch_selftest(const void* x, const void* y, const void* z, float* o0, float* o1,
+                           float* o2, cudaStream_t st) {
+    CUtensorMap tm_y, tm_z;
+    int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128);
+    if (rc) return rc;
+    rc = make_tmap_qkv(&tm_z, z, 1, 128, 1, DH, 128);
+    if (rc) return rc;
+    unsigned int* status = status_word();
+    if (!status) return EVO_ERR_CUDA;
+    const int smem = SQ_BYTES + 2 * RowTile<DH>::BYTES + 64 + 1024;
+    rc = cuda_err(cudaFuncSetAttribute(selftest_mma_kernel<DH>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (rc) return rc;
+    selftest_mma_kernel<DH><<<1, 128, smem, st>>>(tm_y, tm_z, static_cast<const __nv_bfloat16*>(x),
+                                                   o0, o1, o2, status);
+    return cuda_err(cudaGetLastError());
+}
+
+}  // namespace evo
+
+extern "C" int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
+                                float* out_xy, float* out_xty, void* stream) {
+    if (!x || !y || !z || !out_yzt || !out_xy || !out_xty) return EVO_ERR_NULL_PTR;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (D == 32) return evo::launch_selftest<32>(x, y, z, out_yzt, out_xy, out_xty, st);
+    if (D == 64) return evo::launch_selftest<64>(x, y, z, out_yzt, out_xy, out_xty, st);
+    return EVO_ERR_BAD_DIMS;
+}

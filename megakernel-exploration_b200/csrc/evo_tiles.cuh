@@ -1,0 +1,59 @@
+// Shared-memory tile conventions used by every kernel of this library, and the
+// UMMA descriptors that address them.
+//
+// ROW TILE  [R rows][DH bf16], DH in {32, 64}: what one TMA box load of a
+//   q/k/v/dO tile produces.  Row pitch 2*DH bytes (64 B or 128 B), swizzled
+//   with the matching TMA mode (SWIZZLE_64B / SWIZZLE_128B); the tile base is
+//   1024-byte aligned.
+//     * as a K-major operand  (rows index M or N, DH is the contraction axis)
+//     * as an MN-major operand (rows index K, DH is the M or N axis)
+//
+// SQUARE TILE [128 rows][128 bf16]: P / dS, written by threads.  Stored as two
+//   sub-tiles of [128 rows][64 bf16] (16 KB each, 128-byte rows, 128B swizzle):
+//   16-byte chunk c of row r of sub-tile t sits at
+//       t*16384 + r*128 + ((c ^ (r & 7)) << 4).
+//     * as a K-major A operand  (rows = M, columns = K)
+//     * as an MN-major A operand (rows = K, columns = M)
+#pragma once
+#include "evo_ptx.cuh"
+
+namespace evo {
+
+constexpr int TILE = 128;                 // q rows and kv rows per tile
+constexpr uint32_t SQ_SUB_BYTES = 16384;  // one [128][64] bf16 sub-tile
+constexpr uint32_t SQ_BYTES = 2 * SQ_SUB_BYTES;
+
+template <int DH>
+struct RowTile {
+    static_assert(DH == 32 || DH == 64, "head dim 32 or 64");
+    static constexpr uint32_t ROW_BYTES = DH * 2;
+    static constexpr uint32_t SWZ = (DH == 32) ? SWZ_64B : SWZ_128B;
+    static constexpr uint32_t SBO = 8 * ROW_BYTES;       // eight rows
+    static constexpr uint32_t BYTES = TILE * ROW_BYTES;  // 128-row tile
+    static constexpr int KBLOCKS = DH / 16;              // UMMA K = 16 for bf16
+
+    // K-major operand, contraction block kb (16 bf16 = 32 bytes along the row).
+    __device__ static __forceinline__ uint64_t kmajor(uint32_t saddr, int kb) {
+        return make_smem_desc(saddr + kb * 32, 16, SBO, SWZ);
+    }
+    // MN-major operand, contraction block kb = rows 16*kb .. 16*kb+15.
+    __device__ static __forceinline__ uint64_t mnmajor(uint32_t saddr, int kb) {
+        return make_smem_desc(saddr + kb * 16 * ROW_BYTES, BYTES, SBO, SWZ);
+    }
+};
+
+// Byte offset of the 16-byte chunk `cc` (0..15, eight bf16 columns each) of row r.
+__device__ __forceinline__ uint32_t sq_chunk_off(int r, int cc) {
+    return (cc >> 3) * SQ_SUB_BYTES + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+}
+// Square tile as K-major A: contraction block kb (0..7) = columns 16*kb..16*kb+15.
+__device__ __forceinline__ uint64_t sq_kmajor(uint32_t saddr, int kb) {
+    return make_smem_desc(saddr + (kb >> 2) * SQ_SUB_BYTES + (kb & 3) * 32, 16, 1024, SWZ_128B);
+}
+// Square tile as MN-major A (M = the 128 columns, two 64-wide swizzle atoms
+// SQ_SUB_BYTES apart): contraction block kb (0..7) = rows 16*kb..16*kb+15.
+__device__ __forceinline__ uint64_t sq_mnmajor(uint32_t saddr, int kb) {
+    return make_smem_desc(saddr + kb * 16 * 128, SQ_SUB_BYTES, 1024, SWZ_128B);
+}
+
+}  // namespace evo

@@ -1,0 +1,42 @@
+"""Shared helpers of the GPU parity tests."""
+import torch
+
+from oracle import evo_ref
+
+
+def bf16_round(*ts):
+    return tuple(t.to(torch.bfloat16).float() for t in ts)
+
+
+def run_layer(q, k, v, mask, bias, d_o, device="cuda"):
+    """fwd + bwd through TKEvoAttention on `device`; returns fp32 CPU tensors."""
+    from tk_evo_attention_layer import TKEvoAttention
+    Q = q.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
+    K = k.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
+    V = v.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
+    PB = bias.to(device=device, dtype=torch.float32).requires_grad_(True)
+    M = mask.to(device)
+    O = TKEvoAttention.apply(Q, K, V, M, PB)
+    O.backward(d_o.to(device=device, dtype=torch.bfloat16))
+    import _evoattn
+    _evoattn.device_status()
+    return {"o": O.detach().float().cpu(), "dq": Q.grad.float().cpu(), "dk": K.grad.float().cpu(),
+            "dv": V.grad.float().cpu(), "dbias": PB.grad.float().cpu()}
+
+
+def oracle_on_rounded(q, k, v, mask, bias, d_o, s_chunk=32):
+    """The oracle evaluated on the same bf16-rounded inputs the kernels see."""
+    qr, kr, vr, br, mr, dor = bf16_round(q, k, v, bias, mask, d_o)
+    return evo_ref.evo_attention_fwd_bwd_ref(qr, kr, vr, mr, br, dor, s_chunk=s_chunk)
+
+
+def assert_parity(ref, got, names=("o", "dq", "dk", "dv", "dbias"), tag=""):
+    """max-abs <= 2e-2 and relative-L2 <= 1e-2 on every tensor (fp32 compare)."""
+    worst = {}
+    for n in names:
+        ma, rl = evo_ref.parity(ref[n], got[n])
+        worst[n] = (ma, rl)
+    bad = {n: w for n, w in worst.items()
+           if not (w[0] <= evo_ref.MAX_ABS_TOL and w[1] <= evo_ref.REL_L2_TOL)}
+    assert not bad, f"{tag} parity failed: {bad} (all: {worst})"
+    return worst

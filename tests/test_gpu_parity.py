@@ -1,0 +1,156 @@
+"""GPU parity of the sm_100a EvoAttention kernels against the CPU oracle.
+
+Every case goes through the reference-facing operator (TKEvoAttention.apply,
+which calls the C ABI of libevoattn.so) on seeded inputs; the oracle sees the
+same bf16-rounded inputs.  Bar: fp32 compare, max-abs <= 2e-2 and
+relative-L2 <= 1e-2 for O, dQ, dK, dV and dBias.
+"""
+import pytest
+import torch
+
+from oracle import evo_ref
+from _util import assert_parity, oracle_on_rounded, run_layer
+
+pytestmark = pytest.mark.gpu
+
+# (B, S, H, N, D): the reference's own case grid (evo_h100/test_tk_evoattention.py:80-103,
+# evo_h100/test_tk_evoattention_bwd.py:102-112) restricted to the head dims built
+# here (D=96/128 are not), with the reference's input distributions.
+REFERENCE_GRID = [
+    (1, 1, 4, 128, 64), (1, 1, 4, 256, 64), (1, 1, 4, 384, 64), (2, 1, 16, 384, 64),
+    (4, 1, 16, 256, 64), (1, 32, 4, 384, 64), (1, 64, 4, 256, 64), (2, 1, 16, 256, 64),
+    (1, 4, 4, 256, 64),
+    (1, 1, 4, 384, 32), (1, 32, 4, 256, 32), (2, 4, 8, 384, 32),
+    (1, 1, 4, 384, 16), (1, 16, 4, 256, 16),
+]
+
+
+@pytest.mark.parametrize("B,S,H,N,D", REFERENCE_GRID)
+def test_reference_grid(B, S, H, N, D):
+    q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "randint", seed=B * 1000 + S + N + D)
+    got = run_layer(q, k, v, mask, bias, d_o)
+    ref = oracle_on_rounded(q, k, v, mask, bias, d_o)
+    assert_parity(ref, got, tag=f"B={B} S={S} H={H} N={N} D={D}")
+
+
+# edge cases the reference never tested: ragged N (not a multiple of 128), a
+# single partial tile, S that does not divide the row chunk, B > 1 with S > 1
+EDGE_CASES = [
+    (1, 32, 4, 64, 32, "bernoulli0.9"),     # BASELINE config 1's shape, bf16
+    (1, 3, 2, 8, 32, "valid"),              # smallest N
+    (1, 5, 2, 200, 32, "tail0to32"),        # ragged N, odd S
+    (2, 3, 3, 136, 64, "bernoulli0.95"),    # ragged N, D=64, odd H
+    (1, 2, 2, 520, 32, "tail10pct"),        # five tiles, ragged
+    (1, 7, 1, 384, 32, "valid"),            # one head
+]
+
+
+@pytest.mark.parametrize("B,S,H,N,D,mk", EDGE_CASES)
+def test_edge_cases(B, S, H, N, D, mk):
+    q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, mk, seed=S * 31 + N)
+    got = run_layer(q, k, v, mask, bias, d_o)
+    ref = oracle_on_rounded(q, k, v, mask, bias, d_o)
+    assert_parity(ref, got, tag=f"B={B} S={S} H={H} N={N} D={D} {mk}")
+
+
+def test_golden_config1():
+    """BASELINE config 1 against the committed fixture (tests/golden/)."""
+    import os
+    import numpy as np
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "cfg1_golden.npz"))
+    q, k, v, mask, bias, d_o = evo_ref.make_workload("cfg1_cpu_fp32")
+    got = run_layer(q, k, v, mask, bias, d_o)
+    rows = g["rows"].tolist()
+    # the fixture is the fp32 oracle on UNROUNDED inputs; the kernels see bf16
+    # inputs, so this is a looser sanity bound.  Exact-input parity is asserted
+    # against the oracle on the rounded inputs below.
+    for n in ("o", "dq", "dk", "dv"):
+        ref = torch.from_numpy(g[n])
+        assert evo_ref.rel_l2_err(ref, got[n][:, rows]) < 3e-2, n
+    assert evo_ref.rel_l2_err(torch.from_numpy(g["dbias"]), got["dbias"]) < 3e-2
+    ref = oracle_on_rounded(q, k, v, mask, bias, d_o)
+    assert_parity(ref, got, tag="cfg1")
+
+
+@pytest.mark.parametrize("name", ["cfg2_msa_row", "cfg3_triangle"])
+def test_full_size_configs(name):
+    q, k, v, mask, bias, d_o = evo_ref.make_workload(name)
+    got = run_layer(q, k, v, mask, bias, d_o)
+    ref = oracle_on_rounded(q, k, v, mask, bias, d_o)
+    assert_parity(ref, got, tag=name)
+
+
+@pytest.mark.parametrize("name,S_sub", [("cfg4_large_msa", 48), ("cfg5_long_triangle", 24)])
+def test_large_configs_row_subset(name, S_sub):
+    """Configs 4/5 at their full N/H/D on the first S_sub rows (rows are
+    independent problems; the oracle at full S would take minutes)."""
+    q, k, v, mask, bias, d_o = evo_ref.make_workload(name, 0, S_sub)
+    got = run_layer(q, k, v, mask, bias, d_o)
+    ref = oracle_on_rounded(q, k, v, mask, bias, d_o, s_chunk=8)
+    assert_parity(ref, got, tag=name)
+
+
+def test_full_size_properties_config4():
+    """Size-independent properties at config 4's full size: rows of S are
+    independent (a row block recomputed alone reproduces the same O, dQ, dK, dV
+    bit for bit) and dBias is additive over row blocks (sum of the shards'
+    dBias equals the full dBias up to fp32 summation order)."""
+    name = "cfg4_large_msa"
+    B, S, N, H, D = evo_ref.WORKLOADS[name][:5]
+    q, k, v, mask, bias, d_o = evo_ref.make_workload(name)
+    full = run_layer(q, k, v, mask, bias, d_o)
+    acc = torch.zeros_like(full["dbias"])
+    for lo in range(0, S, S // 4):
+        hi = lo + S // 4
+        part = run_layer(q[:, lo:hi], k[:, lo:hi], v[:, lo:hi], mask[:, lo:hi], bias, d_o[:, lo:hi])
+        for n in ("o", "dk", "dv"):
+            assert torch.equal(part[n], full[n][:, lo:hi]), (n, lo)
+        # dQ goes through fp32 reduce-adds whose order may differ between runs
+        assert evo_ref.max_abs_err(full["dq"][:, lo:hi], part["dq"]) <= 2.0 ** -6, ("dq", lo)
+        acc += part["dbias"]
+    ma, rl = evo_ref.parity(full["dbias"], acc)
+    assert ma <= 1e-3 and rl <= 1e-4, (ma, rl)
+    for n in ("o", "dq", "dk", "dv", "dbias"):
+        assert torch.isfinite(full[n]).all(), n
+
+
+def test_deterministic_forward():
+    q, k, v, mask, bias, d_o = evo_ref.make_workload("cfg3_triangle", 0, 16)
+    a = run_layer(q, k, v, mask, bias, d_o)
+    b = run_layer(q, k, v, mask, bias, d_o)
+    assert torch.equal(a["o"], b["o"])
+    assert torch.equal(a["dk"], b["dk"]) and torch.equal(a["dv"], b["dv"])
+
+
+def test_c_abi_direct():
+    """evo_fwd / evo_bwd called straight through ctypes with raw device pointers."""
+    import _evoattn
+    B, S, N, H, D = 1, 4, 256, 4, 32
+    q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "tail0to32", seed=5)
+    dev = "cuda"
+    bf = torch.bfloat16
+    qd, kd, vd, dod = (t.to(dev, bf) for t in (q, k, v, d_o))
+    bd = bias.reshape(B, H, N, N).to(dev, bf)
+    md = mask.reshape(B, S, N).to(dev, bf)
+    o = torch.empty_like(qd)
+    lse = torch.empty((B, S, H, N), dtype=torch.float32, device=dev)
+    dims = _evoattn.EvoDims(B, S, N, H, D)
+    st = torch.cuda.current_stream().cuda_stream
+    _evoattn.fwd(dims, qd, kd, vd, bd, md, o, lse, 0.0, st)      # scale <= 0 -> 1/sqrt(D)
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
+    dbias = torch.empty((B, H, N, N), dtype=torch.float32, device=dev)
+    ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=dev)
+    _evoattn.bwd(dims, qd, kd, vd, bd, md, o, lse, dod, dq, dk, dv, dbias, ws, 0.0, st)
+    _evoattn.device_status()
+    ref = oracle_on_rounded(q, k, v, mask, bias, d_o)
+    got = {"o": o.float().cpu(), "dq": dq.float().cpu(), "dk": dk.float().cpu(), "dv": dv.float().cpu(),
+           "dbias": dbias.unsqueeze(1).cpu()}
+    assert_parity(ref, got, tag="c-abi")
+    qr, kr, br, mr = (t.to(bf).float() for t in (q, k, bias, mask))
+    lse_ref = evo_ref.evo_lse_ref(qr, kr, mr, br)
+    assert evo_ref.max_abs_err(lse_ref, lse.cpu()) < 1e-2
+    # argument validation returns codes, never throws from C
+    bad = _evoattn.EvoDims(B, S, N, H, 128)
+    with pytest.raises(_evoattn.EvoAttnError) as ei:
+        _evoattn.fwd(bad, qd, kd, vd, bd, md, o, lse, 0.0, st)
+    assert ei.value.code == -1

@@ -1,0 +1,46 @@
+"""Host-side behaviour of the operator surface (no GPU): the reference's
+names, shape assertions and head-dim rules."""
+import pytest
+import torch
+
+
+def _inputs(B=1, S=2, N=16, H=2, D=32):
+    q = torch.zeros((B, S, N, H, D))
+    return q, q.clone(), q.clone(), torch.zeros((B, S, 1, 1, N)), torch.zeros((B, 1, H, N, N))
+
+
+def test_surface_names():
+    import tk_evo_attention_layer as L
+    assert hasattr(L, "TKEvoAttention") and issubclass(L.TKEvoAttention, torch.autograd.Function)
+    assert L.TK_SUPPORTED_DIMS == (32, 64)
+    assert L._next_supported_dim(16) == 32 and L._next_supported_dim(32) == 32
+    assert L._next_supported_dim(33) == 64 and L._next_supported_dim(64) == 64
+    with pytest.raises(ValueError):
+        L._next_supported_dim(96)
+    with pytest.raises(ValueError):
+        L._next_supported_dim(128)
+
+
+def test_shape_errors_are_assertions():
+    from tk_evo_attention_layer import TKEvoAttention
+    q, k, v, m, b = _inputs()
+    with pytest.raises(AssertionError):
+        TKEvoAttention.apply(q, k[:, :1], v, m, b)
+    with pytest.raises(AssertionError):
+        TKEvoAttention.apply(q, k, v, m.reshape(1, 2, 16), b)
+    with pytest.raises(AssertionError):
+        TKEvoAttention.apply(q, k, v, m, b.squeeze(1))
+
+
+def test_no_cpu_fallback():
+    from tk_evo_attention_layer import TKEvoAttention
+    q, k, v, m, b = _inputs()
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        TKEvoAttention.apply(q, k, v, m, b)
+
+
+def test_unsupported_head_dim():
+    from tk_evo_attention_layer import TKEvoAttention
+    q, k, v, m, b = _inputs(D=128)
+    with pytest.raises(ValueError):
+        TKEvoAttention.apply(q, k, v, m, b)
