@@ -1,0 +1,330 @@
+"""EvoAttention fwd+bwd benchmark (one JSON line on stdout, printed by rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2_msa_row] [--scaling weak|strong]
+
+A step is one forward + backward of the workload through
+TKEvoAttention.apply on seeded synthetic inputs.  N=1 runs BASELINE config 2
+(B=1, S=512, N=384, H=8, D=32, bf16).  N>1 (under torchrun, one rank per GPU)
+shards the independent S axis over ranks with the pair bias replicated and an
+NCCL all-reduce of dBias in backward: "weak" keeps S rows per GPU fixed,
+"strong" splits the workload's S over the ranks.
+
+value      whole-job TFLOP/s, algorithmic FLOPs 14*B*S*H*N^2*D, inputs resident in HBM
+e2e        same metric with host (pinned) buffers: H2D of q,k,v,dO,mask,bias and
+           D2H of O,dQ,dK,dV,dBias inside the timed region
+roofline   backward main kernel: its 10*B*S*H*N^2*D FLOPs / its CUDA-event time,
+           against the measured sustained bf16 GEMM peak
+cpu_baseline / --impl reference   the eager PyTorch restatement on the host cores
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "megakernel-exploration_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import evo_workloads as wl  # noqa: E402
+
+METRIC = "EvoAttention fwd+bwd TFLOP/s"
+UNIT = "TFLOP/s"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops_sustained"]), "measured sustained cuBLAS bf16 (MEASURED_PEAKS.json)"
+    return 1400.0, "fallback sustained bf16 estimate"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the
+    timed region runs (reading only)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def _cpu_fwd_bwd(name: str, rows: int, repeats: int):
+    """Eager oracle on the host cores over `rows` S rows of the workload; returns
+    (TFLOP/s, seconds per pass, threads)."""
+    from oracle import evo_ref
+    B, S, N, H, D = wl.WORKLOADS[name][:5]
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v, mask, bias, d_o = wl.make_workload(name, 0, rows)
+    evo_ref.evo_attention_fwd_bwd_ref(q[:, :4], k[:, :4], v[:, :4], mask[:, :4], bias, d_o[:, :4])  # warm-up
+    ts = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        evo_ref.evo_attention_fwd_bwd_ref(q, k, v, mask, bias, d_o, s_chunk=32)
+        ts.append(time.perf_counter() - t0)
+    sec = min(ts)
+    return wl.flops_fwd_bwd(B, rows, N, H, D) / sec / 1e12, sec, torch.get_num_threads()
+
+
+def run_reference(args, rank: int):
+    """The reference's path on the host CPU: its documented math restated in eager
+    PyTorch (the reference kernel itself needs ThunderKittens and an sm_90a GPU)."""
+    if rank != 0:
+        return
+    name = args.workload
+    B, S, N, H, D = wl.WORKLOADS[name][:5]
+    vals = []
+    torch.set_num_threads(os.cpu_count() or 1)
+    from oracle import evo_ref
+    # size the per-step sample so that the whole run takes about a minute
+    probe = wl.make_workload(name, 0, min(S, 4))
+    t0 = time.perf_counter()
+    evo_ref.evo_attention_fwd_bwd_ref(*probe[:3], probe[3], probe[4], probe[5])
+    per_row = (time.perf_counter() - t0) / min(S, 4)
+    rows = int(60.0 / max(args.steps + args.warmup, 1) / max(per_row, 1e-6))
+    rows = max(2, min(S, args.cpu_rows, rows))
+    q, k, v, mask, bias, d_o = wl.make_workload(name, 0, rows)
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        evo_ref.evo_attention_fwd_bwd_ref(q, k, v, mask, bias, d_o, s_chunk=32)
+        dt = time.perf_counter() - t0
+        if i >= args.warmup:
+            vals.append(dt)
+    sec = sum(vals) / len(vals)
+    tf = wl.flops_fwd_bwd(B, rows, N, H, D) / sec / 1e12
+    sample = f"{rows} of {S} S rows of {name} per step (rows are independent), fp32 eager, S-chunked by 32"
+    out = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": name, "B": B, "S": S, "N": N, "H": H, "D": D, "sample": sample},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch.distributed as dist
+    import _evoattn
+    from tk_evo_attention_layer import TKEvoAttention
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    pg = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        pg = dist.group.WORLD
+
+    name = args.workload
+    B, S, N, H, D = wl.WORKLOADS[name][:5]
+    if args.rows:
+        S = args.rows
+    if args.scaling == "weak":
+        rows, S_total = S, S * world
+        lo = rank * S
+    else:
+        assert S % world == 0, "strong scaling needs S divisible by the number of GPUs"
+        rows, S_total = S // world, S
+        lo = rank * rows
+    q, k, v, mask, bias, d_o = wl.make_workload(name, lo, lo + rows, S_override=S_total)
+    bf = torch.bfloat16
+    # host side: pinned bf16 / fp32 buffers (what a host-buffer caller would hold)
+    h_in = [t.to(bf).pin_memory() for t in (q, k, v, d_o)] + [mask.to(bf).pin_memory(), bias.pin_memory()]
+    d_in = [t.to(dev, non_blocking=True) for t in h_in]
+    Q, K, V, DO, M, PB = d_in
+    for t in (Q, K, V, PB):
+        t.requires_grad_(True)
+    h_out = [torch.empty((B, rows, N, H, D), dtype=bf).pin_memory() for _ in range(4)]
+    h_out.append(torch.empty((B, 1, H, N, N), dtype=torch.float32).pin_memory())
+    h2d = sum(t.numel() * t.element_size() for t in h_in)
+    d2h = sum(t.numel() * t.element_size() for t in h_out)
+
+    def step():
+        for t in (Q, K, V, PB):
+            t.grad = None
+        if pg is None:
+            O = TKEvoAttention.apply(Q, K, V, M, PB)
+        else:
+            O = TKEvoAttention.apply(Q, K, V, M, PB, pg)
+        O.backward(DO)
+        return O
+
+    def step_e2e():
+        ins = [h.to(dev, non_blocking=True) for h in h_in]
+        q_, k_, v_, do_, m_, pb_ = ins
+        for t in (q_, k_, v_, pb_):
+            t.requires_grad_(True)
+        O = TKEvoAttention.apply(q_, k_, v_, m_, pb_) if pg is None else TKEvoAttention.apply(q_, k_, v_, m_, pb_, pg)
+        O.backward(do_)
+        for dst, src in zip(h_out, (O.detach(), q_.grad, k_.grad, v_.grad, pb_.grad)):
+            dst.copy_(src, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _evoattn.device_status()
+    _evoattn.profile_enable(True)
+    with ClockSampler(local_rank) as cs:
+        ms_total = timed(step, args.steps)
+    _evoattn.profile_enable(False)
+    fwd_ms, fwd_n = _evoattn.profile_read(0)
+    bwd_ms, bwd_n = _evoattn.profile_read(1)
+    _evoattn.device_status()
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, e2e_steps)
+    _evoattn.device_status()
+
+    flops_step = wl.flops_fwd_bwd(B, S_total, N, H, D)          # whole job, all ranks
+    ms_step = ms_total / args.steps
+    value = flops_step / (ms_step * 1e-3) / 1e12
+    e2e_value = flops_step / (ms_e2e / e2e_steps * 1e-3) / 1e12
+
+    peak, peak_src = _peaks()
+    bwd_flops_launch = 10.0 * B * rows * H * N * N * D           # this rank's launch
+    bwd_avg_ms = bwd_ms / max(bwd_n, 1)
+    achieved = bwd_flops_launch / (bwd_avg_ms * 1e-3) / 1e12 if bwd_n else None
+    roofline = {
+        "kernel": "evo_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+        "frac": (achieved / peak) if achieved else None, "traffic": None, "peak_source": peak_src,
+        "avg_launch_ms": bwd_avg_ms, "launches_timed": bwd_n,
+        "fwd_kernel": {"avg_launch_ms": fwd_ms / max(fwd_n, 1), "launches_timed": fwd_n,
+                       "achieved": (4.0 * B * rows * H * N * N * D) / (fwd_ms / max(fwd_n, 1) * 1e-3) / 1e12 if fwd_n else None},
+    }
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        S = wl.WORKLOADS[name][1]
+        tf, sec, cores = _cpu_fwd_bwd(name, min(S, args.cpu_rows), 2)
+        cpu = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"{min(S, args.cpu_rows)} of {S} S rows of {name}, fp32 eager PyTorch, best of 2 "
+                         f"({sec:.2f} s per pass)"}
+
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": name, "B": B, "S_total": S_total, "S_per_gpu": rows, "N": N, "H": H, "D": D,
+                       "parallelism": f"S-sharded x{world}, pair bias replicated, NCCL all-reduce of dBias",
+                       "l2": "each step streams > 126 MB (inputs larger than L2)",
+                       "pct_of_2250_dense_bf16": 100.0 * value / (2250.0 * world)},
+            "clocks": cs.summary(),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps},
+            "gpu_launches": 4 * args.steps,
+            "roofline": roofline,
+        }
+        if cpu is not None:
+            out["cpu_baseline"] = cpu
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2_msa_row", choices=sorted(wl.WORKLOADS))
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--cpu-rows", type=int, default=64, help="S rows per CPU pass (bounded sample)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="override the workload's S (small captures under a profiler)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -48,15 +48,21 @@ int evo_version(void);
 const char* evo_strerror(int code);
 /* cudaError_t of the most recent failing runtime call on this thread (0 if none). */
 int evo_last_cuda_error(void);
+/* Text describing the most recent tensor-map encoding failure on this thread ("" if none). */
+const char* evo_last_error_detail(void);
 
 /* Forward.  Replaces evoattention_forward (evo_h100/tk_evoattention.cu:911-1043):
  * O = softmax(q k^T * scale + pair_bias + res_mask) v, LSE saved for backward.
  * scale <= 0 means 1/sqrt(D) (tk_evoattention.cu:988-990).  Unlike the
  * reference it does not allocate outputs and does not synchronise the stream
- * (tk_evoattention.cu:977-978, :1040). */
+ * (tk_evoattention.cu:977-978, :1040).
+ * o_resid (optional, may be NULL): bf16 [B][S][N][H][D] that receives the
+ * rounding residual O_fp32 - bf16(O).  Passing it on to evo_bwd makes
+ * delta = rowsum(dO o O) accurate to about 16 bits of O instead of 8, which
+ * keeps the error of dBias (a sum over S rows) within 2e-2 at large S. */
 int evo_fwd(const EvoDims* dims, const void* q, const void* k, const void* v,
-            const void* pair_bias, const void* res_mask, void* o, float* lse, float scale,
-            void* stream);
+            const void* pair_bias, const void* res_mask, void* o, void* o_resid, float* lse,
+            float scale, void* stream);
 
 /* Bytes of scratch evo_bwd needs for these dims (delta rows + fp32 dQ accumulator). */
 size_t evo_bwd_workspace_bytes(const EvoDims* dims);
@@ -66,19 +72,30 @@ size_t evo_bwd_workspace_bytes(const EvoDims* dims);
  * dbias = sum over S of dS (unscaled, tk_evoattention.cu:824-833), dS = P o (dP - delta).
  * dq/dk/dv are written as bf16 in the caller layout (the reference returns
  * padded fp32, tk_evoattention.cu:1109-1112); dbias (fp32) is overwritten, not
- * accumulated into.  `workspace` is scratch of at least
+ * accumulated into.  o_resid is the optional residual written by evo_fwd (NULL:
+ * delta is computed from the bf16 O alone).  `workspace` is scratch of at least
  * evo_bwd_workspace_bytes(dims), 256-byte aligned; its contents are undefined
  * afterwards. */
 int evo_bwd(const EvoDims* dims, const void* q, const void* k, const void* v,
-            const void* pair_bias, const void* res_mask, const void* o, const float* lse,
-            const void* d_o, void* dq, void* dk, void* dv, float* dbias, void* workspace,
-            size_t workspace_bytes, float scale, void* stream);
+            const void* pair_bias, const void* res_mask, const void* o, const void* o_resid,
+            const float* lse, const void* d_o, void* dq, void* dk, void* dv, float* dbias,
+            void* workspace, size_t workspace_bytes, float scale, void* stream);
 
 /* Reads (and clears) the device status word that kernels set when a bounded
  * wait gives up.  Synchronises the device.  Returns EVO_OK, EVO_ERR_DEVICE_WAIT
  * (raw word in *raw if non-NULL) or EVO_ERR_CUDA.  The reference has no
  * counterpart: its kernels wait without bound. */
 int evo_device_status(uint32_t* raw);
+
+/* Optional timing of the two main kernels with CUDA events recorded on the
+ * caller's stream around each launch (no counterpart in the reference, which
+ * times whole calls from Python, evo_h100/benchmark.py:76-124).
+ * evo_profile_enable(1) starts recording (at most 4096 launches per kernel are
+ * kept), evo_profile_enable(0) stops.  evo_profile_read waits for the recorded
+ * events, returns the summed milliseconds and the launch count of
+ * kernel 0 (forward) or 1 (backward main kernel), and clears that record. */
+int evo_profile_enable(int on);
+int evo_profile_read(int kernel, float* total_ms, int* launches);
 
 /* Unit check of the tensor-core operand conventions used by the kernels (no
  * counterpart in the reference).  x: bf16 [128][128], y, z: bf16 [128][D].

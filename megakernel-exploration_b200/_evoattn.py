@@ -12,7 +12,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libevoattn.so")
 
-ABI_VERSION = 100
+ABI_VERSION = 101
 
 
 class EvoDims(C.Structure):
@@ -31,11 +31,14 @@ SYMBOLS = {
     "evo_version": (C.c_int, []),
     "evo_strerror": (C.c_char_p, [C.c_int]),
     "evo_last_cuda_error": (C.c_int, []),
-    "evo_fwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 7 + [C.c_float, C.c_void_p]),
+    "evo_last_error_detail": (C.c_char_p, []),
+    "evo_fwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 8 + [C.c_float, C.c_void_p]),
     "evo_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
-    "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 13 + [C.c_size_t, C.c_float, C.c_void_p]),
+    "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 14 + [C.c_size_t, C.c_float, C.c_void_p]),
     "evo_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
     "evo_selftest_mma": (C.c_int, [C.c_int] + [C.c_void_p] * 7),
+    "evo_profile_enable": (C.c_int, [C.c_int]),
+    "evo_profile_read": (C.c_int, [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
 }
 
 _lib = None
@@ -74,6 +77,8 @@ def check(code: int, what: str) -> None:
         detail = strerror(code)
         if code == -7:
             detail += f" (cudaError {lib().evo_last_cuda_error()})"
+        if code == -6:
+            detail += f" ({lib().evo_last_error_detail().decode()})"
         raise EvoAttnError(code, what, detail)
 
 
@@ -81,19 +86,19 @@ def _ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
 
 
-def fwd(dims: EvoDims, q, k, v, bias, mask, o, lse, scale: float, stream: int) -> None:
+def fwd(dims: EvoDims, q, k, v, bias, mask, o, o_resid, lse, scale: float, stream: int) -> None:
     check(lib().evo_fwd(C.byref(dims), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
-                        _ptr(o), _ptr(lse), float(scale), stream), "evo_fwd")
+                        _ptr(o), _ptr(o_resid), _ptr(lse), float(scale), stream), "evo_fwd")
 
 
 def bwd_workspace_bytes(dims: EvoDims) -> int:
     return int(lib().evo_bwd_workspace_bytes(C.byref(dims)))
 
 
-def bwd(dims: EvoDims, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, workspace,
+def bwd(dims: EvoDims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, workspace,
         scale: float, stream: int) -> None:
     check(lib().evo_bwd(C.byref(dims), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
-                        _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv),
+                        _ptr(o), _ptr(o_resid), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv),
                         _ptr(dbias), _ptr(workspace),
                         workspace.numel() * workspace.element_size(), float(scale), stream),
           "evo_bwd")
@@ -107,6 +112,17 @@ def device_status() -> int:
         raise EvoAttnError(code, "evo_device_status",
                            f"{strerror(code)} (status word 0x{raw.value:08x})")
     return 0
+
+
+def profile_enable(on: bool) -> None:
+    check(lib().evo_profile_enable(1 if on else 0), "evo_profile_enable")
+
+
+def profile_read(kernel: int):
+    """(total milliseconds, launches) of kernel 0 (forward) / 1 (backward main)."""
+    ms, n = C.c_float(0.0), C.c_int(0)
+    check(lib().evo_profile_read(kernel, C.byref(ms), C.byref(n)), "evo_profile_read")
+    return ms.value, n.value
 
 
 def selftest_mma(D: int, x, y, z, out_yzt, out_xy, out_xty, stream: int) -> None:

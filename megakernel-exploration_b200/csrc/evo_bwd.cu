@@ -22,51 +22,77 @@
 // reference issues one scalar atomic per element per row
 // (tk_evoattention.cu:583-611).
 //
-//   warp 8 (producer)  TMA: K/V tiles + mask rows per item; Q/dO tiles + LSE/delta
-//                      rows per step; the pair-bias tile per q tile
-//   warp 9 (mma)       tcgen05.mma: S = Q K^T, dP = dO V^T, then dV += P^T dO,
-//                      dK += dS^T Q, dQ = dS K, accumulators in tensor memory
+//   warp 8 (producer)  TMA per step: Q, dO tiles and the -LSE / delta rows; K, V
+//                      tiles and the mask row per step (D=32) or per item (D=64)
+//   warp 9 (mma)       tcgen05.mma, issued in whatever order operands become
+//                      ready: S = Q K^T and dP = dO V^T of the next step, or
+//                      dV += P^T dO, dK += dS^T Q, dQ = dS K of the current one
 //   warps 0-3, 4-7     two compute groups; group g owns kv columns 64g..64g+63
-//                      (thread = one q row): P, dS -> shared memory as bf16 MMA
-//                      operands; dBias partial sums; drains dQ (TMA reduce-add
-//                      into the fp32 accumulator), dBias (TMA reduce-add) and
-//                      dK/dV (TMA store, bf16)
+//                      (thread = one q row).  Per step: P and dS from S and dP,
+//                      kept packed in registers until the previous step's
+//                      dV/dK/dQ MMAs have finished reading the P/dS tiles, then
+//                      written to shared memory as MMA operands.  The pair bias
+//                      of a thread's row and 64 columns is loaded straight from
+//                      global memory into registers, one q tile ahead.  Afterwards,
+//                      off the critical path and warp-locally (no barrier beyond
+//                      the warp): each warp stages its 32 rows of the previous
+//                      step's dQ and, after the last row of a chunk, of the dBias
+//                      sums in its own shared-memory slots and issues TMA
+//                      reduce-adds (fp32) for them; after an item, dK/dV go out as
+//                      bf16 stores.
 #include "evo_host.cuh"
 #include "evo_tiles.cuh"
 
+#ifndef EVO_EXP
+#define EVO_EXP 0
+#endif
+
 namespace evo {
 
-constexpr int BWD_THREADS = 320;
-constexpr int BWD_GROUP_THREADS = 256;
+constexpr int BWD_THREADS = 384;           // 3 warpgroups: 2 compute + (producer, mma, 2 idle warps)
 constexpr uint32_t BWD_TMEM_COLS = 512;
+constexpr int BWD_REGS_COMPUTE = 224;
+constexpr int BWD_REGS_OTHER = 56;
 
 template <int DH>
 struct BwdCfg {
-    static constexpr int RC = (DH == 32) ? 2 : 1;    // S rows per chunk
-    static constexpr int QS = (DH == 32) ? 2 : 1;    // Q/dO stages
-    static constexpr int KVB = (DH == 32) ? 2 : 1;   // K/V buffers (items in flight)
+    static constexpr int RC = (DH == 32) ? 3 : 1;     // S rows per chunk
+    static constexpr int QS = (DH == 32) ? 3 : 2;     // load stages
+    // D=32: K/V travel with every step's stage; D=64: one resident K/V buffer per item
+    static constexpr bool KV_RESIDENT = (DH == 64);
+    static constexpr int HALF = DH / 2;               // head-dim columns drained per group
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;
-    static constexpr uint32_t OFF_K = 0;
-    static constexpr uint32_t OFF_V = OFF_K + KVB * RC * ROWT;
-    static constexpr uint32_t OFF_Q = OFF_V + KVB * RC * ROWT;
-    static constexpr uint32_t OFF_DO = OFF_Q + QS * ROWT;
-    static constexpr uint32_t OFF_BIAS = OFF_DO + QS * ROWT;
-    static constexpr uint32_t OFF_P = OFF_BIAS + SQ_BYTES;
-    static constexpr uint32_t OFF_DS = OFF_P + SQ_BYTES;          // P,dS contiguous: dBias staging
-    static constexpr uint32_t OFF_DQS = OFF_DS + SQ_BYTES;        // fp32 [128][DH] dQ staging
-    static constexpr uint32_t DQS_BYTES = 128 * DH * 4;
-    static constexpr uint32_t OFF_ROWV = OFF_DQS + DQS_BYTES;     // per stage: nlse2[128], delta[128]
-    static constexpr uint32_t OFF_MASK = OFF_ROWV + QS * 1024;    // [KVB][RC][128] float
-    static constexpr uint32_t OFF_BARS = OFF_MASK + KVB * RC * 512;
-    static constexpr uint32_t NUM_BARS = 2 * KVB + 2 * QS + 2 + 6 + 1;
+    // one stage: Q, dO [, K, V] tiles, then -LSE*log2e[128], delta[128] [, mask*log2e[128]]
+    static constexpr uint32_t ST_Q = 0, ST_DO = ROWT;
+    static constexpr uint32_t ST_K = 2 * ROWT, ST_V = 3 * ROWT;            // streaming only
+    static constexpr uint32_t ST_TILES = KV_RESIDENT ? 2 : 4;
+    static constexpr uint32_t ST_ROWV = ST_TILES * ROWT, ST_MASK = ST_ROWV + 1024;
+    static constexpr uint32_t STAGE_TX = ST_TILES * ROWT + (KV_RESIDENT ? 1024 : 1536);
+    static constexpr uint32_t STAGE_STRIDE = ST_TILES * ROWT + 2048;
+    // resident K/V buffer: K[RC], V[RC], mask rows [RC][128]
+    static constexpr uint32_t KV_BYTES = KV_RESIDENT ? (2 * RC * ROWT + 1024) : 0;
+    static constexpr uint32_t KV_TX = 2 * ROWT + 512;                       // per row of the chunk
+    static constexpr uint32_t OFF_STAGE = 0;
+    static constexpr uint32_t OFF_KV = OFF_STAGE + QS * STAGE_STRIDE;
+    static constexpr uint32_t OFF_P = OFF_KV + KV_BYTES;
+    static constexpr uint32_t OFF_DS = OFF_P + SQ_BYTES;
+    // per warp: dQ slot [32 rows][HALF fp32], then dBias slot [32 rows][DBW fp32]
+    static constexpr int DBW = (DH == 32) ? 32 : 16;   // dBias columns per reduce
+    static constexpr uint32_t WQ_BYTES = 32 * HALF * 4;
+    static constexpr uint32_t WB_BYTES = 32 * DBW * 4;
+    static constexpr uint32_t WSTG_STRIDE = WQ_BYTES + WB_BYTES;
+    static constexpr uint32_t OFF_WSTG = OFF_DS + SQ_BYTES;
+    static constexpr uint32_t OFF_BARS = OFF_WSTG + 8 * WSTG_STRIDE;
+    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 6;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
-    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;  // + alignment slack
+    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
     static constexpr uint32_t TMEM_DP = 128;
     static constexpr uint32_t TMEM_DQ = 256;
-    static constexpr uint32_t TMEM_DKV = 256 + DH;                // + r*2*DH (dK), + DH (dV)
+    static constexpr uint32_t TMEM_DKV = 256 + DH;                          // + r*2*DH (dK), + DH (dV)
     static_assert(TMEM_DKV + RC * 2 * DH <= BWD_TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+    static_assert(OFF_KV % 1024 == 0 && OFF_P % 1024 == 0 && WQ_BYTES % 1024 == 0, "tile alignment");
 };
 
 struct BwdParams {
@@ -80,6 +106,9 @@ struct BwdParams {
     const float* nlse2;   // [B*S][H][NTP]  -LSE*log2e, -inf in the padding
     const float* delta;   // [B*S][H][NTP]  0 in the padding
     const float* maskl2;  // [B*S][NTP]     mask*log2e, -inf in the padding
+    const __nv_bfloat16* bias;   // [B][H][N][N]
+    __nv_bfloat16* dk;    // [B*S][N][H][D]
+    __nv_bfloat16* dv;
     unsigned int* status;
 };
 
@@ -91,30 +120,26 @@ template <int DH>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-               const __grid_constant__ CUtensorMap tm_bias, const __grid_constant__ CUtensorMap tm_dk,
-               const __grid_constant__ CUtensorMap tm_dv, const __grid_constant__ CUtensorMap tm_dq,
-               const __grid_constant__ CUtensorMap tm_dbias, const BwdParams p) {
+               const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dbias,
+               const BwdParams p) {
     using C = BwdCfg<DH>;
     using RT = RowTile<DH>;
-    constexpr int RC = C::RC, QS = C::QS, KVB = C::KVB;
-    constexpr int HALF = DH / 2;
+    constexpr int RC = C::RC, QS = C::QS, HALF = C::HALF;
+    constexpr bool KVR = C::KV_RESIDENT;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BARS);
-    uint64_t* kv_full = bars;                  // [KVB]
-    uint64_t* kv_empty = kv_full + KVB;        // [KVB]
-    uint64_t* qd_full = kv_empty + KVB;        // [QS]
-    uint64_t* qd_empty = qd_full + QS;         // [QS]
-    uint64_t* bias_full = qd_empty + QS;
-    uint64_t* bias_empty = bias_full + 1;
-    uint64_t* sdp_full = bias_empty + 1;
+    uint64_t* st_full = bars;                  // [QS]
+    uint64_t* st_empty = st_full + QS;         // [QS]
+    uint64_t* kv_full = st_empty + QS;         // resident K/V only
+    uint64_t* kv_empty = kv_full + 1;
+    uint64_t* sdp_full = kv_empty + 1;
     uint64_t* sdp_free = sdp_full + 1;
     uint64_t* pds_ready = sdp_free + 1;
     uint64_t* dq_full = pds_ready + 1;
     uint64_t* dq_free = dq_full + 1;
     uint64_t* dkv_free = dq_free + 1;
-    uint64_t* grp_bar = dkv_free + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -126,17 +151,15 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < KVB; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 9); }
-        for (int i = 0; i < QS; ++i) { mbar_init(&qd_full[i], 1); mbar_init(&qd_empty[i], 9); }
-        mbar_init(bias_full, 1);
-        mbar_init(bias_empty, 8);
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 9); }
+        mbar_init(kv_full, 1);
+        mbar_init(kv_empty, 9);
         mbar_init(sdp_full, 1);
         mbar_init(sdp_free, 8);
         mbar_init(pds_ready, 8);
         mbar_init(dq_full, 1);
         mbar_init(dq_free, 8);
         mbar_init(dkv_free, 8);
-        mbar_init(grp_bar, BWD_GROUP_THREADS);
         fence_mbar_init();
         fence_async_smem();
     }
@@ -146,13 +169,13 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     if (warp == 8 && lane == 0) {
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
-        prefetch_tmap(&tm_bias); prefetch_tmap(&tm_dk); prefetch_tmap(&tm_dv); prefetch_tmap(&tm_dq);
-        prefetch_tmap(&tm_dbias);
+        prefetch_tmap(&tm_dq); prefetch_tmap(&tm_dbias);
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    EVO_TS(t_kernel);
 
     const int first = blockIdx.x;
     const int stride = gridDim.x;
@@ -174,346 +197,385 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         return x;
     };
 
-    if (warp == 8) {
-        // ------------------------------ producer ------------------------------
-        if (lane == 0) {
+    if (warp >= 8) {
+        reg_dec<BWD_REGS_OTHER>();
+        if (warp == 8 && lane == 0) {
+            // ------------------------------ producer ------------------------------
             bool ok = true;
-            int gs = 0, gb = 0;
-            for (int it = 0; it < n_items && ok; ++it) {
-                const BwdItem x = decode(it);
-                const int kb = it % KVB;
-                if (it >= KVB) ok = mbar_wait(&kv_empty[kb], ((it / KVB) - 1) & 1, wc, 0x40);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&kv_full[kb], x.nr * (2 * C::ROWT + 512));
-                for (int r = 0; r < x.nr; ++r) {
-                    const int t = kb * RC + r;
-                    tma_load_4d(smem + C::OFF_K + t * C::ROWT, &tm_k, &kv_full[kb], 0, x.h, x.j * TILE, x.bs0 + r);
-                    tma_load_4d(smem + C::OFF_V + t * C::ROWT, &tm_v, &kv_full[kb], 0, x.h, x.j * TILE, x.bs0 + r);
-                    bulk_load(smem + C::OFF_MASK + t * 512,
-                              p.maskl2 + static_cast<size_t>(x.bs0 + r) * p.NTP + x.j * TILE, 512, &kv_full[kb]);
-                }
-                const int nsteps = NT * x.nr;
-                for (int n = 0; n < nsteps && ok; ++n, ++gs) {
-                    const int i = n / x.nr, r = n - i * x.nr;
-                    const int st = gs % QS;
-                    if (r == 0) {
-                        if (gb > 0) ok = mbar_wait(bias_empty, (gb - 1) & 1, wc, 0x41);
-                        if (!ok) break;
-                        mbar_arrive_expect_tx(bias_full, SQ_BYTES);
-                        tma_load_4d(smem + C::OFF_BIAS, &tm_bias, bias_full, x.j * TILE, i * TILE, x.h, x.b);
-                        tma_load_4d(smem + C::OFF_BIAS + SQ_SUB_BYTES, &tm_bias, bias_full, x.j * TILE + 64,
-                                    i * TILE, x.h, x.b);
-                        ++gb;
-                    }
-                    if (gs >= QS) ok = mbar_wait(&qd_empty[st], ((gs / QS) - 1) & 1, wc, 0x42);
-                    if (!ok) break;
-                    const int bs = x.bs0 + r;
-                    mbar_arrive_expect_tx(&qd_full[st], 2 * C::ROWT + 1024);
-                    tma_load_4d(smem + C::OFF_Q + st * C::ROWT, &tm_q, &qd_full[st], 0, x.h, i * TILE, bs);
-                    tma_load_4d(smem + C::OFF_DO + st * C::ROWT, &tm_do, &qd_full[st], 0, x.h, i * TILE, bs);
-                    const size_t ro = (static_cast<size_t>(bs) * p.H + x.h) * p.NTP + i * TILE;
-                    bulk_load(smem + C::OFF_ROWV + st * 1024, p.nlse2 + ro, 512, &qd_full[st]);
-                    bulk_load(smem + C::OFF_ROWV + st * 1024 + 512, p.delta + ro, 512, &qd_full[st]);
-                }
-            }
-            // Drain: the most recent loads have landed before the CTA exits.
-            for (int k = (gs > QS ? gs - QS : 0); k < gs; ++k)
-                (void)mbar_wait(&qd_full[k % QS], (k / QS) & 1, wc, 0x43);
-            if (gb > 0) (void)mbar_wait(bias_full, (gb - 1) & 1, wc, 0x44);
-            for (int it = (n_items > KVB ? n_items - KVB : 0); it < n_items; ++it)
-                (void)mbar_wait(&kv_full[it % KVB], (it / KVB) & 1, wc, 0x45);
-        }
-    } else if (warp == 9) {
-        // ------------------------------ mma issuer ------------------------------
-        if (lane == 0) {
-            constexpr uint32_t IDESC_SDP = make_idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t IDESC_DKV = make_idesc_bf16(128, DH, 1, 1);
-            constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, DH, 0, 1);
-            const uint32_t aK = smem_u32(smem + C::OFF_K), aV = smem_u32(smem + C::OFF_V);
-            const uint32_t aQ = smem_u32(smem + C::OFF_Q), aDO = smem_u32(smem + C::OFF_DO);
-            const uint32_t aP = smem_u32(smem + C::OFF_P), aDS = smem_u32(smem + C::OFF_DS);
-            bool ok = true;
-
-            // S and dP of step (it, n), global step gs
-            auto issue_sdp = [&](int it, const BwdItem& x, int n, int gs) -> bool {
-                const int kb = it % KVB, st = gs % QS;
-                const int i = n / x.nr, r = n - i * x.nr;
-                (void)i;
-                if (n == 0 && !mbar_wait(&kv_full[kb], (it / KVB) & 1, wc, 0x50)) return false;
-                if (!mbar_wait(&qd_full[st], (gs / QS) & 1, wc, 0x51)) return false;
-                if (gs > 0 && !mbar_wait(sdp_free, (gs - 1) & 1, wc, 0x52)) return false;
-                tc_fence_after();
-                const uint32_t k_t = aK + (kb * RC + r) * C::ROWT, v_t = aV + (kb * RC + r) * C::ROWT;
-#pragma unroll
-                for (int kk = 0; kk < RT::KBLOCKS; ++kk)
-                    umma_ss(tmem + C::TMEM_S, RT::kmajor(aQ + st * C::ROWT, kk), RT::kmajor(k_t, kk),
-                            IDESC_SDP, kk > 0);
-#pragma unroll
-                for (int kk = 0; kk < RT::KBLOCKS; ++kk)
-                    umma_ss(tmem + C::TMEM_DP, RT::kmajor(aDO + st * C::ROWT, kk), RT::kmajor(v_t, kk),
-                            IDESC_SDP, kk > 0);
-                umma_commit(sdp_full);
-                return true;
-            };
-            // dV, dK, dQ of step (it, n)
-            auto issue_tail = [&](int it, const BwdItem& x, int n, int gs) -> bool {
-                const int kb = it % KVB, st = gs % QS;
-                const int i = n / x.nr, r = n - i * x.nr;
-                if (!mbar_wait(pds_ready, gs & 1, wc, 0x53)) return false;
-                if (gs > 0 && !mbar_wait(dq_free, (gs - 1) & 1, wc, 0x54)) return false;
-                if (n == 0 && it > 0 && !mbar_wait(dkv_free, (it - 1) & 1, wc, 0x55)) return false;
-                tc_fence_after();
-                const uint32_t k_t = aK + (kb * RC + r) * C::ROWT;
-                const uint32_t q_t = aQ + st * C::ROWT, do_t = aDO + st * C::ROWT;
-                const uint32_t t_dk = tmem + C::TMEM_DKV + r * 2 * DH, t_dv = t_dk + DH;
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    umma_ss(t_dv, sq_mnmajor(aP, kk), RT::mnmajor(do_t, kk), IDESC_DKV, (i > 0 || kk > 0));
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    umma_ss(t_dk, sq_mnmajor(aDS, kk), RT::mnmajor(q_t, kk), IDESC_DKV, (i > 0 || kk > 0));
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    umma_ss(tmem + C::TMEM_DQ, sq_kmajor(aDS, kk), RT::mnmajor(k_t, kk), IDESC_DQ, kk > 0);
-                umma_commit(dq_full);
-                umma_commit(&qd_empty[st]);
-                if (n == NT * x.nr - 1) umma_commit(&kv_empty[kb]);
-                return true;
-            };
-
             int gs = 0;
             for (int it = 0; it < n_items && ok; ++it) {
                 const BwdItem x = decode(it);
                 const int nsteps = NT * x.nr;
-                if (QS >= 2) {
-                    // look one step ahead inside the item: S/dP of step n+1 are
-                    // queued before dV/dK/dQ of step n
-                    ok = issue_sdp(it, x, 0, gs);
-                    for (int n = 0; n < nsteps && ok; ++n, ++gs) {
-                        if (n + 1 < nsteps) ok = issue_sdp(it, x, n + 1, gs + 1);
-                        if (ok) ok = issue_tail(it, x, n, gs);
+                if (KVR) {
+                    if (it > 0) ok = mbar_wait(kv_empty, (it - 1) & 1, wc, 0x40);
+                    if (!ok) break;
+                    uint8_t* kvb = smem + C::OFF_KV;
+                    mbar_arrive_expect_tx(kv_full, x.nr * C::KV_TX);
+                    for (int r = 0; r < x.nr; ++r) {
+                        tma_load_4d(kvb + r * C::ROWT, &tm_k, kv_full, 0, x.h, x.j * TILE, x.bs0 + r);
+                        tma_load_4d(kvb + (RC + r) * C::ROWT, &tm_v, kv_full, 0, x.h, x.j * TILE, x.bs0 + r);
+                        bulk_load(kvb + 2 * RC * C::ROWT + r * 512,
+                                  p.maskl2 + static_cast<size_t>(x.bs0 + r) * p.NTP + x.j * TILE, 512, kv_full);
                     }
+                }
+                for (int n = 0; n < nsteps && ok; ++n, ++gs) {
+                    const int i = n / x.nr, r = n - i * x.nr;
+                    const int st = gs % QS;
+                    if (gs >= QS) ok = mbar_wait(&st_empty[st], ((gs / QS) - 1) & 1, wc, 0x42);
+                    if (!ok) break;
+                    const int bs = x.bs0 + r;
+                    uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
+                    mbar_arrive_expect_tx(&st_full[st], C::STAGE_TX);
+                    tma_load_4d(sb + C::ST_Q, &tm_q, &st_full[st], 0, x.h, i * TILE, bs);
+                    tma_load_4d(sb + C::ST_DO, &tm_do, &st_full[st], 0, x.h, i * TILE, bs);
+                    if (!KVR) {
+                        tma_load_4d(sb + C::ST_K, &tm_k, &st_full[st], 0, x.h, x.j * TILE, bs);
+                        tma_load_4d(sb + C::ST_V, &tm_v, &st_full[st], 0, x.h, x.j * TILE, bs);
+                        bulk_load(sb + C::ST_MASK, p.maskl2 + static_cast<size_t>(bs) * p.NTP + x.j * TILE, 512,
+                                  &st_full[st]);
+                    }
+                    const size_t ro = (static_cast<size_t>(bs) * p.H + x.h) * p.NTP + i * TILE;
+                    bulk_load(sb + C::ST_ROWV, p.nlse2 + ro, 512, &st_full[st]);
+                    bulk_load(sb + C::ST_ROWV + 512, p.delta + ro, 512, &st_full[st]);
+                }
+            }
+            // Drain: the most recent loads have landed before the CTA exits.
+            for (int k = (gs > QS ? gs - QS : 0); k < gs; ++k)
+                (void)mbar_wait(&st_full[k % QS], (k / QS) & 1, wc, 0x43);
+            if (KVR && n_items > 0) (void)mbar_wait(kv_full, (n_items - 1) & 1, wc, 0x45);
+        } else if (warp == 9 && lane == 0) {
+            // ------------------------------ mma issuer ------------------------------
+            constexpr uint32_t IDESC_SDP = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t IDESC_DKV = make_idesc_bf16(128, DH, 1, 1);
+            constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, DH, 0, 1);
+            const uint32_t aSt = smem_u32(smem + C::OFF_STAGE), aKV = smem_u32(smem + C::OFF_KV);
+            const uint32_t aP = smem_u32(smem + C::OFF_P), aDS = smem_u32(smem + C::OFF_DS);
+
+            struct Cursor {
+                int it, n, gs, nsteps;
+                BwdItem x;
+            };
+            auto cur_start = [&](Cursor& c) {
+                c.it = 0; c.n = 0; c.gs = 0; c.nsteps = 1;
+                if (n_items > 0) { c.x = decode(0); c.nsteps = NT * c.x.nr; }
+            };
+            auto cur_next = [&](Cursor& c) {
+                ++c.gs;
+                if (++c.n == c.nsteps) {
+                    c.n = 0;
+                    if (++c.it < n_items) { c.x = decode(c.it); c.nsteps = NT * c.x.nr; }
+                }
+            };
+            auto k_tile = [&](const Cursor& c, int r) -> uint32_t {
+                return KVR ? aKV + r * C::ROWT : aSt + (c.gs % QS) * C::STAGE_STRIDE + C::ST_K;
+            };
+            auto v_tile = [&](const Cursor& c, int r) -> uint32_t {
+                return KVR ? aKV + (RC + r) * C::ROWT : aSt + (c.gs % QS) * C::STAGE_STRIDE + C::ST_V;
+            };
+            // S and dP of the step under the cursor, if everything they need is there
+            auto try_sdp = [&](const Cursor& c) -> bool {
+                const int st = c.gs % QS;
+                if (!mbar_test(&st_full[st], (c.gs / QS) & 1)) return false;
+                if (KVR && c.n == 0 && !mbar_test(kv_full, c.it & 1)) return false;
+                if (c.gs > 0 && !mbar_test(sdp_free, (c.gs - 1) & 1)) return false;
+                tc_fence_after();
+                const int r = c.n % c.x.nr;
+                const uint32_t sb = aSt + st * C::STAGE_STRIDE;
+                const uint32_t kt = k_tile(c, r), vt = v_tile(c, r);
+#pragma unroll
+                for (int kk = 0; kk < RT::KBLOCKS; ++kk)
+                    umma_ss(tmem + C::TMEM_S, RT::kmajor(sb + C::ST_Q, kk), RT::kmajor(kt, kk), IDESC_SDP, kk > 0);
+#pragma unroll
+                for (int kk = 0; kk < RT::KBLOCKS; ++kk)
+                    umma_ss(tmem + C::TMEM_DP, RT::kmajor(sb + C::ST_DO, kk), RT::kmajor(vt, kk), IDESC_SDP, kk > 0);
+                umma_commit(sdp_full);
+                return true;
+            };
+            // dV, dK, dQ of the step under the cursor, if P/dS are out and the accumulators are free
+            auto try_tail = [&](const Cursor& c) -> bool {
+                const int st = c.gs % QS;
+                const int i = c.n / c.x.nr, r = c.n - i * c.x.nr;
+                if (!mbar_test(pds_ready, c.gs & 1)) return false;
+                if (c.gs > 0 && !mbar_test(dq_free, (c.gs - 1) & 1)) return false;
+                if (c.n == 0 && c.it > 0 && !mbar_test(dkv_free, (c.it - 1) & 1)) return false;
+                tc_fence_after();
+                const uint32_t sb = aSt + st * C::STAGE_STRIDE;
+                const uint32_t kt = k_tile(c, r);
+                const uint32_t t_dk = tmem + C::TMEM_DKV + r * 2 * DH, t_dv = t_dk + DH;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_ss(t_dv, sq_mnmajor(aP, kk), RT::mnmajor(sb + C::ST_DO, kk), IDESC_DKV, (i > 0 || kk > 0));
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_ss(t_dk, sq_mnmajor(aDS, kk), RT::mnmajor(sb + C::ST_Q, kk), IDESC_DKV, (i > 0 || kk > 0));
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_ss(tmem + C::TMEM_DQ, sq_kmajor(aDS, kk), RT::mnmajor(kt, kk), IDESC_DQ, kk > 0);
+                umma_commit(dq_full);
+                umma_commit(&st_empty[st]);
+                if (KVR && c.n == c.nsteps - 1) umma_commit(kv_empty);
+                return true;
+            };
+
+            Cursor a, b;          // a: next S/dP to issue, b: next dV/dK/dQ to issue
+            cur_start(a);
+            cur_start(b);
+            uint32_t idle = 0;
+            uint64_t idle_t0 = 0;
+            while (b.it < n_items) {
+                bool progress = false;
+                // S/dP run at most one step ahead (they share one accumulator pair)
+                if (a.it < n_items && a.gs <= b.gs + 1 && try_sdp(a)) {
+                    cur_next(a);
+                    progress = true;
+                }
+                if (b.gs < a.gs && try_tail(b)) {
+                    cur_next(b);
+                    progress = true;
+                }
+                if (progress) {
+                    idle = 0;
                 } else {
-                    for (int n = 0; n < nsteps && ok; ++n, ++gs) {
-                        ok = issue_sdp(it, x, n, gs);
-                        if (ok) ok = issue_tail(it, x, n, gs);
+                    __nanosleep(20);
+                    if ((++idle & 255u) == 0u) {
+                        if (*abort_flag) break;
+                        const uint64_t now = global_ns();
+                        if (idle == 256u) idle_t0 = now;
+                        if (now - idle_t0 > EVO_WAIT_NS) {
+                            report(p.status, ST_WAIT_TIMEOUT, 0x5f);
+                            *abort_flag = 1u;
+                            break;
+                        }
                     }
                 }
             }
         }
     } else {
+        reg_inc<BWD_REGS_COMPUTE>();
         // ------------------------------ compute groups ------------------------------
         const int wg = warp >> 2;            // kv columns 64*wg .. 64*wg+63 of the tile
         const int row = tid & 127;           // q row within the tile == TMEM lane
-        const int t256 = tid;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        const int wrow0 = (warp & 3) * 32;   // first tile row of this warp
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(wrow0) << 16);
         uint8_t* sP = smem + C::OFF_P;
         uint8_t* sDS = smem + C::OFF_DS;
-        uint8_t* sDQS = smem + C::OFF_DQS;
+        uint8_t* wq = smem + C::OFF_WSTG + warp * C::WSTG_STRIDE;   // this warp's dQ slot
+        uint8_t* wb = wq + C::WQ_BYTES;                              // this warp's dBias slot
         bool ok = true;
-        int gs = 0, gb = 0;
-        uint32_t grp_phase = 0;
-        auto group_sync = [&]() -> bool {
-            mbar_arrive(grp_bar);
-            const bool r = mbar_wait(grp_bar, grp_phase, wc, 0x60);
-            grp_phase ^= 1u;
-            return warp_all(r);
+        int gs = 0;
+
+        // This thread's 64 pair-bias values (row `row` of q tile i, columns of kv tile x.j
+        // owned by this group), straight from global memory; zeros outside the matrix.
+        auto load_bias = [&](uint32_t (&pk)[32], const BwdItem& x, int i) {
+            const int q = i * TILE + row;
+            const int c0 = x.j * TILE + wg * 64;
+            const __nv_bfloat16* src = p.bias + ((static_cast<size_t>(x.b) * p.H + x.h) * p.N + q) * p.N + c0;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (q < p.N && c0 + c8 * 8 + 8 <= p.N) v = __ldg(reinterpret_cast<const uint4*>(src + c8 * 8));
+                pk[c8 * 4 + 0] = v.x; pk[c8 * 4 + 1] = v.y; pk[c8 * 4 + 2] = v.z; pk[c8 * 4 + 3] = v.w;
+            }
         };
 
         float acc[64];                       // dBias partial sums of this thread's 64 columns
         uint32_t bias_pk[32];                // this thread's 64 bias values (bf16 pairs)
 
-        // Finishes step `pgs` (tile row pi of item px, chunk row pr): drains dQ into
-        // the fp32 accumulator and, after the last row of the chunk, flushes dBias.
-        auto finish_step = [&](const BwdItem& px, int pi, int pr, int pgs) -> bool {
-            if (!warp_all(mbar_wait(dq_full, pgs & 1, wc, 0x61))) return false;
-            tc_fence_after();
-            float dq[HALF];
-            tmem_ld_f32<HALF>(lane_base + C::TMEM_DQ + wg * HALF, dq);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(dq_free);
-            const bool flush = (pr == px.nr - 1);
-            // staging buffers are free once every earlier bulk reduce has read them
-            if (t256 == 0) tma_wait_group_read<0>();
-            if (!group_sync()) return false;
+        // Work left over from earlier steps, done after this step's P/dS are out:
+        //   drain  dQ of step (px, pi, pr) from tensor memory -> fp32 reductions
+        //   flush  dBias sums of (fx, fi) -> fp32 reductions
+        //   dkv    dK/dV of item kx -> bf16 stores
+        auto post_step = [&](bool drain, const BwdItem& px, int pi, int pr, bool flush, const BwdItem& fx,
+                             int fi, bool dkv, const BwdItem& kx) {
+            EVO_TS(t_post);
+            if (drain) {
+                float dqv[HALF];
+                tc_fence_after();
+                tmem_ld_f32<HALF>(lane_base + C::TMEM_DQ + wg * HALF, dqv);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dq_free);
+                if (!(EVO_EXP & 1) && pi * TILE + wrow0 < p.N) {     // warp-uniform
+                    // the slot is free once this lane-0's earlier bulk operations have read it
+                    if (lane == 0) tma_wait_group_read<0>();
+                    __syncwarp();
 #pragma unroll
-            for (int cc = 0; cc < HALF / 4; ++cc) {
-                const int gc = wg * (HALF / 4) + cc;          // 16-byte chunk within the fp32 row
-                const float4 v = make_float4(dq[cc * 4 + 0] * p.scale, dq[cc * 4 + 1] * p.scale,
-                                             dq[cc * 4 + 2] * p.scale, dq[cc * 4 + 3] * p.scale);
-                *reinterpret_cast<float4*>(sDQS + (gc >> 3) * 16384 + row * 128 + (((gc & 7) ^ (row & 7)) << 4)) = v;
-            }
-            if (flush) {
-                // dBias staging over the (idle) P and dS tiles: four [128][32] fp32 boxes
-#pragma unroll
-                for (int cc = 0; cc < 16; ++cc) {
-                    const int box = wg * 2 + (cc >> 3);
-                    const float4 v = make_float4(acc[cc * 4 + 0], acc[cc * 4 + 1], acc[cc * 4 + 2], acc[cc * 4 + 3]);
-                    *reinterpret_cast<float4*>(sP + box * 16384 + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = v;
+                    for (int cc = 0; cc < HALF / 4; ++cc)
+                        *reinterpret_cast<float4*>(wq + swz_off<HALF * 4>(lane, cc)) =
+                            make_float4(dqv[cc * 4 + 0] * p.scale, dqv[cc * 4 + 1] * p.scale,
+                                        dqv[cc * 4 + 2] * p.scale, dqv[cc * 4 + 3] * p.scale);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_reduce_add_4d(&tm_dq, wq, wg * HALF, px.h, pi * TILE + wrow0, px.bs0 + pr);
+                        tma_commit_group();
+                    }
                 }
             }
-            fence_async_smem();
-            if (!group_sync()) return false;
-            if (t256 == 0) {
+            if (flush && !(EVO_EXP & 2)) {
+                const int q0 = fi * TILE + wrow0;
 #pragma unroll
-                for (int bx = 0; bx < DH / 32; ++bx)
-                    tma_reduce_add_4d(&tm_dq, sDQS + bx * 16384, bx * 32, px.h, pi * TILE, px.bs0 + pr);
-                if (flush) {
-                    for (int bx = 0; bx < 4; ++bx)
-                        if (px.j * TILE + bx * 32 < p.N)
-                            tma_reduce_add_4d(&tm_dbias, sP + bx * 16384, px.j * TILE + bx * 32, pi * TILE, px.h, px.b);
+                for (int rd = 0; rd < 64 / C::DBW; ++rd) {
+                    const int col = fx.j * TILE + wg * 64 + rd * C::DBW;
+                    if (q0 >= p.N || col >= p.N) break;            // warp-uniform
+                    if (lane == 0) tma_wait_group_read<0>();
+                    __syncwarp();
+#pragma unroll
+                    for (int cc = 0; cc < C::DBW / 4; ++cc)
+                        *reinterpret_cast<float4*>(wb + swz_off<C::DBW * 4>(lane, cc)) =
+                            make_float4(acc[rd * C::DBW + cc * 4 + 0], acc[rd * C::DBW + cc * 4 + 1],
+                                        acc[rd * C::DBW + cc * 4 + 2], acc[rd * C::DBW + cc * 4 + 3]);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_reduce_add_4d(&tm_dbias, wb, col, q0, fx.h, fx.b);
+                        tma_commit_group();
+                    }
                 }
-                tma_commit_group();
-                if (flush) tma_wait_group_read<0>();
             }
-            if (flush) {
-                // P / dS tiles are rewritten next: wait until the reduce has read them
-                if (!group_sync()) return false;
+            if (dkv) {
+                tc_fence_after();
+                const int kvrow = kx.j * TILE + row;
+                for (int t = 0; t < 2 * kx.nr; ++t) {      // 2*r: dK of row r, 2*r+1: dV
+                    float v[HALF];
+                    tmem_ld_f32<HALF>(lane_base + C::TMEM_DKV + (t >> 1) * 2 * DH + (t & 1) * DH + wg * HALF, v);
+                    const float sc = (t & 1) ? 1.0f : p.scale;
+                    if (kvrow < p.N && !(EVO_EXP & 4)) {
+                        __nv_bfloat16* out = ((t & 1) ? p.dv : p.dk) +
+                            ((static_cast<size_t>(kx.bs0 + (t >> 1)) * p.N + kvrow) * p.H + kx.h) * DH + wg * HALF;
+#pragma unroll
+                        for (int c8 = 0; c8 < HALF / 8; ++c8) {
+                            uint4 u;
+                            u.x = pack_bf16(v[c8 * 8 + 0] * sc, v[c8 * 8 + 1] * sc);
+                            u.y = pack_bf16(v[c8 * 8 + 2] * sc, v[c8 * 8 + 3] * sc);
+                            u.z = pack_bf16(v[c8 * 8 + 4] * sc, v[c8 * 8 + 5] * sc);
+                            u.w = pack_bf16(v[c8 * 8 + 6] * sc, v[c8 * 8 + 7] * sc);
+                            *reinterpret_cast<uint4*>(out + c8 * 8) = u;
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dkv_free);
             }
-            return true;
+            EVO_TE(t_post, p.status, 0x71);
         };
+
+        bool have_prev = false, prev_item_end = false;
+        BwdItem prev_x{};                     // item of the previous step
+        int prev_i = 0, prev_r = 0;
+        if (n_items > 0) load_bias(bias_pk, decode(0), 0);
 
         for (int it = 0; it < n_items && ok; ++it) {
             const BwdItem x = decode(it);
-            const int kb = it % KVB;
             const int nsteps = NT * x.nr;
-            ok = warp_all(mbar_wait(&kv_full[kb], (it / KVB) & 1, wc, 0x62));   // mask rows
-            if (!ok) break;
+            if (KVR) {
+                ok = warp_all(mbar_wait(kv_full, it & 1, wc, 0x62));     // mask rows of this item
+                if (!ok) break;
+            }
             for (int n = 0; n < nsteps && ok; ++n, ++gs) {
                 const int i = n / x.nr, r = n - i * x.nr;
                 const int st = gs % QS;
+                const uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
                 ok = warp_all(mbar_wait(sdp_full, gs & 1, wc, 0x63));
                 if (!ok) break;
-                if (n > 0) {
-                    const int pn = n - 1, pi = pn / x.nr, pr = pn - pi * x.nr;
-                    ok = finish_step(x, pi, pr, gs - 1);
-                    if (!ok) break;
-                }
+                EVO_TS(t_cmp);
                 if (r == 0) {
-                    ok = warp_all(mbar_wait(bias_full, gb & 1, wc, 0x64));
-                    if (!ok) break;
-                    const uint8_t* sb = smem + C::OFF_BIAS + wg * SQ_SUB_BYTES + row * 128;
-#pragma unroll
-                    for (int c8 = 0; c8 < 8; ++c8) {
-                        const uint4 bv = *reinterpret_cast<const uint4*>(sb + ((c8 ^ (row & 7)) << 4));
-                        bias_pk[c8 * 4 + 0] = bv.x; bias_pk[c8 * 4 + 1] = bv.y;
-                        bias_pk[c8 * 4 + 2] = bv.z; bias_pk[c8 * 4 + 3] = bv.w;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bias_empty);
-                    ++gb;
 #pragma unroll
                     for (int c = 0; c < 64; ++c) acc[c] = 0.f;
                 }
-                ok = warp_all(mbar_wait(&qd_full[st], (gs / QS) & 1, wc, 0x65));
+                ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x65));
                 if (!ok) break;
-                const float* rowv = reinterpret_cast<const float*>(smem + C::OFF_ROWV + st * 1024);
+                const float* rowv = reinterpret_cast<const float*>(sb + C::ST_ROWV);
                 const float nl = rowv[row];          // -LSE*log2e (-inf for padded rows)
                 const float dl = rowv[128 + row];    // delta (0 for padded rows)
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&qd_empty[st]);
-                const float* mrow = reinterpret_cast<const float*>(smem + C::OFF_MASK + (kb * RC + r) * 512) + 64 * wg;
+                const float* mrow = (KVR ? reinterpret_cast<const float*>(smem + C::OFF_KV + 2 * RC * C::ROWT) + r * 128
+                                         : reinterpret_cast<const float*>(sb + C::ST_MASK)) + 64 * wg;
 
+                uint32_t pkp[32], pkd[32];           // P and dS of this thread's 64 columns, bf16 pairs
                 tc_fence_after();
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    uint32_t sv[32], dv[32];
-                    tmem_ld32(lane_base + C::TMEM_S + 64 * wg + 32 * hf, sv);
-                    tmem_ld32(lane_base + C::TMEM_DP + 64 * wg + 32 * hf, dv);
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t sv[16], dv[16];
+                    tmem_ld16(lane_base + C::TMEM_S + 64 * wg + 16 * ch, sv);
+                    tmem_ld16(lane_base + C::TMEM_DP + 64 * wg + 16 * ch, dv);
                     tmem_wait_ld();
-                    if (hf == 1) {
+                    if (ch == 3) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(sdp_free);
                     }
 #pragma unroll
-                    for (int q4 = 0; q4 < 8; ++q4) {
-                        const float4 mv = *reinterpret_cast<const float4*>(mrow + 32 * hf + q4 * 4);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 mv = *reinterpret_cast<const float4*>(mrow + 16 * ch + q4 * 4);
                         const float mm[4] = {mv.x, mv.y, mv.z, mv.w};
+                        float pv[4], ds[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int c = q4 * 4 + e;                  // 0..31 within this half
-                            const uint32_t word = bias_pk[hf * 16 + (c >> 1)];
+                            const int c = q4 * 4 + e;                  // 0..15 within this chunk
+                            const uint32_t word = bias_pk[ch * 8 + (c >> 1)];
                             const float bval = (c & 1) ? bf16_hi(word) : bf16_lo(word);
+                            if (EVO_EXP & 8) {
+                                pv[e] = __uint_as_float(sv[c]);
+                                ds[e] = __uint_as_float(dv[c]) + bval + mm[e] + nl + dl;
+                                continue;
+                            }
                             const float xv = fmaf(__uint_as_float(sv[c]), p.c1, fmaf(bval, LOG2E, mm[e]));
-                            const float pv = ex2(xv + nl);
-                            const float ds = pv * (__uint_as_float(dv[c]) - dl);
-                            acc[hf * 32 + c] += ds;
-                            sv[c] = __float_as_uint(pv);
-                            dv[c] = __float_as_uint(ds);
+                            pv[e] = ex2(xv + nl);
+                            ds[e] = pv[e] * (__uint_as_float(dv[c]) - dl);
+                            acc[ch * 16 + c] += ds[e];
                         }
+                        pkp[ch * 8 + q4 * 2 + 0] = pack_bf16(pv[0], pv[1]);
+                        pkp[ch * 8 + q4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
+                        pkd[ch * 8 + q4 * 2 + 0] = pack_bf16(ds[0], ds[1]);
+                        pkd[ch * 8 + q4 * 2 + 1] = pack_bf16(ds[2], ds[3]);
                     }
+                }
+                if (r == x.nr - 1) {
+                    // bias of the next q tile (or of the next item's first one): the values of
+                    // this q tile are dead now; the loads land while the rest of the step runs
+                    if (n + 1 < nsteps) load_bias(bias_pk, x, i + 1);
+                    else if (it + 1 < n_items) load_bias(bias_pk, decode(it + 1), 0);
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&st_empty[st]);                          // rows (and mask) of this stage are read
+                    if (KVR && n == nsteps - 1) mbar_arrive(kv_empty);   // resident mask rows are read
+                }
+                EVO_TE(t_cmp, p.status, 0x70);
+
+                // the P / dS tiles are free once the previous step's dV/dK/dQ MMAs are done
+                if (have_prev) {
+                    ok = warp_all(mbar_wait(dq_full, (gs - 1) & 1, wc, 0x61));
+                    if (!ok) break;
+                }
 #pragma unroll
-                    for (int c8 = 0; c8 < 4; ++c8) {
-                        uint4 v, w;
-                        v.x = pack_bf16(__uint_as_float(sv[c8 * 8 + 0]), __uint_as_float(sv[c8 * 8 + 1]));
-                        v.y = pack_bf16(__uint_as_float(sv[c8 * 8 + 2]), __uint_as_float(sv[c8 * 8 + 3]));
-                        v.z = pack_bf16(__uint_as_float(sv[c8 * 8 + 4]), __uint_as_float(sv[c8 * 8 + 5]));
-                        v.w = pack_bf16(__uint_as_float(sv[c8 * 8 + 6]), __uint_as_float(sv[c8 * 8 + 7]));
-                        w.x = pack_bf16(__uint_as_float(dv[c8 * 8 + 0]), __uint_as_float(dv[c8 * 8 + 1]));
-                        w.y = pack_bf16(__uint_as_float(dv[c8 * 8 + 2]), __uint_as_float(dv[c8 * 8 + 3]));
-                        w.z = pack_bf16(__uint_as_float(dv[c8 * 8 + 4]), __uint_as_float(dv[c8 * 8 + 5]));
-                        w.w = pack_bf16(__uint_as_float(dv[c8 * 8 + 6]), __uint_as_float(dv[c8 * 8 + 7]));
-                        const uint32_t off = wg * SQ_SUB_BYTES + row * 128 + ((((hf * 4 + c8)) ^ (row & 7)) << 4);
-                        *reinterpret_cast<uint4*>(sP + off) = v;
-                        *reinterpret_cast<uint4*>(sDS + off) = w;
-                    }
+                for (int c8 = 0; c8 < 8; ++c8) {
+                    const uint32_t off = wg * SQ_SUB_BYTES + swz_off<128>(row, c8);
+                    *reinterpret_cast<uint4*>(sP + off) =
+                        make_uint4(pkp[c8 * 4 + 0], pkp[c8 * 4 + 1], pkp[c8 * 4 + 2], pkp[c8 * 4 + 3]);
+                    *reinterpret_cast<uint4*>(sDS + off) =
+                        make_uint4(pkd[c8 * 4 + 0], pkd[c8 * 4 + 1], pkd[c8 * 4 + 2], pkd[c8 * 4 + 3]);
                 }
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pds_ready);
-            }
-            if (!ok) break;
-            // last step of the item
-            {
-                const int pn = nsteps - 1, pi = pn / x.nr, pr = pn - pi * x.nr;
-                ok = finish_step(x, pi, pr, gs - 1);
-                if (!ok) break;
-            }
-            if (lane == 0) mbar_arrive(&kv_empty[kb]);     // mask rows no longer needed
 
-            // ---- dK / dV of every row of the chunk: tensor memory -> bf16 -> TMA store ----
-            // staging: row tiles over the (idle) P tile, tile index 2*r (dK), 2*r+1 (dV)
-            for (int r = 0; r < x.nr; ++r) {
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    float v[HALF];
-                    tmem_ld_f32<HALF>(lane_base + C::TMEM_DKV + r * 2 * DH + t * DH + wg * HALF, v);
-                    const float sc = (t == 0) ? p.scale : 1.0f;
-                    uint8_t* dst = sP + (2 * r + t) * C::ROWT + row * RT::ROW_BYTES;
-                    const int sw = (DH == 32) ? ((row >> 1) & 3) : (row & 7);
-#pragma unroll
-                    for (int c8 = 0; c8 < HALF / 8; ++c8) {
-                        uint4 u;
-                        u.x = pack_bf16(v[c8 * 8 + 0] * sc, v[c8 * 8 + 1] * sc);
-                        u.y = pack_bf16(v[c8 * 8 + 2] * sc, v[c8 * 8 + 3] * sc);
-                        u.z = pack_bf16(v[c8 * 8 + 4] * sc, v[c8 * 8 + 5] * sc);
-                        u.w = pack_bf16(v[c8 * 8 + 6] * sc, v[c8 * 8 + 7] * sc);
-                        const int chunk = wg * (HALF / 8) + c8;
-                        *reinterpret_cast<uint4*>(dst + ((chunk ^ sw) << 4)) = u;
-                    }
-                }
+                post_step(have_prev, prev_x, prev_i, prev_r, r == x.nr - 1, x, i, have_prev && prev_item_end, prev_x);
+                have_prev = true;
+                prev_x = x; prev_i = i; prev_r = r;
+                prev_item_end = (n == nsteps - 1);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(dkv_free);
-            fence_async_smem();
-            ok = group_sync();
-            if (!ok) break;
-            if (t256 == 0) {
-                for (int r = 0; r < x.nr; ++r) {
-                    tma_store_4d(&tm_dk, sP + (2 * r) * C::ROWT, 0, x.h, x.j * TILE, x.bs0 + r);
-                    tma_store_4d(&tm_dv, sP + (2 * r + 1) * C::ROWT, 0, x.h, x.j * TILE, x.bs0 + r);
-                }
-                tma_commit_group();
-                tma_wait_group_read<0>();
-            }
-            ok = group_sync();           // the P tile may be rewritten
         }
-        if (t256 == 0) tma_wait_group<0>();
+        if (ok && have_prev) {
+            // the very last step: its dQ, and the last item's dK/dV
+            ok = warp_all(mbar_wait(dq_full, (gs - 1) & 1, wc, 0x66));
+            if (ok) post_step(true, prev_x, prev_i, prev_r, false, prev_x, 0, true, prev_x);
+        }
+        if (lane == 0) tma_wait_group<0>();
     }
 
+    if (tid == 0) EVO_TE(t_kernel, p.status, 0x7f);
     tc_fence_before();
     __syncthreads();
     if (warp == 9) tmem_dealloc(tmem, BWD_TMEM_COLS);
@@ -522,12 +584,16 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // ---------------------------------------------------------------------------
 // prep: delta = rowsum(dO o O) (replaces evo_bwd_prep_ker, tk_evoattention.cu:352-416),
 // plus the pre-scaled, tile-padded LSE and mask rows the main kernel streams.
+// With o_resid (the bf16 rounding residual of O written by the forward), delta
+// uses O to about 16 bits instead of 8: the rounding of O otherwise puts an
+// error of order 2^-9 |dO||O| on every dS, which adds up over the S rows of dBias.
 // ---------------------------------------------------------------------------
 template <int DH>
-__global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                const float* __restrict__ lse, const __nv_bfloat16* __restrict__ mask,
-                                float* __restrict__ nlse2, float* __restrict__ delta,
-                                float* __restrict__ maskl2, int BS, int N, int H, int NTP) {
+__global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ o_resid,
+                                const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
+                                const __nv_bfloat16* __restrict__ mask, float* __restrict__ nlse2,
+                                float* __restrict__ delta, float* __restrict__ maskl2, int BS, int N, int H,
+                                int NTP) {
     const size_t rows = static_cast<size_t>(BS) * N * H;
     const size_t gstride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const size_t t0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -537,16 +603,22 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
         const int n = static_cast<int>(bn % N);
         const size_t bs = bn / N;
         const uint4* po = reinterpret_cast<const uint4*>(o + idx * DH);
+        const uint4* pr = o_resid ? reinterpret_cast<const uint4*>(o_resid + idx * DH) : nullptr;
         const uint4* pd = reinterpret_cast<const uint4*>(d_o + idx * DH);
         float s = 0.f;
 #pragma unroll
         for (int c = 0; c < DH / 8; ++c) {
             const uint4 a = po[c], b = pd[c];
             const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+            uint32_t rw[4] = {0u, 0u, 0u, 0u};
+            if (pr) {
+                const uint4 rr = pr[c];
+                rw[0] = rr.x; rw[1] = rr.y; rw[2] = rr.z; rw[3] = rr.w;
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                s = fmaf(bf16_lo(aw[e]), bf16_lo(bw[e]), s);
-                s = fmaf(bf16_hi(aw[e]), bf16_hi(bw[e]), s);
+                s = fmaf(bf16_lo(aw[e]) + bf16_lo(rw[e]), bf16_lo(bw[e]), s);
+                s = fmaf(bf16_hi(aw[e]) + bf16_hi(rw[e]), bf16_hi(bw[e]), s);
             }
         }
         const size_t ro = (bs * H + h) * NTP + n;
@@ -602,8 +674,8 @@ static BwdWorkspace bwd_workspace(const EvoDims* d) {
 
 template <int DH>
 static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
-                      const void* mask, const void* o, const float* lse, const void* d_o, void* dq,
-                      void* dk, void* dv, float* dbias, uint8_t* ws, float scale, cudaStream_t st) {
+                      const void* mask, const void* o, const void* o_resid, const float* lse, const void* d_o,
+                      void* dq, void* dk, void* dv, float* dbias, uint8_t* ws, float scale, cudaStream_t st) {
     using C = BwdCfg<DH>;
     const int BS = d->B * d->S;
     const int NT = (d->N + TILE - 1) / TILE;
@@ -613,17 +685,14 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     float* maskl2 = reinterpret_cast<float*>(ws + w.off_maskl2);
     float* dq_acc = reinterpret_cast<float*>(ws + w.off_dq);
 
-    CUtensorMap tq, tk, tv, tdo, tb, tdk, tdv, tdq, tdb;
+    CUtensorMap tq, tk, tv, tdo, tdq, tdb;
     int rc;
     if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
-    if ((rc = make_tmap_qkv(&tdk, dk, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_qkv(&tdv, dv, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_qkv_f32(&tdq, dq_acc, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_dbias(&tdb, dbias, d->B, d->H, d->N))) return rc;
+    if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, C::HALF, 32))) return rc;
+    if ((rc = make_tmap_dbias_box(&tdb, dbias, d->B, d->H, d->N, C::DBW, 32))) return rc;
 
     BwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
@@ -634,6 +703,8 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     p.scale = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH));
     p.c1 = p.scale * LOG2E;
     p.nlse2 = nlse2; p.delta = delta; p.maskl2 = maskl2;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
@@ -647,15 +718,18 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     if ((rc = cuda_err(cudaMemsetAsync(dbias, 0, db_bytes, st)))) return rc;
 
     bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse,
-        static_cast<const __nv_bfloat16*>(mask), nlse2, delta, maskl2, BS, d->N, d->H, p.NTP);
+        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
+        static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), nlse2, delta,
+        maskl2, BS, d->N, d->H, p.NTP);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 
     if ((rc = cuda_err(cudaFuncSetAttribute(evo_bwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(C::SMEM_BYTES)))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
-    evo_bwd_kernel<DH><<<grid, BWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tb, tdk, tdv, tdq, tdb, p);
+    prof_begin(1, st);
+    evo_bwd_kernel<DH><<<grid, BWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, tdb, p);
+    prof_end(1, st);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 
     cvt_dq_kernel<<<sms * 8, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), dq_bytes / 32);
@@ -670,9 +744,9 @@ extern "C" size_t evo_bwd_workspace_bytes(const EvoDims* dims) {
 }
 
 extern "C" int evo_bwd(const EvoDims* dims, const void* q, const void* k, const void* v,
-                       const void* pair_bias, const void* res_mask, const void* o, const float* lse,
-                       const void* d_o, void* dq, void* dk, void* dv, float* dbias, void* workspace,
-                       size_t workspace_bytes, float scale, void* stream) {
+                       const void* pair_bias, const void* res_mask, const void* o, const void* o_resid,
+                       const float* lse, const void* d_o, void* dq, void* dk, void* dv, float* dbias,
+                       void* workspace, size_t workspace_bytes, float scale, void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse || !d_o || !dq || !dk || !dv || !dbias ||
@@ -683,13 +757,16 @@ extern "C" int evo_bwd(const EvoDims* dims, const void* q, const void* k, const 
                           reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o) |
                           reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
                           reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(dbias) |
-                          reinterpret_cast<uintptr_t>(lse);
+                          reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(o_resid);
     if (all & 15u) return EVO_ERR_ALIGNMENT;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < evo::bwd_workspace(dims).total)
         return EVO_ERR_WORKSPACE;
+    if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     if (dims->D == 32)
-        return evo::launch_bwd<32>(dims, q, k, v, pair_bias, res_mask, o, lse, d_o, dq, dk, dv, dbias, ws, scale, st);
-    return evo::launch_bwd<64>(dims, q, k, v, pair_bias, res_mask, o, lse, d_o, dq, dk, dv, dbias, ws, scale, st);
+        return evo::launch_bwd<32>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
+                                   scale, st);
+    return evo::launch_bwd<64>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
+                               scale, st);
 }

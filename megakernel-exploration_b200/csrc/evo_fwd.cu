@@ -13,8 +13,9 @@
 //
 //   warp 8  (producer)  TMA: Q tile (double buffered), then per kv tile K, V and
 //                       the [128 x 128] bf16 pair-bias tile into a ring of stages
-//   warp 9  (mma)       tcgen05.mma: S = Q K^T into tensor memory; later, per
-//                       softmax group g, PV_g = P[:, 64g:64g+64] V[64g:64g+64, :]
+//   warp 9  (mma)       tcgen05.mma, issued in whatever order operands become
+//                       ready: S = Q K^T into tensor memory and, per softmax
+//                       group g, PV_g = P[:, 64g:64g+64] V[64g:64g+64, :]
 //   warps 0-3, 4-7      two softmax groups.  Group g owns kv columns 64g..64g+63
 //                       of every tile and runs its own online softmax over them
 //                       (thread = one q row): x = S*scale*log2e + bias*log2e +
@@ -26,11 +27,16 @@
 #include "evo_host.cuh"
 #include "evo_tiles.cuh"
 
+#ifndef EVO_EXP
+#define EVO_EXP 0
+#endif
+
 namespace evo {
 
-constexpr int FWD_THREADS = 320;
-constexpr int FWD_SOFTMAX_THREADS = 256;
+constexpr int FWD_THREADS = 384;           // 3 warpgroups: 2 softmax + (producer, mma, 2 idle warps)
 constexpr uint32_t FWD_TMEM_COLS = 256;
+constexpr int FWD_REGS_SOFTMAX = 224;
+constexpr int FWD_REGS_OTHER = 56;
 
 template <int DH>
 struct FwdCfg {
@@ -59,6 +65,7 @@ struct FwdParams {
     float c1;          // scale * log2(e)
     const __nv_bfloat16* mask;   // [B*S][N]
     float* lse;                  // [B*S][H][N]
+    __nv_bfloat16* o_resid;      // [B*S][N][H][D] or nullptr
     unsigned int* status;
 };
 
@@ -82,7 +89,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* s_free = s_full + 1;           // [1]
     uint64_t* p_ready = s_free + 1;          // [2]
     uint64_t* pv_full = p_ready + 2;         // [2]
-    uint64_t* grp_bar = pv_full + 2;         // [1] 256-thread rendezvous of the softmax groups
+    uint64_t* grp_bar = pv_full + 2;         // [1] rendezvous of the eight softmax warps
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* s_mask = reinterpret_cast<float*>(smem + C::OFF_MASK);
@@ -101,7 +108,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(s_full, 1);
         mbar_init(s_free, 8);
         for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
-        mbar_init(grp_bar, FWD_SOFTMAX_THREADS);
+        mbar_init(grp_bar, 8);
         fence_mbar_init();
         fence_async_smem();
     }
@@ -117,6 +124,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    EVO_TS(t_kernel);
 
     const int first = blockIdx.x;
     const int stride = gridDim.x;
@@ -131,9 +139,10 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bs = r / p.QT;
     };
 
-    if (warp == 8) {
-        // ------------------------------ producer ------------------------------
-        if (lane == 0) {
+    if (warp >= 8) {
+        reg_dec<FWD_REGS_OTHER>();
+        if (warp == 8 && lane == 0) {
+            // ------------------------------ producer ------------------------------
             bool ok = true;
             int g = 0;   // running kv-tile counter across items
             for (int it = 0; it < n_items && ok; ++it) {
@@ -163,52 +172,80 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 (void)mbar_wait(&kv_full[k % ST], (k / ST) & 1, wc, 0x12);
             for (int it = (n_items > 2 ? n_items - 2 : 0); it < n_items; ++it)
                 (void)mbar_wait(&q_full[it & 1], (it >> 1) & 1, wc, 0x13);
-        }
-    } else if (warp == 9) {
-        // ------------------------------ mma issuer ------------------------------
-        if (lane == 0) {
+        } else if (warp == 9 && lane == 0) {
+            // ------------------------------ mma issuer ------------------------------
+            // Issues whichever MMA has its operands ready: S of the next tile (needs
+            // its loads and the S accumulator read out) or PV_g of a tile whose P_g
+            // is in shared memory.  Nothing here blocks on one barrier while
+            // another piece of work could go.
             constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, DH, 0, 1);
             const uint32_t aQ = smem_u32(smem + C::OFF_Q), aK = smem_u32(smem + C::OFF_K);
             const uint32_t aV = smem_u32(smem + C::OFF_V), aP = smem_u32(smem + C::OFF_P);
             const int total_tiles = n_items * NT;
+            int s_next = 0;
+            int pv_next[2] = {0, 0};
+            uint32_t idle = 0;
+            uint64_t idle_t0 = 0;
             bool ok = true;
-            auto issue_s = [&](int g) -> bool {
-                const int it = g / NT, j = g - it * NT;
-                const int qb = it & 1, st = g % ST;
-                if (j == 0 && !mbar_wait(&q_full[qb], (it >> 1) & 1, wc, 0x20)) return false;
-                if (!mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x21)) return false;
-                if (g > 0 && !mbar_wait(s_free, (g - 1) & 1, wc, 0x22)) return false;
-                tc_fence_after();
+            while (ok && (pv_next[0] < total_tiles || pv_next[1] < total_tiles)) {
+                bool progress = false;
+                if (s_next < total_tiles) {
+                    const int g = s_next;
+                    const int it = g / NT, j = g - it * NT;
+                    const int qb = it & 1, st = g % ST;
+                    const bool rdy = (j != 0 || mbar_test(&q_full[qb], (it >> 1) & 1)) &&
+                                     mbar_test(&kv_full[st], (g / ST) & 1) &&
+                                     (g == 0 || mbar_test(s_free, (g - 1) & 1));
+                    if (rdy) {
+                        tc_fence_after();
 #pragma unroll
-                for (int kb = 0; kb < RT::KBLOCKS; ++kb)
-                    umma_ss(tmem + C::TMEM_S, RT::kmajor(aQ + qb * C::ROWT, kb),
-                            RT::kmajor(aK + st * C::ROWT, kb), IDESC_S, kb > 0);
-                umma_commit(s_full);
-                if (j == NT - 1) umma_commit(&q_empty[qb]);
-                return true;
-            };
-            if (total_tiles > 0) ok = issue_s(0);
-            for (int g = 0; g < total_tiles && ok; ++g) {
-                if (g + 1 < total_tiles) ok = issue_s(g + 1);
-                if (!ok) break;
-                const int st = g % ST;
-                for (int w = 0; w < 2 && ok; ++w) {
-                    ok = mbar_wait(&p_ready[w], g & 1, wc, 0x23);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const int kb = 4 * w + kk;
-                        umma_ss(tmem + C::TMEM_PV + w * DH, sq_kmajor(aP, kb),
-                                RT::mnmajor(aV + st * C::ROWT, kb), IDESC_PV, kk > 0);
+                        for (int kb = 0; kb < RT::KBLOCKS; ++kb)
+                            umma_ss(tmem + C::TMEM_S, RT::kmajor(aQ + qb * C::ROWT, kb),
+                                    RT::kmajor(aK + st * C::ROWT, kb), IDESC_S, kb > 0);
+                        umma_commit(s_full);
+                        if (j == NT - 1) umma_commit(&q_empty[qb]);
+                        ++s_next;
+                        progress = true;
                     }
-                    umma_commit(&pv_full[w]);
                 }
-                if (ok) umma_commit(&kv_empty[st]);
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int g = pv_next[w];
+                    if (g < s_next && mbar_test(&p_ready[w], g & 1)) {
+                        const int st = g % ST;
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const int kb = 4 * w + kk;
+                            umma_ss(tmem + C::TMEM_PV + w * DH, sq_kmajor(aP, kb),
+                                    RT::mnmajor(aV + st * C::ROWT, kb), IDESC_PV, kk > 0);
+                        }
+                        umma_commit(&pv_full[w]);
+                        ++pv_next[w];
+                        if (pv_next[w ^ 1] > g) umma_commit(&kv_empty[st]);   // both groups' PV of tile g issued
+                        progress = true;
+                    }
+                }
+                if (progress) {
+                    idle = 0;
+                } else if (EVO_EXP & 16) {
+                    __nanosleep(32);
+                    if ((++idle & 255u) == 0u && *abort_flag) { ok = false; break; }
+                } else if ((++idle & 255u) == 0u) {
+                    if (*abort_flag) { ok = false; break; }
+                    const uint64_t now = global_ns();
+                    if (idle == 256u) idle_t0 = now;
+                    if (now - idle_t0 > EVO_WAIT_NS) {
+                        report(p.status, ST_WAIT_TIMEOUT, 0x2f);
+                        *abort_flag = 1u;
+                        ok = false;
+                    }
+                }
             }
         }
     } else {
+        reg_inc<FWD_REGS_SOFTMAX>();
         // ------------------------------ softmax groups ------------------------------
         const int wg = warp >> 2;            // 0 or 1: kv columns 64*wg .. 64*wg+63 of each tile
         const int row = tid & 127;           // q row within the tile == TMEM lane
@@ -219,11 +256,13 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         int g = 0;
         uint32_t grp_phase = 0;
+        // rendezvous of both groups (bounded)
         auto group_sync = [&]() -> bool {
-            mbar_arrive(grp_bar);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(grp_bar);
             const bool r = mbar_wait(grp_bar, grp_phase, wc, 0x30);
             grp_phase ^= 1u;
-            return r;
+            return warp_all(r);
         };
 
         for (int it = 0; it < n_items && ok; ++it) {
@@ -232,13 +271,13 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             float* mk = s_mask + (it & 1) * NT * TILE;
             {
                 const __nv_bfloat16* src = p.mask + static_cast<size_t>(bs) * p.N;
-                for (int i = t256; i < NT * TILE; i += FWD_SOFTMAX_THREADS)
+                for (int i = t256; i < NT * TILE; i += 256)
                     mk[i] = (i < p.N) ? __bfloat162float(src[i]) * LOG2E : -INFINITY;
             }
             // The thread that issued the previous item's O store makes sure the
             // store has finished reading sO before anyone rewrites it.
             if (t256 == 0) tma_wait_group_read<0>();
-            ok = warp_all(group_sync());
+            ok = group_sync();
             if (!ok) break;
 
             float m = -INFINITY, l = 0.f;
@@ -250,6 +289,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int st = g % ST;
                 ok = warp_all(mbar_wait(s_full, g & 1, wc, 0x31));
                 if (!ok) break;
+                EVO_TS(t_tile);
                 tc_fence_after();
                 uint32_t sr[64];
                 {
@@ -265,12 +305,12 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
                 ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x32));
                 if (!ok) break;
-                const uint8_t* sb = smem + C::OFF_BIAS + st * SQ_BYTES + wg * SQ_SUB_BYTES + row * 128;
+                const uint8_t* sb = smem + C::OFF_BIAS + st * SQ_BYTES + wg * SQ_SUB_BYTES;
                 const float* mrow = mk + j * TILE + 64 * wg;
-                float tmax = -INFINITY;
+                float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: ILP
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
-                    const uint4 bv = *reinterpret_cast<const uint4*>(sb + ((c8 ^ (row & 7)) << 4));
+                    const uint4 bv = *reinterpret_cast<const uint4*>(sb + swz_off<128>(row, c8));
                     const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                     for (int q4 = 0; q4 < 2; ++q4) {
@@ -283,24 +323,25 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             const float bval = (e & 1) ? bf16_hi(word) : bf16_lo(word);
                             const float x = fmaf(__uint_as_float(sr[c]), p.c1, fmaf(bval, LOG2E, mm[e]));
                             sr[c] = __float_as_uint(x);
-                            tmax = fmaxf(tmax, x);
+                            tmx[e] = fmaxf(tmx[e], x);
                         }
                     }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&kv_empty[st]);
 
+                const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
                 const float m_new = fmaxf(m, tmax);
                 const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
                 const float alpha = ex2(m - m_safe);
-                float rs = 0.f;
+                float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const float pv = ex2(__uint_as_float(sr[c]) - m_safe);
-                    rs += pv;
+                    rs[c & 3] += pv;
                     sr[c] = __float_as_uint(pv);
                 }
-                l = l * alpha + rs;
+                l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
                 m = m_new;
 
                 if (j > 0) {
@@ -326,14 +367,16 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     v.y = pack_bf16(__uint_as_float(sr[c8 * 8 + 2]), __uint_as_float(sr[c8 * 8 + 3]));
                     v.z = pack_bf16(__uint_as_float(sr[c8 * 8 + 4]), __uint_as_float(sr[c8 * 8 + 5]));
                     v.w = pack_bf16(__uint_as_float(sr[c8 * 8 + 6]), __uint_as_float(sr[c8 * 8 + 7]));
-                    *reinterpret_cast<uint4*>(sP + wg * SQ_SUB_BYTES + row * 128 + ((c8 ^ (row & 7)) << 4)) = v;
+                    *reinterpret_cast<uint4*>(sP + wg * SQ_SUB_BYTES + swz_off<128>(row, c8)) = v;
                 }
                 fence_async_smem();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[wg]);
+                EVO_TE(t_tile, p.status, 0x78);
             }
             if (!ok) break;
+            EVO_TS(t_epi);
             // last tile's PV
             ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x34));
             if (!ok) break;
@@ -354,12 +397,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // (now idle) half of the P tile.
             constexpr int HALF = DH / 2;                  // floats per row handed over
             constexpr int XCH = HALF / 4;                 // 16-byte chunks per row
-            constexpr uint32_t XROW = HALF * 4;           // 64 or 128 bytes
             const int other = wg ^ 1;
-            auto xoff = [&](int r, int c) -> uint32_t {
-                const int sw = (XROW == 64) ? ((r >> 1) & 3) : (r & 7);
-                return r * XROW + ((c ^ sw) << 4);
-            };
             // keep[] = the half this group finalises, give[] = the half it hands over
             float keep[HALF], give[HALF];
 #pragma unroll
@@ -372,11 +410,11 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                 for (int c = 0; c < XCH; ++c) {
                     float4 v = make_float4(give[c * 4 + 0], give[c * 4 + 1], give[c * 4 + 2], give[c * 4 + 3]);
-                    *reinterpret_cast<float4*>(mine + xoff(row, c)) = v;
+                    *reinterpret_cast<float4*>(mine + swz_off<HALF * 4>(row, c)) = v;
                 }
                 s_ml[wg * 128 + row] = make_float2(m, l);
             }
-            ok = warp_all(group_sync());
+            ok = group_sync();
             if (!ok) break;
             {
                 const float2 ml_o = s_ml[other * 128 + row];
@@ -388,13 +426,15 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 float outv[HALF];
 #pragma unroll
                 for (int c = 0; c < XCH; ++c) {
-                    const float4 v = *reinterpret_cast<const float4*>(theirs + xoff(row, c));
+                    const float4 v = *reinterpret_cast<const float4*>(theirs + swz_off<HALF * 4>(row, c));
                     outv[c * 4 + 0] = (keep[c * 4 + 0] * f + v.x * fo) * inv;
                     outv[c * 4 + 1] = (keep[c * 4 + 1] * f + v.y * fo) * inv;
                     outv[c * 4 + 2] = (keep[c * 4 + 2] * f + v.z * fo) * inv;
                     outv[c * 4 + 3] = (keep[c * 4 + 3] * f + v.w * fo) * inv;
                 }
-                // bf16 row into the O staging tile (same swizzle as a row tile)
+                const int qrow = qt * TILE + row;
+                // bf16 row into the O staging tile (same swizzle as a row tile); the
+                // rounding residual goes straight to global memory
 #pragma unroll
                 for (int c8 = 0; c8 < HALF / 8; ++c8) {
                     uint4 v;
@@ -403,26 +443,35 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
                     v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
                     const int chunk = wg * (HALF / 8) + c8;   // 16-byte chunk within the row
-                    const int sw = (DH == 32) ? ((row >> 1) & 3) : (row & 7);
-                    *reinterpret_cast<uint4*>(sO + row * RT::ROW_BYTES + ((chunk ^ sw) << 4)) = v;
+                    *reinterpret_cast<uint4*>(sO + swz_off<RT::ROW_BYTES>(row, chunk)) = v;
+                    if (p.o_resid != nullptr && qrow < p.N) {
+                        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                        uint32_t rw[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]),
+                                              outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
+                        __nv_bfloat16* dst = p.o_resid +
+                            ((static_cast<size_t>(bs) * p.N + qrow) * p.H + h) * DH + wg * HALF + c8 * 8;
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                    }
                 }
-                if (wg == 0) {
-                    const int qrow = qt * TILE + row;
-                    if (qrow < p.N)
-                        p.lse[(static_cast<size_t>(bs) * p.H + h) * p.N + qrow] = mt * LN2 + __logf(lt);
-                }
+                if (wg == 0 && qrow < p.N)
+                    p.lse[(static_cast<size_t>(bs) * p.H + h) * p.N + qrow] = mt * LN2 + __logf(lt);
             }
             fence_async_smem();
-            ok = warp_all(group_sync());
+            ok = group_sync();
             if (!ok) break;
             if (t256 == 0) {
                 tma_store_4d(&tm_o, sO, 0, h, qt * TILE, bs);
                 tma_commit_group();
             }
+            EVO_TE(t_epi, p.status, 0x79);
         }
         if (t256 == 0) tma_wait_group<0>();
     }
 
+    if (tid == 0) EVO_TE(t_kernel, p.status, 0x7e);
     tc_fence_before();
     __syncthreads();
     if (warp == 9) tmem_dealloc(tmem, FWD_TMEM_COLS);
@@ -430,7 +479,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 template <int DH>
 static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
-                      const void* mask, void* o, float* lse, float scale, cudaStream_t st) {
+                      const void* mask, void* o, void* o_resid, float* lse, float scale, cudaStream_t st) {
     using C = FwdCfg<DH>;
     const int BS = d->B * d->S;
     const int QT = (d->N + TILE - 1) / TILE;
@@ -452,6 +501,7 @@ static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void
     p.c1 = ((scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH))) * LOG2E;
     p.mask = static_cast<const __nv_bfloat16*>(mask);
     p.lse = lse;
+    p.o_resid = static_cast<__nv_bfloat16*>(o_resid);
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
@@ -462,24 +512,27 @@ static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void
                                             static_cast<int>(smem)))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
+    prof_begin(0, st);
     evo_fwd_kernel<DH><<<grid, FWD_THREADS, smem, st>>>(tq, tk, tv, tb, to, p);
+    prof_end(0, st);
     return cuda_err(cudaGetLastError());
 }
 
 }  // namespace evo
 
 extern "C" int evo_fwd(const EvoDims* dims, const void* q, const void* k, const void* v,
-                       const void* pair_bias, const void* res_mask, void* o, float* lse, float scale,
-                       void* stream) {
+                       const void* pair_bias, const void* res_mask, void* o, void* o_resid, float* lse,
+                       float scale, void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse) return EVO_ERR_NULL_PTR;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(pair_bias) |
-                          reinterpret_cast<uintptr_t>(o);
+                          reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(o_resid);
     if (all & 15u) return EVO_ERR_ALIGNMENT;
+    if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dims->D == 32)
-        return evo::launch_fwd<32>(dims, q, k, v, pair_bias, res_mask, o, lse, scale, st);
-    return evo::launch_fwd<64>(dims, q, k, v, pair_bias, res_mask, o, lse, scale, st);
+        return evo::launch_fwd<32>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
+    return evo::launch_fwd<64>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
 }

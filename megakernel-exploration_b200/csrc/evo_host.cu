@@ -2,11 +2,14 @@
 // the device status word.
 #include "evo_host.cuh"
 
+#include <cstdio>
 #include <mutex>
+#include <vector>
 
 namespace evo {
 
 static thread_local int t_last_cuda_error = 0;
+static thread_local char t_detail[512] = "";
 
 int cuda_err(cudaError_t e) {
     if (e == cudaSuccess) return EVO_OK;
@@ -48,7 +51,14 @@ int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int ra
     CUresult r = fn(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), extent, stride,
                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? EVO_OK : EVO_ERR_TENSOR_MAP;
+    if (r == CUDA_SUCCESS) return EVO_OK;
+    int n = snprintf(t_detail, sizeof(t_detail), "cuTensorMapEncodeTiled -> %d: base=%p dtype=%d rank=%d swizzle=%d",
+                     static_cast<int>(r), base, static_cast<int>(dt), rank, static_cast<int>(swz));
+    for (int i = 0; i < rank && n > 0 && n < static_cast<int>(sizeof(t_detail)); ++i)
+        n += snprintf(t_detail + n, sizeof(t_detail) - n, " [extent=%llu stride=%llu box=%u]",
+                      static_cast<unsigned long long>(dims[i].extent),
+                      static_cast<unsigned long long>(i > 0 ? dims[i].stride_bytes : 0), dims[i].box);
+    return EVO_ERR_TENSOR_MAP;
 }
 
 int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows) {
@@ -95,8 +105,55 @@ int make_tmap_dbias(CUtensorMap* out, const void* base, int B, int H, int N) {
     return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+static CUtensorMapSwizzle swizzle_for(int row_bytes) {
+    return row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                           : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+int make_tmap_rows_box(CUtensorMap* out, const void* base, int elem_bytes, int BS, int N, int H, int D,
+                       int box_cols, int rows) {
+    const uint64_t e = static_cast<uint64_t>(elem_bytes);
+    const int rb = box_cols * elem_bytes;
+    if (rb != 32 && rb != 64 && rb != 128) return EVO_ERR_TENSOR_MAP;
+    TmapDim d[4] = {
+        {static_cast<uint64_t>(D), 0, static_cast<uint32_t>(box_cols)},
+        {static_cast<uint64_t>(H), D * e, 1},
+        {static_cast<uint64_t>(N), static_cast<uint64_t>(H) * D * e, static_cast<uint32_t>(rows)},
+        {static_cast<uint64_t>(BS), static_cast<uint64_t>(N) * H * D * e, 1},
+    };
+    return make_tmap(out, base, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                     4, d, swizzle_for(rb));
+}
+
+int make_tmap_dbias_box(CUtensorMap* out, const void* base, int B, int H, int N, int box_cols, int rows) {
+    const uint64_t e = 4;
+    const int rb = box_cols * 4;
+    if (rb != 32 && rb != 64 && rb != 128) return EVO_ERR_TENSOR_MAP;
+    TmapDim d[4] = {
+        {static_cast<uint64_t>(N), 0, static_cast<uint32_t>(box_cols)},
+        {static_cast<uint64_t>(N), N * e, static_cast<uint32_t>(rows)},
+        {static_cast<uint64_t>(H), static_cast<uint64_t>(N) * N * e, 1},
+        {static_cast<uint64_t>(B), static_cast<uint64_t>(H) * N * N * e, 1},
+    };
+    return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, swizzle_for(rb));
+}
+
+// Binds the device's primary context to the calling thread.  The tensor-map
+// encoder is a driver call and fails with "invalid context" on a thread (for
+// example an autograd worker) that has not made a runtime call yet.
+int ensure_context() {
+    int dev = 0;
+    int rc = cuda_err(cudaGetDevice(&dev));
+    if (rc) return rc;
+    return cuda_err(cudaSetDevice(dev));
+}
+
 // One status word per device; kernels receive its address as an argument.
+#ifdef EVO_TRACE
+__device__ unsigned long long g_status_word[1 + 512] = {0};   // status word + cycle accounting
+#else
 __device__ unsigned int g_status_word = 0;
+#endif
 
 unsigned int* status_word() {
     static std::mutex mu;
@@ -115,6 +172,37 @@ unsigned int* status_word() {
     return cache[dev];
 }
 
+// ---- optional per-kernel timing ------------------------------------------------
+namespace {
+struct ProfRec {
+    std::vector<cudaEvent_t> start, stop;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+ProfRec g_prof[2];
+constexpr size_t PROF_MAX = 4096;
+}  // namespace
+
+void prof_begin(int kernel, cudaStream_t st) {
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    if (!g_prof_on || g_prof[kernel].start.size() >= PROF_MAX) return;
+    cudaEvent_t a = nullptr, b = nullptr;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return;
+    }
+    cudaEventRecord(a, st);
+    g_prof[kernel].start.push_back(a);
+    g_prof[kernel].stop.push_back(b);
+}
+
+void prof_end(int kernel, cudaStream_t st) {
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    ProfRec& r = g_prof[kernel];
+    if (!g_prof_on || r.start.empty() || r.start.size() > PROF_MAX) return;
+    cudaEventRecord(r.stop.back(), st);
+}
+
 int check_dims(const EvoDims* d) {
     if (!d) return EVO_ERR_NULL_PTR;
     if (d->B <= 0 || d->S <= 0 || d->N <= 0 || d->H <= 0) return EVO_ERR_BAD_DIMS;
@@ -131,9 +219,11 @@ int check_dims(const EvoDims* d) {
 
 extern "C" {
 
-int evo_version(void) { return 100; }
+int evo_version(void) { return 101; }
 
 int evo_last_cuda_error(void) { return evo::t_last_cuda_error; }
+
+const char* evo_last_error_detail(void) { return evo::t_detail; }
 
 int evo_device_status(uint32_t* raw) {
     unsigned int* p = evo::status_word();
@@ -148,6 +238,51 @@ int evo_device_status(uint32_t* raw) {
     rc = evo::cuda_err(cudaMemset(p, 0, sizeof(v)));
     if (rc) return rc;
     return EVO_ERR_DEVICE_WAIT;
+}
+
+#ifdef EVO_TRACE
+// Trace builds only: copies (and clears) the 256 (cycles, count) pairs.
+int evo_trace_read(unsigned long long* out) {
+    unsigned int* p = evo::status_word();
+    if (!p) return EVO_ERR_CUDA;
+    int rc = evo::cuda_err(cudaDeviceSynchronize());
+    if (rc) return rc;
+    rc = evo::cuda_err(cudaMemcpy(out, p + 2, 512 * 8, cudaMemcpyDeviceToHost));
+    if (rc) return rc;
+    return evo::cuda_err(cudaMemset(p + 2, 0, 512 * 8));
+}
+#endif
+
+int evo_profile_enable(int on) {
+    std::lock_guard<std::mutex> lock(evo::g_prof_mu);
+    evo::g_prof_on = (on != 0);
+    return EVO_OK;
+}
+
+int evo_profile_read(int kernel, float* total_ms, int* launches) {
+    if (kernel < 0 || kernel > 1 || !total_ms || !launches) return EVO_ERR_NULL_PTR;
+    std::lock_guard<std::mutex> lock(evo::g_prof_mu);
+    evo::ProfRec& r = evo::g_prof[kernel];
+    float sum = 0.f;
+    int n = 0, rc = EVO_OK;
+    for (size_t i = 0; i < r.start.size(); ++i) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(r.stop[i]) == cudaSuccess &&
+            cudaEventElapsedTime(&ms, r.start[i], r.stop[i]) == cudaSuccess) {
+            sum += ms;
+            ++n;
+        } else {
+            (void)cudaGetLastError();
+            rc = EVO_ERR_CUDA;
+        }
+        cudaEventDestroy(r.start[i]);
+        cudaEventDestroy(r.stop[i]);
+    }
+    r.start.clear();
+    r.stop.clear();
+    *total_ms = sum;
+    *launches = n;
+    return rc;
 }
 
 const char* evo_strerror(int code) {

@@ -86,6 +86,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe of phase `parity`.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Optional cycle accounting (builds with -DEVO_TRACE only): per wait site / code
+// region, summed over warps and CTAs, in the words that follow the status word.
+#ifdef EVO_TRACE
+__device__ __forceinline__ void trace_add(unsigned int* status, uint32_t site, long long dt) {
+    if ((threadIdx.x & 31u) == 0u) {
+        unsigned long long* t = reinterpret_cast<unsigned long long*>(status + 2);
+        atomicAdd(&t[(site & 255u) * 2], static_cast<unsigned long long>(dt));
+        atomicAdd(&t[(site & 255u) * 2 + 1], 1ull);
+    }
+}
+#define EVO_T0() const long long evo_t0_ = clock64()
+#define EVO_T1(status, site) trace_add((status), (site), clock64() - evo_t0_)
+#define EVO_TS(var) const long long var = clock64()
+#define EVO_TE(var, status, site) trace_add((status), (site), clock64() - var)
+#else
+#define EVO_T0() do {} while (0)
+#define EVO_T1(status, site) do {} while (0)
+#define EVO_TS(var) do {} while (0)
+#define EVO_TE(var, status, site) do {} while (0)
+#endif
+
 // Budget of one wait: an iteration limit and a wall-clock limit (try_wait may
 // itself block for a hardware-defined interval), whichever comes first.
 #ifndef EVO_WAIT_LIMIT
@@ -104,10 +140,17 @@ __device__ __forceinline__ uint64_t global_ns() {
 // Bounded wait on phase `parity` of `bar`.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
                                           uint32_t site) {
-    if (mbar_try_wait(bar, parity)) return true;
+    EVO_T0();
+    if (mbar_try_wait(bar, parity)) {
+        EVO_T1(w.status, site);
+        return true;
+    }
     uint64_t t0 = 0;
     for (uint32_t it = 0; it < EVO_WAIT_LIMIT; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) {
+            EVO_T1(w.status, site);
+            return true;
+        }
         if ((it & 63u) == 63u) {
             if (*w.abort_flag) return false;
             const uint64_t now = global_ns();
@@ -331,6 +374,29 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 // Named barrier over `nthreads` threads (ids 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Register reallocation between warpgroups (all four warps of the warpgroup
+// execute it): the producer/mma warpgroup gives registers back, the compute
+// warpgroups take them.
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Byte offset of 16-byte chunk c of row r in a TMA-swizzled tile whose rows are
+// ROW_BYTES (32, 64 or 128) long: the swizzle XORs the chunk index with address
+// bits 7.. (row >> 2, row >> 1, row for 32/64/128-byte rows).
+template <int ROW_BYTES>
+__device__ __forceinline__ uint32_t swz_off(int r, int c) {
+    static_assert(ROW_BYTES == 32 || ROW_BYTES == 64 || ROW_BYTES == 128, "swizzled row");
+    constexpr int SH = (ROW_BYTES == 128) ? 0 : (ROW_BYTES == 64 ? 1 : 2);
+    constexpr int MASK = ROW_BYTES / 16 - 1;
+    return r * ROW_BYTES + ((c ^ ((r >> SH) & MASK)) << 4);
 }
 
 constexpr float LOG2E = 1.4426950408889634f;

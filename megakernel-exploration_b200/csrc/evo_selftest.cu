@@ -123,6 +123,8 @@ static int launch_selftest(const void* x, const void* y, const void* z, float* o
 extern "C" int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
                                 float* out_xy, float* out_xty, void* stream) {
     if (!x || !y || !z || !out_yzt || !out_xy || !out_xty) return EVO_ERR_NULL_PTR;
+    if (D != 32 && D != 64) return EVO_ERR_BAD_DIMS;
+    if (int rc = evo::ensure_context()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (D == 32) return evo::launch_selftest<32>(x, y, z, out_yzt, out_xy, out_xty, st);
     if (D == 64) return evo::launch_selftest<64>(x, y, z, out_yzt, out_xy, out_xty, st);

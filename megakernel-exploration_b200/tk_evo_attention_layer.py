@@ -66,6 +66,15 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def _check_device(t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise RuntimeError("TKEvoAttention needs CUDA tensors (there is no CPU path)")
+
+
+def _device_ctx(t: torch.Tensor):
+    return torch.cuda.device(t.device)
+
+
 class TKEvoAttention(torch.autograd.Function):
     """Evo / triangle attention: softmax(Q K^T / sqrt(D) + pair_bias + res_mask) V."""
 
@@ -81,8 +90,7 @@ class TKEvoAttention(torch.autograd.Function):
             f"pair_bias shape mismatch: expected (B,1,H,N,N)={(B, 1, H, N_CTX, N_CTX)}, got {pair_bias.shape}"
         )
         padded_D = _next_supported_dim(D)
-        if not Q.is_cuda:
-            raise RuntimeError("TKEvoAttention needs CUDA tensors (there is no CPU path)")
+        _check_device(Q)
         if N_CTX % 8 != 0:
             raise ValueError(f"N_CTX must be a multiple of 8, got {N_CTX}")
 
@@ -99,12 +107,14 @@ class TKEvoAttention(torch.autograd.Function):
         softmax_scale = 1.0 / (D ** 0.5)
 
         o = torch.empty_like(q)
+        # rounding residual of O, kept for backward only (accurate delta -> accurate dBias)
+        o_resid = torch.empty_like(q) if any(ctx.needs_input_grad) else None
         lse = torch.empty((B, N_SEQ, H, N_CTX), dtype=torch.float32, device=q.device)
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
-        with torch.cuda.device(q.device):
-            _evoattn.fwd(dims, q, k, v, bias, mask, o, lse, softmax_scale, _stream())
+        with _device_ctx(q):
+            _evoattn.fwd(dims, q, k, v, bias, mask, o, o_resid, lse, softmax_scale, _stream())
 
-        ctx.save_for_backward(q, k, v, bias, mask, o, lse)
+        ctx.save_for_backward(q, k, v, bias, mask, o, o_resid, lse)
         ctx.softmax_scale = softmax_scale
         ctx.true_D = D
         ctx.padded_D = padded_D
@@ -116,7 +126,7 @@ class TKEvoAttention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dO):
-        q, k, v, bias, mask, o, lse = ctx.saved_tensors
+        q, k, v, bias, mask, o, o_resid, lse = ctx.saved_tensors
         B, N_SEQ, N_CTX, H = ctx.dims
         D, padded_D = ctx.true_D, ctx.padded_D
 
@@ -130,8 +140,8 @@ class TKEvoAttention(torch.autograd.Function):
         dbias = torch.empty((B, H, N_CTX, N_CTX), dtype=torch.float32, device=q.device)
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
         ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=q.device)
-        with torch.cuda.device(q.device):
-            _evoattn.bwd(dims, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, ws,
+        with _device_ctx(q):
+            _evoattn.bwd(dims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
                          ctx.softmax_scale, _stream())
 
         if ctx.process_group is not None:

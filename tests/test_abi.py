@@ -43,13 +43,14 @@ def test_argument_validation_without_gpu():
     for bad in (_evoattn.EvoDims(1, 4, 128, 2, 128), _evoattn.EvoDims(1, 4, 100, 2, 32),
                 _evoattn.EvoDims(0, 4, 128, 2, 32), _evoattn.EvoDims(1, 4, 128, 2, 48)):
         assert lib.evo_bwd_workspace_bytes(C.byref(bad)) == 0
-        rc = lib.evo_fwd(C.byref(bad), 16, 16, 16, 16, 16, 16, 16, 0.0, None)
+        rc = lib.evo_fwd(C.byref(bad), 16, 16, 16, 16, 16, 16, None, 16, 0.0, None)
         assert rc == -1
-    assert lib.evo_fwd(C.byref(good), None, 16, 16, 16, 16, 16, 16, 0.0, None) == -2
-    assert lib.evo_fwd(C.byref(good), 8, 16, 16, 16, 16, 16, 16, 0.0, None) == -3
-    assert lib.evo_fwd(None, 16, 16, 16, 16, 16, 16, 16, 0.0, None) == -2
+    assert lib.evo_fwd(C.byref(good), None, 16, 16, 16, 16, 16, None, 16, 0.0, None) == -2
+    assert lib.evo_fwd(C.byref(good), 8, 16, 16, 16, 16, 16, None, 16, 0.0, None) == -3
+    assert lib.evo_fwd(C.byref(good), 16, 16, 16, 16, 16, 16, 8, 16, 0.0, None) == -3    # o_resid misaligned
+    assert lib.evo_fwd(None, 16, 16, 16, 16, 16, 16, None, 16, 0.0, None) == -2
     args = [16] * 13
-    assert lib.evo_bwd(C.byref(good), *args[:12], 256, 0, 0.0, None) == -4    # workspace too small
+    assert lib.evo_bwd(C.byref(good), *args, 256, 0, 0.0, None) == -4    # workspace too small
     assert lib.evo_selftest_mma(48, 16, 16, 16, 16, 16, 16, None) == -1
 
 

@@ -136,11 +136,12 @@ def test_c_abi_direct():
     lse = torch.empty((B, S, H, N), dtype=torch.float32, device=dev)
     dims = _evoattn.EvoDims(B, S, N, H, D)
     st = torch.cuda.current_stream().cuda_stream
-    _evoattn.fwd(dims, qd, kd, vd, bd, md, o, lse, 0.0, st)      # scale <= 0 -> 1/sqrt(D)
+    o_resid = torch.empty_like(qd)
+    _evoattn.fwd(dims, qd, kd, vd, bd, md, o, o_resid, lse, 0.0, st)      # scale <= 0 -> 1/sqrt(D)
     dq, dk, dv = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
     dbias = torch.empty((B, H, N, N), dtype=torch.float32, device=dev)
     ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=dev)
-    _evoattn.bwd(dims, qd, kd, vd, bd, md, o, lse, dod, dq, dk, dv, dbias, ws, 0.0, st)
+    _evoattn.bwd(dims, qd, kd, vd, bd, md, o, o_resid, lse, dod, dq, dk, dv, dbias, ws, 0.0, st)
     _evoattn.device_status()
     ref = oracle_on_rounded(q, k, v, mask, bias, d_o)
     got = {"o": o.float().cpu(), "dq": dq.float().cpu(), "dk": dk.float().cpu(), "dv": dv.float().cpu(),
@@ -152,5 +153,5 @@ def test_c_abi_direct():
     # argument validation returns codes, never throws from C
     bad = _evoattn.EvoDims(B, S, N, H, 128)
     with pytest.raises(_evoattn.EvoAttnError) as ei:
-        _evoattn.fwd(bad, qd, kd, vd, bd, md, o, lse, 0.0, st)
+        _evoattn.fwd(bad, qd, kd, vd, bd, md, o, None, lse, 0.0, st)
     assert ei.value.code == -1
