@@ -102,9 +102,10 @@ int evo_profile_read(int kernel, float* total_ms, int* launches);
  *   out_yzt [128][128] = y z^T      (both operands K-major row tiles)
  *   out_xy  [128][D]   = x y        (A K-major square tile, B MN-major row tile)
  *   out_xty [128][D]   = x^T y      (A MN-major square tile, B MN-major row tile)
+ *   out_ts  [128][D]   = x y        (A in tensor memory, B MN-major row tile)
  * all fp32. */
 int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
-                     float* out_xy, float* out_xty, void* stream);
+                     float* out_xy, float* out_xty, float* out_ts, void* stream);
 
 #ifdef __cplusplus
 }

@@ -36,7 +36,7 @@ SYMBOLS = {
     "evo_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
     "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 14 + [C.c_size_t, C.c_float, C.c_void_p]),
     "evo_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
-    "evo_selftest_mma": (C.c_int, [C.c_int] + [C.c_void_p] * 7),
+    "evo_selftest_mma": (C.c_int, [C.c_int] + [C.c_void_p] * 8),
     "evo_profile_enable": (C.c_int, [C.c_int]),
     "evo_profile_read": (C.c_int, [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
 }
@@ -125,6 +125,6 @@ def profile_read(kernel: int):
     return ms.value, n.value
 
 
-def selftest_mma(D: int, x, y, z, out_yzt, out_xy, out_xty, stream: int) -> None:
+def selftest_mma(D: int, x, y, z, out_yzt, out_xy, out_xty, out_ts, stream: int) -> None:
     check(lib().evo_selftest_mma(int(D), _ptr(x), _ptr(y), _ptr(z), _ptr(out_yzt), _ptr(out_xy),
-                                 _ptr(out_xty), stream), "evo_selftest_mma")
+                                 _ptr(out_xty), _ptr(out_ts), stream), "evo_selftest_mma")

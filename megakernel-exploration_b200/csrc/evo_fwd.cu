@@ -11,30 +11,30 @@
 // fastest so that CTAs running side by side touch the same 128-byte lines of
 // q/k/v.  Per item it streams kv tiles of 128 residues:
 //
-//   warp 8  (producer)  TMA: Q tile (double buffered), then per kv tile K, V and
-//                       the [128 x 128] bf16 pair-bias tile into a ring of stages
+//   warp 8  (producer)  TMA: Q tile (double buffered), then per kv tile K, V, the
+//                       [128 x 128] bf16 pair-bias tile and the mask row into a
+//                       ring of stages
 //   warp 9  (mma)       tcgen05.mma, issued in whatever order operands become
 //                       ready: S = Q K^T into tensor memory and, per softmax
-//                       group g, PV_g = P[:, 64g:64g+64] V[64g:64g+64, :]
+//                       group g, PV_g = P_g V[64g:64g+64, :] with P_g read from
+//                       tensor memory
 //   warps 0-3, 4-7      two softmax groups.  Group g owns kv columns 64g..64g+63
 //                       of every tile and runs its own online softmax over them
 //                       (thread = one q row): x = S*scale*log2e + bias*log2e +
-//                       mask*log2e, running max, exp2, P (bf16) to shared memory,
-//                       O_g = (O_g + PV_g) * alpha.  The two partial results are
-//                       merged once per item (split-kv merge) and O goes out by TMA.
+//                       mask*log2e, running max, exp2, P (bf16) back into tensor
+//                       memory, O_g = (O_g + PV_g) * alpha.  After an item, group 1
+//                       hands its partial (m, l, O) to group 0, which merges the
+//                       two (split-kv merge) and sends O out by TMA.  That
+//                       epilogue is deferred into the next item's first tile, so
+//                       the last PV of an item is never waited for idly.
 //
 // LSE is stored in natural log (tk_evoattention.cu:330-334).
 #include "evo_host.cuh"
 #include "evo_tiles.cuh"
 
-#ifndef EVO_EXP
-#define EVO_EXP 0
-#endif
-
 namespace evo {
 
 constexpr int FWD_THREADS = 384;           // 3 warpgroups: 2 softmax + (producer, mma, 2 idle warps)
-constexpr uint32_t FWD_TMEM_COLS = 256;
 constexpr int FWD_REGS_SOFTMAX = 224;
 constexpr int FWD_REGS_OTHER = 56;
 
@@ -42,20 +42,26 @@ template <int DH>
 struct FwdCfg {
     static constexpr int STAGES = (DH == 32) ? 3 : 2;
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;          // one [128][DH] bf16 tile
-    static constexpr uint32_t STAGE_TX = 2 * ROWT + SQ_BYTES;      // K + V + bias tile
+    // one stage: K tile, V tile, bias tile (two [128][64] halves), raw bf16 mask row
+    static constexpr uint32_t ST_K = 0, ST_V = ROWT, ST_BIAS = 2 * ROWT, ST_MASK = 2 * ROWT + SQ_BYTES;
+    static constexpr uint32_t STAGE_STRIDE = 2 * ROWT + SQ_BYTES + 1024;
     static constexpr uint32_t OFF_Q = 0;                           // 2 buffers
-    static constexpr uint32_t OFF_K = OFF_Q + 2 * ROWT;
-    static constexpr uint32_t OFF_V = OFF_K + STAGES * ROWT;
-    static constexpr uint32_t OFF_BIAS = OFF_V + STAGES * ROWT;
-    static constexpr uint32_t OFF_P = OFF_BIAS + STAGES * SQ_BYTES;
-    static constexpr uint32_t OFF_O = OFF_P + SQ_BYTES;
-    static constexpr uint32_t OFF_ML = OFF_O + ROWT;               // [2][128] float2
-    static constexpr uint32_t OFF_BARS = OFF_ML + 2 * 128 * 8;
-    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 2 + 2 + 2 + 1;
-    static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;  // tmem slot, abort flag
-    static constexpr uint32_t OFF_MASK = (OFF_MISC + 16 + 127) & ~127u;  // 2 x [NT*128] float
+    static constexpr uint32_t OFF_STAGE = OFF_Q + 2 * ROWT;
+    static constexpr uint32_t OFF_O = OFF_STAGE + STAGES * STAGE_STRIDE;
+    // group 1 -> group 0 hand-over: per row m, l and DH accumulator values, padded pitch
+    static constexpr uint32_t XCH_PITCH = (DH + 4) * 4;
+    static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
+    static constexpr uint32_t OFF_WMASK = OFF_XCH + 128 * XCH_PITCH;       // 8 warps x 64 floats
+    static constexpr uint32_t OFF_BARS = OFF_WMASK + 8 * 256;
+    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 2 + 2 + 2 + 3;
+    static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
+    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
     static constexpr uint32_t TMEM_PV = 128;                       // + g * DH
+    static constexpr uint32_t TMEM_P = 128 + 2 * DH;               // + g * 32: 64 bf16 per lane
+    static constexpr uint32_t TMEM_COLS = (TMEM_P + 64 <= 256) ? 256 : 512;
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+    static_assert(OFF_STAGE % 1024 == 0 && STAGE_STRIDE % 1024 == 0 && OFF_O % 1024 == 0, "tile alignment");
 };
 
 struct FwdParams {
@@ -89,11 +95,11 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* s_free = s_full + 1;           // [1]
     uint64_t* p_ready = s_free + 1;          // [2]
     uint64_t* pv_full = p_ready + 2;         // [2]
-    uint64_t* grp_bar = pv_full + 2;         // [1] rendezvous of the eight softmax warps
+    uint64_t* xch_full = pv_full + 2;        // group 1 has written its partial result
+    uint64_t* xch_empty = xch_full + 1;      // group 0 has read it
+    uint64_t* g0_bar = xch_empty + 1;        // rendezvous of group 0's four warps
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_mask = reinterpret_cast<float*>(smem + C::OFF_MASK);
-    float2* s_ml = reinterpret_cast<float2*>(smem + C::OFF_ML);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -108,12 +114,14 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(s_full, 1);
         mbar_init(s_free, 8);
         for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
-        mbar_init(grp_bar, 8);
+        mbar_init(xch_full, 4);
+        mbar_init(xch_empty, 4);
+        mbar_init(g0_bar, 4);
         fence_mbar_init();
         fence_async_smem();
     }
     if (warp == 9) {
-        tmem_alloc(tmem_slot, FWD_TMEM_COLS);
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
         tmem_relinquish();
     }
     if (warp == 8 && lane == 0) {
@@ -158,12 +166,14 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     const int st = g % ST;
                     if (g >= ST) ok = mbar_wait(&kv_empty[st], ((g / ST) - 1) & 1, wc, 0x11);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&kv_full[st], C::STAGE_TX);
-                    tma_load_4d(smem + C::OFF_K + st * C::ROWT, &tm_k, &kv_full[st], 0, h, j * TILE, bs);
-                    tma_load_4d(smem + C::OFF_V + st * C::ROWT, &tm_v, &kv_full[st], 0, h, j * TILE, bs);
-                    uint8_t* sb = smem + C::OFF_BIAS + st * SQ_BYTES;
-                    tma_load_4d(sb, &tm_bias, &kv_full[st], j * TILE, qt * TILE, h, b);
-                    tma_load_4d(sb + SQ_SUB_BYTES, &tm_bias, &kv_full[st], j * TILE + 64, qt * TILE, h, b);
+                    uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
+                    const int ncol = (p.N - j * TILE < TILE) ? (p.N - j * TILE) : TILE;   // multiple of 8
+                    mbar_arrive_expect_tx(&kv_full[st], 2 * C::ROWT + SQ_BYTES + ncol * 2);
+                    tma_load_4d(sb + C::ST_K, &tm_k, &kv_full[st], 0, h, j * TILE, bs);
+                    tma_load_4d(sb + C::ST_V, &tm_v, &kv_full[st], 0, h, j * TILE, bs);
+                    tma_load_4d(sb + C::ST_BIAS, &tm_bias, &kv_full[st], j * TILE, qt * TILE, h, b);
+                    tma_load_4d(sb + C::ST_BIAS + SQ_SUB_BYTES, &tm_bias, &kv_full[st], j * TILE + 64, qt * TILE, h, b);
+                    bulk_load(sb + C::ST_MASK, p.mask + static_cast<size_t>(bs) * p.N + j * TILE, ncol * 2, &kv_full[st]);
                 }
             }
             // Drain: every load issued above has landed before the CTA exits.
@@ -176,19 +186,17 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // ------------------------------ mma issuer ------------------------------
             // Issues whichever MMA has its operands ready: S of the next tile (needs
             // its loads and the S accumulator read out) or PV_g of a tile whose P_g
-            // is in shared memory.  Nothing here blocks on one barrier while
+            // is in tensor memory.  Nothing here blocks on one barrier while
             // another piece of work could go.
             constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, DH, 0, 1);
-            const uint32_t aQ = smem_u32(smem + C::OFF_Q), aK = smem_u32(smem + C::OFF_K);
-            const uint32_t aV = smem_u32(smem + C::OFF_V), aP = smem_u32(smem + C::OFF_P);
+            const uint32_t aQ = smem_u32(smem + C::OFF_Q), aSt = smem_u32(smem + C::OFF_STAGE);
             const int total_tiles = n_items * NT;
             int s_next = 0;
             int pv_next[2] = {0, 0};
             uint32_t idle = 0;
             uint64_t idle_t0 = 0;
-            bool ok = true;
-            while (ok && (pv_next[0] < total_tiles || pv_next[1] < total_tiles)) {
+            while (pv_next[0] < total_tiles || pv_next[1] < total_tiles) {
                 bool progress = false;
                 if (s_next < total_tiles) {
                     const int g = s_next;
@@ -202,7 +210,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                         for (int kb = 0; kb < RT::KBLOCKS; ++kb)
                             umma_ss(tmem + C::TMEM_S, RT::kmajor(aQ + qb * C::ROWT, kb),
-                                    RT::kmajor(aK + st * C::ROWT, kb), IDESC_S, kb > 0);
+                                    RT::kmajor(aSt + st * C::STAGE_STRIDE + C::ST_K, kb), IDESC_S, kb > 0);
                         umma_commit(s_full);
                         if (j == NT - 1) umma_commit(&q_empty[qb]);
                         ++s_next;
@@ -216,11 +224,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const int st = g % ST;
                         tc_fence_after();
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const int kb = 4 * w + kk;
-                            umma_ss(tmem + C::TMEM_PV + w * DH, sq_kmajor(aP, kb),
-                                    RT::mnmajor(aV + st * C::ROWT, kb), IDESC_PV, kk > 0);
-                        }
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_ts(tmem + C::TMEM_PV + w * DH, tmem + C::TMEM_P + w * 32 + kk * 8,
+                                    RT::mnmajor(aSt + st * C::STAGE_STRIDE + C::ST_V, 4 * w + kk), IDESC_PV, kk > 0);
                         umma_commit(&pv_full[w]);
                         ++pv_next[w];
                         if (pv_next[w ^ 1] > g) umma_commit(&kv_empty[st]);   // both groups' PV of tile g issued
@@ -229,17 +235,17 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 if (progress) {
                     idle = 0;
-                } else if (EVO_EXP & 16) {
-                    __nanosleep(32);
-                    if ((++idle & 255u) == 0u && *abort_flag) { ok = false; break; }
-                } else if ((++idle & 255u) == 0u) {
-                    if (*abort_flag) { ok = false; break; }
-                    const uint64_t now = global_ns();
-                    if (idle == 256u) idle_t0 = now;
-                    if (now - idle_t0 > EVO_WAIT_NS) {
-                        report(p.status, ST_WAIT_TIMEOUT, 0x2f);
-                        *abort_flag = 1u;
-                        ok = false;
+                } else {
+                    __nanosleep(20);
+                    if ((++idle & 255u) == 0u) {
+                        if (*abort_flag) break;
+                        const uint64_t now = global_ns();
+                        if (idle == 256u) idle_t0 = now;
+                        if (now - idle_t0 > EVO_WAIT_NS) {
+                            report(p.status, ST_WAIT_TIMEOUT, 0x2f);
+                            *abort_flag = 1u;
+                            break;
+                        }
                     }
                 }
             }
@@ -250,43 +256,106 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int wg = warp >> 2;            // 0 or 1: kv columns 64*wg .. 64*wg+63 of each tile
         const int row = tid & 127;           // q row within the tile == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-        const int t256 = tid;                // 0..255 over both groups
-        uint8_t* sP = smem + C::OFF_P;
         uint8_t* sO = smem + C::OFF_O;
+        float* xrow = reinterpret_cast<float*>(smem + C::OFF_XCH + row * C::XCH_PITCH);
+        float* wmask = reinterpret_cast<float*>(smem + C::OFF_WMASK + warp * 256);
         bool ok = true;
         int g = 0;
-        uint32_t grp_phase = 0;
-        // rendezvous of both groups (bounded)
-        auto group_sync = [&]() -> bool {
+        uint32_t g0_phase = 0;
+        auto g0_sync = [&]() -> bool {       // group 0 only (bounded)
             __syncwarp();
-            if (lane == 0) mbar_arrive(grp_bar);
-            const bool r = mbar_wait(grp_bar, grp_phase, wc, 0x30);
-            grp_phase ^= 1u;
+            if (lane == 0) mbar_arrive(g0_bar);
+            const bool r = mbar_wait(g0_bar, g0_phase, wc, 0x30);
+            g0_phase ^= 1u;
             return warp_all(r);
         };
+
+        float m = -INFINITY, l = 0.f;
+        float acc[DH];
+#pragma unroll
+        for (int i = 0; i < DH; ++i) acc[i] = 0.f;
+
+        // Finishes item `k` (coordinates pbs/pqt/ph) from its partial state (pm, pl, acc):
+        // group 1 hands its state over, group 0 merges, normalises and writes O / LSE.
+        auto epilogue = [&](int k, int pbs, int pqt, int ph, float pm, float pl) -> bool {
+            EVO_TS(t_epi);
+            if (wg == 1) {
+                if (k > 0 && !warp_all(mbar_wait(xch_empty, (k - 1) & 1, wc, 0x35))) return false;
+                xrow[0] = pm;
+                xrow[1] = pl;
+#pragma unroll
+                for (int c = 0; c < DH / 4; ++c)
+                    *reinterpret_cast<float4*>(xrow + 4 + c * 4) =
+                        make_float4(acc[c * 4 + 0], acc[c * 4 + 1], acc[c * 4 + 2], acc[c * 4 + 3]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(xch_full);
+            } else {
+                if (!warp_all(mbar_wait(xch_full, k & 1, wc, 0x36))) return false;
+                const float om = xrow[0], ol = xrow[1];
+                const float mt = fmaxf(pm, om);            // finite: column 0 of tile 0 is never -inf
+                const float f = ex2(pm - mt), fo = ex2(om - mt);
+                const float lt = pl * f + ol * fo;
+                const float inv = 1.f / lt;
+                float outv[DH];
+#pragma unroll
+                for (int c = 0; c < DH / 4; ++c) {
+                    const float4 v = *reinterpret_cast<const float4*>(xrow + 4 + c * 4);
+                    outv[c * 4 + 0] = (acc[c * 4 + 0] * f + v.x * fo) * inv;
+                    outv[c * 4 + 1] = (acc[c * 4 + 1] * f + v.y * fo) * inv;
+                    outv[c * 4 + 2] = (acc[c * 4 + 2] * f + v.z * fo) * inv;
+                    outv[c * 4 + 3] = (acc[c * 4 + 3] * f + v.w * fo) * inv;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(xch_empty);
+                // the previous O store must have finished reading sO before it is rewritten
+                if (tid == 0) tma_wait_group_read<0>();
+                if (!g0_sync()) return false;
+                const int qrow = pqt * TILE + row;
+#pragma unroll
+                for (int c8 = 0; c8 < DH / 8; ++c8) {
+                    uint4 v;
+                    v.x = pack_bf16(outv[c8 * 8 + 0], outv[c8 * 8 + 1]);
+                    v.y = pack_bf16(outv[c8 * 8 + 2], outv[c8 * 8 + 3]);
+                    v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
+                    v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
+                    *reinterpret_cast<uint4*>(sO + swz_off<RT::ROW_BYTES>(row, c8)) = v;
+                    if (p.o_resid != nullptr && qrow < p.N) {
+                        // rounding residual of O, straight to global memory
+                        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                        uint32_t rw[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]),
+                                              outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
+                        __nv_bfloat16* dst =
+                            p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + c8 * 8;
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                    }
+                }
+                if (qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = mt * LN2 + __logf(lt);
+                fence_async_smem();
+                if (!g0_sync()) return false;
+                if (tid == 0) {
+                    tma_store_4d(&tm_o, sO, 0, ph, pqt * TILE, pbs);
+                    tma_commit_group();
+                }
+            }
+            EVO_TE(t_epi, p.status, 0x79);
+            return true;
+        };
+
+        bool have_prev = false;
+        int pbs = 0, pqt = 0, ph = 0;
+        float pm = 0.f, pl = 0.f;
 
         for (int it = 0; it < n_items && ok; ++it) {
             int bs, qt, h;
             decode(it, bs, qt, h);
-            float* mk = s_mask + (it & 1) * NT * TILE;
-            {
-                const __nv_bfloat16* src = p.mask + static_cast<size_t>(bs) * p.N;
-                for (int i = t256; i < NT * TILE; i += 256)
-                    mk[i] = (i < p.N) ? __bfloat162float(src[i]) * LOG2E : -INFINITY;
-            }
-            // The thread that issued the previous item's O store makes sure the
-            // store has finished reading sO before anyone rewrites it.
-            if (t256 == 0) tma_wait_group_read<0>();
-            ok = group_sync();
-            if (!ok) break;
-
-            float m = -INFINITY, l = 0.f;
-            float acc[DH];
-#pragma unroll
-            for (int i = 0; i < DH; ++i) acc[i] = 0.f;
-
+            m = -INFINITY;
+            l = 0.f;
             for (int j = 0; j < NT && ok; ++j, ++g) {
                 const int st = g % ST;
+                const uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
                 ok = warp_all(mbar_wait(s_full, g & 1, wc, 0x31));
                 if (!ok) break;
                 EVO_TS(t_tile);
@@ -305,16 +374,25 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
                 ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x32));
                 if (!ok) break;
-                const uint8_t* sb = smem + C::OFF_BIAS + st * SQ_BYTES + wg * SQ_SUB_BYTES;
-                const float* mrow = mk + j * TILE + 64 * wg;
+                {
+                    // this warp's copy of the mask row slice: bf16 -> fp32 * log2e, -inf past N
+                    const __nv_bfloat16* mraw = reinterpret_cast<const __nv_bfloat16*>(sb + C::ST_MASK) + 64 * wg;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        const int c = lane + 32 * t;
+                        wmask[c] = (j * TILE + 64 * wg + c < p.N) ? __bfloat162float(mraw[c]) * LOG2E : -INFINITY;
+                    }
+                    __syncwarp();
+                }
+                const uint8_t* sbias = sb + C::ST_BIAS + wg * SQ_SUB_BYTES;
                 float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: ILP
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
-                    const uint4 bv = *reinterpret_cast<const uint4*>(sb + swz_off<128>(row, c8));
+                    const uint4 bv = *reinterpret_cast<const uint4*>(sbias + swz_off<128>(row, c8));
                     const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                     for (int q4 = 0; q4 < 2; ++q4) {
-                        const float4 mv = *reinterpret_cast<const float4*>(mrow + c8 * 8 + q4 * 4);
+                        const float4 mv = *reinterpret_cast<const float4*>(wmask + c8 * 8 + q4 * 4);
                         const float mm[4] = {mv.x, mv.y, mv.z, mv.w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
@@ -344,11 +422,14 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
                 m = m_new;
 
-                if (j > 0) {
-                    // PV of the previous tile: also tells us its MMA no longer reads sP.
+                // The P columns in tensor memory are free once the previous tile's PV MMA is
+                // done; its result is folded in here.  On the first tile of an item that
+                // previous tile belongs to the previous item, whose epilogue runs now.
+                if (j > 0 || have_prev) {
                     ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x33));
                     if (!ok) break;
                     tc_fence_after();
+                    const float sc = (j > 0) ? alpha : 1.0f;
 #pragma unroll
                     for (int c = 0; c < DH / 32; ++c) {
                         uint32_t r[32];
@@ -356,125 +437,57 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(r[i])) * alpha;
+                            acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(r[i])) * sc;
+                    }
+                    if (j == 0) {
+                        ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
+                        if (!ok) break;
+#pragma unroll
+                        for (int i = 0; i < DH; ++i) acc[i] = 0.f;
                     }
                 }
-                // P (bf16) into this group's [128][64] sub-tile of the square tile.
+                // P (bf16 pairs) into this group's 32 columns of tensor memory
+                {
+                    uint32_t pk[32];
 #pragma unroll
-                for (int c8 = 0; c8 < 8; ++c8) {
-                    uint4 v;
-                    v.x = pack_bf16(__uint_as_float(sr[c8 * 8 + 0]), __uint_as_float(sr[c8 * 8 + 1]));
-                    v.y = pack_bf16(__uint_as_float(sr[c8 * 8 + 2]), __uint_as_float(sr[c8 * 8 + 3]));
-                    v.z = pack_bf16(__uint_as_float(sr[c8 * 8 + 4]), __uint_as_float(sr[c8 * 8 + 5]));
-                    v.w = pack_bf16(__uint_as_float(sr[c8 * 8 + 6]), __uint_as_float(sr[c8 * 8 + 7]));
-                    *reinterpret_cast<uint4*>(sP + wg * SQ_SUB_BYTES + swz_off<128>(row, c8)) = v;
+                    for (int c = 0; c < 32; ++c)
+                        pk[c] = pack_bf16(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1]));
+                    tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
+                    tmem_wait_st();
                 }
-                fence_async_smem();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[wg]);
                 EVO_TE(t_tile, p.status, 0x78);
             }
-            if (!ok) break;
-            EVO_TS(t_epi);
-            // last tile's PV
-            ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x34));
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + C::TMEM_PV + wg * DH + c * 32, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
-            }
-            tc_fence_before();
-
-            // ---- merge the two groups' partial softmax results ----
-            // Group g finalises output columns [g*DH/2, (g+1)*DH/2): it hands the
-            // other half of its accumulator to the other group through its own
-            // (now idle) half of the P tile.
-            constexpr int HALF = DH / 2;                  // floats per row handed over
-            constexpr int XCH = HALF / 4;                 // 16-byte chunks per row
-            const int other = wg ^ 1;
-            // keep[] = the half this group finalises, give[] = the half it hands over
-            float keep[HALF], give[HALF];
-#pragma unroll
-            for (int i = 0; i < HALF; ++i) {
-                keep[i] = wg ? acc[HALF + i] : acc[i];
-                give[i] = wg ? acc[i] : acc[HALF + i];
-            }
-            {
-                uint8_t* mine = sP + wg * SQ_SUB_BYTES;
-#pragma unroll
-                for (int c = 0; c < XCH; ++c) {
-                    float4 v = make_float4(give[c * 4 + 0], give[c * 4 + 1], give[c * 4 + 2], give[c * 4 + 3]);
-                    *reinterpret_cast<float4*>(mine + swz_off<HALF * 4>(row, c)) = v;
-                }
-                s_ml[wg * 128 + row] = make_float2(m, l);
-            }
-            ok = group_sync();
-            if (!ok) break;
-            {
-                const float2 ml_o = s_ml[other * 128 + row];
-                const float mt = fmaxf(m, ml_o.x);      // finite: column 0 of tile 0 is never -inf
-                const float f = ex2(m - mt), fo = ex2(ml_o.x - mt);
-                const float lt = l * f + ml_o.y * fo;
-                const float inv = 1.f / lt;
-                const uint8_t* theirs = sP + other * SQ_SUB_BYTES;
-                float outv[HALF];
-#pragma unroll
-                for (int c = 0; c < XCH; ++c) {
-                    const float4 v = *reinterpret_cast<const float4*>(theirs + swz_off<HALF * 4>(row, c));
-                    outv[c * 4 + 0] = (keep[c * 4 + 0] * f + v.x * fo) * inv;
-                    outv[c * 4 + 1] = (keep[c * 4 + 1] * f + v.y * fo) * inv;
-                    outv[c * 4 + 2] = (keep[c * 4 + 2] * f + v.z * fo) * inv;
-                    outv[c * 4 + 3] = (keep[c * 4 + 3] * f + v.w * fo) * inv;
-                }
-                const int qrow = qt * TILE + row;
-                // bf16 row into the O staging tile (same swizzle as a row tile); the
-                // rounding residual goes straight to global memory
-#pragma unroll
-                for (int c8 = 0; c8 < HALF / 8; ++c8) {
-                    uint4 v;
-                    v.x = pack_bf16(outv[c8 * 8 + 0], outv[c8 * 8 + 1]);
-                    v.y = pack_bf16(outv[c8 * 8 + 2], outv[c8 * 8 + 3]);
-                    v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
-                    v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
-                    const int chunk = wg * (HALF / 8) + c8;   // 16-byte chunk within the row
-                    *reinterpret_cast<uint4*>(sO + swz_off<RT::ROW_BYTES>(row, chunk)) = v;
-                    if (p.o_resid != nullptr && qrow < p.N) {
-                        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-                        uint32_t rw[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]),
-                                              outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
-                        __nv_bfloat16* dst = p.o_resid +
-                            ((static_cast<size_t>(bs) * p.N + qrow) * p.H + h) * DH + wg * HALF + c8 * 8;
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
-                    }
-                }
-                if (wg == 0 && qrow < p.N)
-                    p.lse[(static_cast<size_t>(bs) * p.H + h) * p.N + qrow] = mt * LN2 + __logf(lt);
-            }
-            fence_async_smem();
-            ok = group_sync();
-            if (!ok) break;
-            if (t256 == 0) {
-                tma_store_4d(&tm_o, sO, 0, h, qt * TILE, bs);
-                tma_commit_group();
-            }
-            EVO_TE(t_epi, p.status, 0x79);
+            have_prev = true;
+            pbs = bs; pqt = qt; ph = h;
+            pm = m; pl = l;
         }
-        if (t256 == 0) tma_wait_group<0>();
+        if (ok && have_prev) {
+            // last item: its final PV and epilogue
+            ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x34));
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < DH / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_base + C::TMEM_PV + wg * DH + c * 32, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
+                }
+                tc_fence_before();
+                ok = epilogue(n_items - 1, pbs, pqt, ph, pm, pl);
+            }
+        }
+        if (tid == 0) tma_wait_group<0>();
     }
 
     if (tid == 0) EVO_TE(t_kernel, p.status, 0x7e);
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem, FWD_TMEM_COLS);
+    if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
 template <int DH>
@@ -483,8 +496,6 @@ static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void
     using C = FwdCfg<DH>;
     const int BS = d->B * d->S;
     const int QT = (d->N + TILE - 1) / TILE;
-    const size_t smem = 1024 + C::OFF_MASK + static_cast<size_t>(2) * QT * TILE * sizeof(float);
-    if (smem > 232448) return EVO_ERR_BAD_DIMS;
 
     CUtensorMap tq, tk, tv, tb, to;
     int rc;
@@ -509,11 +520,11 @@ static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void
     if ((rc = cuda_err(cudaGetDevice(&dev)))) return rc;
     if ((rc = cuda_err(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))) return rc;
     if ((rc = cuda_err(cudaFuncSetAttribute(evo_fwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(smem)))))
+                                            static_cast<int>(C::SMEM_BYTES)))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
     prof_begin(0, st);
-    evo_fwd_kernel<DH><<<grid, FWD_THREADS, smem, st>>>(tq, tk, tv, tb, to, p);
+    evo_fwd_kernel<DH><<<grid, FWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tb, to, p);
     prof_end(0, st);
     return cuda_err(cudaGetLastError());
 }
@@ -528,7 +539,8 @@ extern "C" int evo_fwd(const EvoDims* dims, const void* q, const void* k, const 
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse) return EVO_ERR_NULL_PTR;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(pair_bias) |
-                          reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(o_resid);
+                          reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(o_resid) |
+                          reinterpret_cast<uintptr_t>(res_mask);
     if (all & 15u) return EVO_ERR_ALIGNMENT;
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

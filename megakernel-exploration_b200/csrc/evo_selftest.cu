@@ -11,7 +11,8 @@ template <int DH>
 __global__ void __launch_bounds__(128, 1)
 selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_z,
                     const __nv_bfloat16* __restrict__ x, float* __restrict__ out_yzt,
-                    float* __restrict__ out_xy, float* __restrict__ out_xty, unsigned int* status) {
+                    float* __restrict__ out_xy, float* __restrict__ out_xty, float* __restrict__ out_ts,
+                    unsigned int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sX = smem;                                // 32 KB square tile
@@ -31,7 +32,7 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
         fence_async_smem();
     }
     if (warp == 0) {
-        tmem_alloc(tmem_slot, 256);
+        tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
     // X: row `tid`, sixteen 16-byte chunks, into the swizzled square tile.
@@ -47,6 +48,24 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    constexpr uint32_t T_A = 128 + 2 * DH;      // X as a bf16 A operand in tensor memory: 64 columns
+    constexpr uint32_t T_TS = T_A + 64;         // its product with y
+    {
+        // row `tid` of X: 64 words of two bf16 each, into this thread's lane
+        const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + T_A;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(x + tid * 128);
+        uint32_t r[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = src[h * 32 + i];
+            tmem_st32(lane_addr + h * 32, r);
+        }
+        tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
 
     if (tid == 0) {
         mbar_arrive_expect_tx(&bars[0], 2 * RowTile<DH>::BYTES);
@@ -67,6 +86,10 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
             for (int kb = 0; kb < 8; ++kb)
                 umma_ss(tmem + 128 + DH, sq_mnmajor(aX, kb), RowTile<DH>::mnmajor(aY, kb),
                         make_idesc_bf16(128, DH, 1, 1), kb > 0);
+#pragma unroll
+            for (int kb = 0; kb < 8; ++kb)
+                umma_ts(tmem + T_TS, tmem + T_A + kb * 8, RowTile<DH>::mnmajor(aY, kb),
+                        make_idesc_bf16(128, DH, 0, 1), kb > 0);
             umma_commit(&bars[1]);
         }
     }
@@ -92,16 +115,20 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) out_xty[tid * DH + c * 32 + i] = __uint_as_float(r[i]);
+            tmem_ld32(lane_base + T_TS + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out_ts[tid * DH + c * 32 + i] = __uint_as_float(r[i]);
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 template <int DH>
 static int launch_selftest(const void* x, const void* y, const void* z, float* o0, float* o1,
-                           float* o2, cudaStream_t st) {
+                           float* o2, float* o3, cudaStream_t st) {
     CUtensorMap tm_y, tm_z;
     int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128);
     if (rc) return rc;
@@ -114,19 +141,19 @@ static int launch_selftest(const void* x, const void* y, const void* z, float* o
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (rc) return rc;
     selftest_mma_kernel<DH><<<1, 128, smem, st>>>(tm_y, tm_z, static_cast<const __nv_bfloat16*>(x),
-                                                   o0, o1, o2, status);
+                                                   o0, o1, o2, o3, status);
     return cuda_err(cudaGetLastError());
 }
 
 }  // namespace evo
 
 extern "C" int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
-                                float* out_xy, float* out_xty, void* stream) {
-    if (!x || !y || !z || !out_yzt || !out_xy || !out_xty) return EVO_ERR_NULL_PTR;
+                                float* out_xy, float* out_xty, float* out_ts, void* stream) {
+    if (!x || !y || !z || !out_yzt || !out_xy || !out_xty || !out_ts) return EVO_ERR_NULL_PTR;
     if (D != 32 && D != 64) return EVO_ERR_BAD_DIMS;
     if (int rc = evo::ensure_context()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (D == 32) return evo::launch_selftest<32>(x, y, z, out_yzt, out_xy, out_xty, st);
-    if (D == 64) return evo::launch_selftest<64>(x, y, z, out_yzt, out_xy, out_xty, st);
+    if (D == 32) return evo::launch_selftest<32>(x, y, z, out_yzt, out_xy, out_xty, out_ts, st);
+    if (D == 64) return evo::launch_selftest<64>(x, y, z, out_yzt, out_xy, out_xty, out_ts, st);
     return EVO_ERR_BAD_DIMS;
 }

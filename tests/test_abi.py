@@ -51,7 +51,7 @@ def test_argument_validation_without_gpu():
     assert lib.evo_fwd(None, 16, 16, 16, 16, 16, 16, None, 16, 0.0, None) == -2
     args = [16] * 13
     assert lib.evo_bwd(C.byref(good), *args, 256, 0, 0.0, None) == -4    # workspace too small
-    assert lib.evo_selftest_mma(48, 16, 16, 16, 16, 16, 16, None) == -1
+    assert lib.evo_selftest_mma(48, 16, 16, 16, 16, 16, 16, 16, None) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -1,6 +1,6 @@
 """Tensor-core operand conventions: one CTA multiplies small tiles through the
 same UMMA descriptors the attention kernels use (K-major and MN-major row
-tiles, K-major and MN-major square tiles), checked against a CPU GEMM."""
+tiles, K-major and MN-major square tiles, an A operand in tensor memory), checked against a CPU GEMM."""
 import pytest
 import torch
 
@@ -19,10 +19,12 @@ def test_mma_operand_layouts(D):
     o0 = torch.full((128, 128), float("nan"), device=dev)
     o1 = torch.full((128, D), float("nan"), device=dev)
     o2 = torch.full((128, D), float("nan"), device=dev)
-    _evoattn.selftest_mma(D, xd, yd, zd, o0, o1, o2, torch.cuda.current_stream().cuda_stream)
+    o3 = torch.full((128, D), float("nan"), device=dev)
+    _evoattn.selftest_mma(D, xd, yd, zd, o0, o1, o2, o3, torch.cuda.current_stream().cuda_stream)
     _evoattn.device_status()
     xf, yf, zf = x.double(), y.double(), z.double()
-    refs = {"y z^T": (yf @ zf.T, o0), "x y": (xf @ yf, o1), "x^T y": (xf.T @ yf, o2)}
+    refs = {"y z^T": (yf @ zf.T, o0), "x y": (xf @ yf, o1), "x^T y": (xf.T @ yf, o2),
+            "x y (A in tensor memory)": (xf @ yf, o3)}
     for name, (ref, got) in refs.items():
         err = (ref - got.double().cpu()).abs().max().item()
         # bf16 products are exact in fp32; only the accumulation order differs
