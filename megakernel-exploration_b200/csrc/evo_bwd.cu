@@ -43,10 +43,6 @@
 #include "evo_host.cuh"
 #include "evo_tiles.cuh"
 
-#ifndef EVO_EXP
-#define EVO_EXP 0
-#endif
-
 namespace evo {
 
 constexpr int BWD_THREADS = 384;           // 3 warpgroups: 2 compute + (producer, mma, 2 idle warps)
@@ -395,7 +391,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dq_free);
-                if (!(EVO_EXP & 1) && pi * TILE + wrow0 < p.N) {     // warp-uniform
+                if (pi * TILE + wrow0 < p.N) {     // warp-uniform
                     // the slot is free once this lane-0's earlier bulk operations have read it
                     if (lane == 0) tma_wait_group_read<0>();
                     __syncwarp();
@@ -412,7 +408,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
             }
-            if (flush && !(EVO_EXP & 2)) {
+            if (flush) {
                 const int q0 = fi * TILE + wrow0;
 #pragma unroll
                 for (int rd = 0; rd < 64 / C::DBW; ++rd) {
@@ -440,7 +436,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     float v[HALF];
                     tmem_ld_f32<HALF>(lane_base + C::TMEM_DKV + (t >> 1) * 2 * DH + (t & 1) * DH + wg * HALF, v);
                     const float sc = (t & 1) ? 1.0f : p.scale;
-                    if (kvrow < p.N && !(EVO_EXP & 4)) {
+                    if (kvrow < p.N) {
                         __nv_bfloat16* out = ((t & 1) ? p.dv : p.dk) +
                             ((static_cast<size_t>(kx.bs0 + (t >> 1)) * p.N + kvrow) * p.H + kx.h) * DH + wg * HALF;
 #pragma unroll
@@ -493,6 +489,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                          : reinterpret_cast<const float*>(sb + C::ST_MASK)) + 64 * wg;
 
                 uint32_t pkp[32], pkd[32];           // P and dS of this thread's 64 columns, bf16 pairs
+                const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
+                const float2 nl2 = make_float2(nl, nl), ndl2 = make_float2(-dl, -dl);
                 tc_fence_after();
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
@@ -507,28 +505,23 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
+                        // two columns per instruction: x = S*c1 + (bias*log2e + mask*log2e) - LSE*log2e,
+                        // P = exp2(x), dS = P * (dP - delta)
                         const float4 mv = *reinterpret_cast<const float4*>(mrow + 16 * ch + q4 * 4);
-                        const float mm[4] = {mv.x, mv.y, mv.z, mv.w};
-                        float pv[4], ds[4];
+                        const float2 mm[2] = {make_float2(mv.x, mv.y), make_float2(mv.z, mv.w)};
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int c = q4 * 4 + e;                  // 0..15 within this chunk
-                            const uint32_t word = bias_pk[ch * 8 + (c >> 1)];
-                            const float bval = (c & 1) ? bf16_hi(word) : bf16_lo(word);
-                            if (EVO_EXP & 8) {
-                                pv[e] = __uint_as_float(sv[c]);
-                                ds[e] = __uint_as_float(dv[c]) + bval + mm[e] + nl + dl;
-                                continue;
-                            }
-                            const float xv = fmaf(__uint_as_float(sv[c]), p.c1, fmaf(bval, LOG2E, mm[e]));
-                            pv[e] = ex2(xv + nl);
-                            ds[e] = pv[e] * (__uint_as_float(dv[c]) - dl);
-                            acc[ch * 16 + c] += ds[e];
+                        for (int w = 0; w < 2; ++w) {
+                            const int c = q4 * 4 + 2 * w;                 // 0..14 within this chunk
+                            const float2 t2 = ffma2(bf16x2_f2(bias_pk[ch * 8 + q4 * 2 + w]), l2e2, mm[w]);
+                            const float2 x2 = fadd2(ffma2(u2f2(sv[c], sv[c + 1]), c1x2, t2), nl2);
+                            const float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
+                            const float2 ds2 = fmul2(p2, fadd2(u2f2(dv[c], dv[c + 1]), ndl2));
+                            const float2 a2 = fadd2(make_float2(acc[ch * 16 + c], acc[ch * 16 + c + 1]), ds2);
+                            acc[ch * 16 + c] = a2.x;
+                            acc[ch * 16 + c + 1] = a2.y;
+                            pkp[ch * 8 + q4 * 2 + w] = pack_bf16(p2.x, p2.y);
+                            pkd[ch * 8 + q4 * 2 + w] = pack_bf16(ds2.x, ds2.y);
                         }
-                        pkp[ch * 8 + q4 * 2 + 0] = pack_bf16(pv[0], pv[1]);
-                        pkp[ch * 8 + q4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
-                        pkd[ch * 8 + q4 * 2 + 0] = pack_bf16(ds[0], ds[1]);
-                        pkd[ch * 8 + q4 * 2 + 1] = pack_bf16(ds[2], ds[3]);
                     }
                 }
                 if (r == x.nr - 1) {

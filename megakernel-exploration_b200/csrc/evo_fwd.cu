@@ -385,24 +385,25 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     __syncwarp();
                 }
                 const uint8_t* sbias = sb + C::ST_BIAS + wg * SQ_SUB_BYTES;
+                // x = S*c1 + (bias*log2e + mask*log2e), two columns per instruction
+                const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
                 float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: ILP
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
                     const uint4 bv = *reinterpret_cast<const uint4*>(sbias + swz_off<128>(row, c8));
                     const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+                    const float4 ma = *reinterpret_cast<const float4*>(wmask + c8 * 8);
+                    const float4 mb = *reinterpret_cast<const float4*>(wmask + c8 * 8 + 4);
+                    const float2 mm[4] = {make_float2(ma.x, ma.y), make_float2(ma.z, ma.w),
+                                          make_float2(mb.x, mb.y), make_float2(mb.z, mb.w)};
 #pragma unroll
-                    for (int q4 = 0; q4 < 2; ++q4) {
-                        const float4 mv = *reinterpret_cast<const float4*>(wmask + c8 * 8 + q4 * 4);
-                        const float mm[4] = {mv.x, mv.y, mv.z, mv.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int c = c8 * 8 + q4 * 4 + e;
-                            const uint32_t word = bw[q4 * 2 + (e >> 1)];
-                            const float bval = (e & 1) ? bf16_hi(word) : bf16_lo(word);
-                            const float x = fmaf(__uint_as_float(sr[c]), p.c1, fmaf(bval, LOG2E, mm[e]));
-                            sr[c] = __float_as_uint(x);
-                            tmx[e] = fmaxf(tmx[e], x);
-                        }
+                    for (int w = 0; w < 4; ++w) {
+                        const int c = c8 * 8 + 2 * w;
+                        const float2 t2 = ffma2(bf16x2_f2(bw[w]), l2e2, mm[w]);
+                        const float2 x2 = ffma2(u2f2(sr[c], sr[c + 1]), c1x2, t2);
+                        sr[c] = __float_as_uint(x2.x);
+                        sr[c + 1] = __float_as_uint(x2.y);
+                        tmx[w] = fmax3(tmx[w], x2.x, x2.y);
                     }
                 }
                 __syncwarp();
@@ -412,14 +413,20 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const float m_new = fmaxf(m, tmax);
                 const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
                 const float alpha = ex2(m - m_safe);
-                float rs[4] = {0.f, 0.f, 0.f, 0.f};
+                // P = exp2(x - m), packed to bf16 pairs; row sum in two packed chains
+                uint32_t pk[32];
+                {
+                    const float2 nm2 = make_float2(-m_safe, -m_safe);
+                    float2 rs[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const float pv = ex2(__uint_as_float(sr[c]) - m_safe);
-                    rs[c & 3] += pv;
-                    sr[c] = __float_as_uint(pv);
+                    for (int c = 0; c < 32; ++c) {
+                        const float2 d2 = fadd2(u2f2(sr[2 * c], sr[2 * c + 1]), nm2);
+                        const float2 p2 = make_float2(ex2(d2.x), ex2(d2.y));
+                        rs[c & 1] = fadd2(rs[c & 1], p2);
+                        pk[c] = pack_bf16(p2.x, p2.y);
+                    }
+                    l = l * alpha + ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y));
                 }
-                l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
                 m = m_new;
 
                 // The P columns in tensor memory are free once the previous tile's PV MMA is
@@ -430,14 +437,19 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (!ok) break;
                     tc_fence_after();
                     const float sc = (j > 0) ? alpha : 1.0f;
+                    const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
                     for (int c = 0; c < DH / 32; ++c) {
                         uint32_t r[32];
                         tmem_ld32(lane_base + C::TMEM_PV + wg * DH + c * 32, r);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(r[i])) * sc;
+                        for (int i = 0; i < 32; i += 2) {
+                            const float2 a2 = fmul2(fadd2(make_float2(acc[c * 32 + i], acc[c * 32 + i + 1]),
+                                                          u2f2(r[i], r[i + 1])), sc2);
+                            acc[c * 32 + i] = a2.x;
+                            acc[c * 32 + i + 1] = a2.y;
+                        }
                     }
                     if (j == 0) {
                         ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
@@ -447,14 +459,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
                 // P (bf16 pairs) into this group's 32 columns of tensor memory
-                {
-                    uint32_t pk[32];
-#pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        pk[c] = pack_bf16(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1]));
-                    tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
-                    tmem_wait_st();
-                }
+                tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
+                tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[wg]);

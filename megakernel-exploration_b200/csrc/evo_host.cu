@@ -72,17 +72,6 @@ int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int 
     return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, d, row_swizzle(D));
 }
 
-int make_tmap_qkv_f32(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows) {
-    const uint64_t e = 4;
-    TmapDim d[4] = {
-        {static_cast<uint64_t>(D), 0, 32},
-        {static_cast<uint64_t>(H), D * e, 1},
-        {static_cast<uint64_t>(N), static_cast<uint64_t>(H) * D * e, static_cast<uint32_t>(rows)},
-        {static_cast<uint64_t>(BS), static_cast<uint64_t>(N) * H * D * e, 1},
-    };
-    return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, CU_TENSOR_MAP_SWIZZLE_128B);
-}
-
 int make_tmap_bias(CUtensorMap* out, const void* base, int B, int H, int N) {
     const uint64_t e = 2;
     TmapDim d[4] = {
@@ -92,17 +81,6 @@ int make_tmap_bias(CUtensorMap* out, const void* base, int B, int H, int N) {
         {static_cast<uint64_t>(B), static_cast<uint64_t>(H) * N * N * e, 1},
     };
     return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, d, CU_TENSOR_MAP_SWIZZLE_128B);
-}
-
-int make_tmap_dbias(CUtensorMap* out, const void* base, int B, int H, int N) {
-    const uint64_t e = 4;
-    TmapDim d[4] = {
-        {static_cast<uint64_t>(N), 0, 32},
-        {static_cast<uint64_t>(N), N * e, 128},
-        {static_cast<uint64_t>(H), static_cast<uint64_t>(N) * N * e, 1},
-        {static_cast<uint64_t>(B), static_cast<uint64_t>(H) * N * N * e, 1},
-    };
-    return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 static CUtensorMapSwizzle swizzle_for(int row_bytes) {

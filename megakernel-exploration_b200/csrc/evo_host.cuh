@@ -37,8 +37,6 @@ inline CUtensorMapSwizzle row_swizzle(int D) {
 // bf16 [BS][N][H][D] (contiguous) viewed as (D, H, N, BS); box = one head's
 // [rows x D] tile, swizzled by row.
 int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows);
-// fp32 [BS][N][H][D] viewed the same way; box [rows x 32 floats] (128 B, 128B swizzle).
-int make_tmap_qkv_f32(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows);
 // [BS][N][H][D] of `elem_bytes`-wide elements (2: bf16, 4: fp32) with a box of
 // [rows x box_cols]; the swizzle matches the box row (32, 64 or 128 bytes).
 int make_tmap_rows_box(CUtensorMap* out, const void* base, int elem_bytes, int BS, int N, int H, int D,
@@ -47,8 +45,6 @@ int make_tmap_rows_box(CUtensorMap* out, const void* base, int elem_bytes, int B
 int make_tmap_dbias_box(CUtensorMap* out, const void* base, int B, int H, int N, int box_cols, int rows);
 // bf16 [B][H][N][N] viewed as (N, N, H, B); box [128 rows x 64 cols], 128B swizzle.
 int make_tmap_bias(CUtensorMap* out, const void* base, int B, int H, int N);
-// fp32 [B][H][N][N] viewed as (N, N, H, B); box [128 rows x 32 cols], 128B swizzle.
-int make_tmap_dbias(CUtensorMap* out, const void* base, int B, int H, int N);
 
 int check_dims(const EvoDims* d);
 // Makes the device's primary context current on this thread (see evo_host.cu).
