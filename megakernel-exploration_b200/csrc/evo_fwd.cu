@@ -15,9 +15,12 @@
 //                       [128 x 128] bf16 pair-bias tile and the mask row into a
 //                       ring of stages
 //   warp 9  (mma)       tcgen05.mma, issued in whatever order operands become
-//                       ready: S = Q K^T into tensor memory and, per softmax
-//                       group g, PV_g = P_g V[64g:64g+64, :] with P_g read from
-//                       tensor memory
+//                       ready, separately for the two softmax groups g:
+//                       S_g = Q K[64g:64g+64, :]^T into tensor memory and
+//                       PV_g = P_g V[64g:64g+64, :] with P_g read from tensor
+//                       memory.  The groups share no barrier inside an item, so
+//                       they drift apart and one group's exp2 phase overlaps the
+//                       other's FMA phase
 //   warps 0-3, 4-7      two softmax groups.  Group g owns kv columns 64g..64g+63
 //                       of every tile and runs its own online softmax over them
 //                       (thread = one q row): x = S*scale*log2e + bias*log2e +
@@ -53,7 +56,7 @@ struct FwdCfg {
     static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
     static constexpr uint32_t OFF_WMASK = OFF_XCH + 128 * XCH_PITCH;       // 8 warps x 64 floats
     static constexpr uint32_t OFF_BARS = OFF_WMASK + 8 * 256;
-    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 2 + 2 + 2 + 3;
+    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 4 + 2 + 2 + 3;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
@@ -91,9 +94,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* q_empty = bars + 2;            // [2]
     uint64_t* kv_full = bars + 4;            // [ST]
     uint64_t* kv_empty = kv_full + ST;       // [ST]
-    uint64_t* s_full = kv_empty + ST;        // [1]
-    uint64_t* s_free = s_full + 1;           // [1]
-    uint64_t* p_ready = s_free + 1;          // [2]
+    uint64_t* s_full = kv_empty + ST;        // [2] per softmax group
+    uint64_t* s_free = s_full + 2;           // [2]
+    uint64_t* p_ready = s_free + 2;          // [2]
     uint64_t* pv_full = p_ready + 2;         // [2]
     uint64_t* xch_full = pv_full + 2;        // group 1 has written its partial result
     uint64_t* xch_empty = xch_full + 1;      // group 0 has read it
@@ -111,9 +114,12 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
         for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 9); }
-        mbar_init(s_full, 1);
-        mbar_init(s_free, 8);
-        for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_free[i], 4);
+            mbar_init(&p_ready[i], 4);
+            mbar_init(&pv_full[i], 1);
+        }
         mbar_init(xch_full, 4);
         mbar_init(xch_empty, 4);
         mbar_init(g0_bar, 4);
@@ -188,39 +194,42 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // its loads and the S accumulator read out) or PV_g of a tile whose P_g
             // is in tensor memory.  Nothing here blocks on one barrier while
             // another piece of work could go.
-            constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t IDESC_S = make_idesc_bf16(128, 64, 0, 0);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, DH, 0, 1);
             const uint32_t aQ = smem_u32(smem + C::OFF_Q), aSt = smem_u32(smem + C::OFF_STAGE);
             const int total_tiles = n_items * NT;
-            int s_next = 0;
-            int pv_next[2] = {0, 0};
+            int s_next[2] = {0, 0};          // per group: next tile whose S_g is to be issued
+            int pv_next[2] = {0, 0};         // per group: next tile whose PV_g is to be issued
             uint32_t idle = 0;
             uint64_t idle_t0 = 0;
             while (pv_next[0] < total_tiles || pv_next[1] < total_tiles) {
                 bool progress = false;
-                if (s_next < total_tiles) {
-                    const int g = s_next;
-                    const int it = g / NT, j = g - it * NT;
-                    const int qb = it & 1, st = g % ST;
-                    const bool rdy = (j != 0 || mbar_test(&q_full[qb], (it >> 1) & 1)) &&
-                                     mbar_test(&kv_full[st], (g / ST) & 1) &&
-                                     (g == 0 || mbar_test(s_free, (g - 1) & 1));
-                    if (rdy) {
-                        tc_fence_after();
-#pragma unroll
-                        for (int kb = 0; kb < RT::KBLOCKS; ++kb)
-                            umma_ss(tmem + C::TMEM_S, RT::kmajor(aQ + qb * C::ROWT, kb),
-                                    RT::kmajor(aSt + st * C::STAGE_STRIDE + C::ST_K, kb), IDESC_S, kb > 0);
-                        umma_commit(s_full);
-                        if (j == NT - 1) umma_commit(&q_empty[qb]);
-                        ++s_next;
-                        progress = true;
-                    }
-                }
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
+                    if (s_next[w] < total_tiles) {
+                        const int g = s_next[w];
+                        const int it = g / NT, j = g - it * NT;
+                        const int qb = it & 1, st = g % ST;
+                        const bool rdy = (j != 0 || mbar_test(&q_full[qb], (it >> 1) & 1)) &&
+                                         mbar_test(&kv_full[st], (g / ST) & 1) &&
+                                         (g == 0 || mbar_test(&s_free[w], (g - 1) & 1));
+                        if (rdy) {
+                            tc_fence_after();
+                            // K rows 64w..64w+63 of the tile: 64 rows further into the K-major tile
+                            const uint32_t kt = aSt + st * C::STAGE_STRIDE + C::ST_K + w * 64 * RT::ROW_BYTES;
+#pragma unroll
+                            for (int kb = 0; kb < RT::KBLOCKS; ++kb)
+                                umma_ss(tmem + C::TMEM_S + 64 * w, RT::kmajor(aQ + qb * C::ROWT, kb),
+                                        RT::kmajor(kt, kb), IDESC_S, kb > 0);
+                            umma_commit(&s_full[w]);
+                            ++s_next[w];
+                            // Q is free once both groups' S of the item's last tile are issued
+                            if (j == NT - 1 && s_next[w ^ 1] > g) umma_commit(&q_empty[qb]);
+                            progress = true;
+                        }
+                    }
                     const int g = pv_next[w];
-                    if (g < s_next && mbar_test(&p_ready[w], g & 1)) {
+                    if (g < s_next[w] && mbar_test(&p_ready[w], g & 1)) {
                         const int st = g % ST;
                         tc_fence_after();
 #pragma unroll
@@ -356,7 +365,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int j = 0; j < NT && ok; ++j, ++g) {
                 const int st = g % ST;
                 const uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
-                ok = warp_all(mbar_wait(s_full, g & 1, wc, 0x31));
+                ok = warp_all(mbar_wait(&s_full[wg], g & 1, wc, 0x31));
                 if (!ok) break;
                 EVO_TS(t_tile);
                 tc_fence_after();
@@ -370,7 +379,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(s_free);
+                if (lane == 0) mbar_arrive(&s_free[wg]);
 
                 ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x32));
                 if (!ok) break;
