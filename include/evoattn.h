@@ -81,6 +81,32 @@ int evo_bwd(const EvoDims* dims, const void* q, const void* k, const void* v,
             const float* lse, const void* d_o, void* dq, void* dk, void* dv, float* dbias,
             void* workspace, size_t workspace_bytes, float scale, void* stream);
 
+/* Backward for callers that may not allocate device memory -- no counterpart in
+ * the reference.  Same computation and arguments as evo_bwd, minus the
+ * workspace: the scratch is a fixed array inside the library
+ * (evo_bwd_static_scratch_capacity() bytes, 32 MiB by default), so this call
+ * makes no cudaMalloc / cudaFree and uses no allocating library routine.  It is
+ * meant for hosts where device memory is handed out up front and nothing may
+ * be allocated afterwards: an inference or training server whose memory pool
+ * already owns the whole GPU, a plugin loaded into such a process, or code that
+ * runs where an allocation would stall or fail (for example inside a section
+ * the host has frozen against allocator calls).
+ *   - Problems whose evo_bwd_workspace_bytes(dims) exceeds the capacity are
+ *     refused with EVO_ERR_TOO_LARGE; nothing is launched.
+ *   - The first call on each device looks up the array's device address (once,
+ *     with that device current).  Make that first call before any stream
+ *     capture begins on the device.
+ *   - Every call on a device shares the one array and leaves its last contents
+ *     there; the call itself re-zeroes the part that must start at zero.  Two
+ *     calls that overlap on the same GPU (different streams, or different
+ *     threads) race on the scratch: serialise them.
+ *   - Every GPU that loads the library holds the array until the process exits. */
+size_t evo_bwd_static_scratch_capacity(void);
+int evo_bwd_static_scratch(const EvoDims* dims, const void* q, const void* k, const void* v,
+                           const void* pair_bias, const void* res_mask, const void* o,
+                           const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk,
+                           void* dv, float* dbias, float scale, void* stream);
+
 /* Reads (and clears) the device status word that kernels set when a bounded
  * wait gives up.  Synchronises the device.  Returns EVO_OK, EVO_ERR_DEVICE_WAIT
  * (raw word in *raw if non-NULL) or EVO_ERR_CUDA.  The reference has no

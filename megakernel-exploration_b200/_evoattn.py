@@ -35,6 +35,8 @@ SYMBOLS = {
     "evo_fwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 8 + [C.c_float, C.c_void_p]),
     "evo_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
     "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 14 + [C.c_size_t, C.c_float, C.c_void_p]),
+    "evo_bwd_static_scratch_capacity": (C.c_size_t, []),
+    "evo_bwd_static_scratch": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 13 + [C.c_float, C.c_void_p]),
     "evo_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
     "evo_selftest_mma": (C.c_int, [C.c_int] + [C.c_void_p] * 8),
     "evo_profile_enable": (C.c_int, [C.c_int]),
@@ -102,6 +104,15 @@ def bwd(dims: EvoDims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, db
                         _ptr(dbias), _ptr(workspace),
                         workspace.numel() * workspace.element_size(), float(scale), stream),
           "evo_bwd")
+
+
+def bwd_static_scratch(dims: EvoDims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+                       scale: float, stream: int) -> None:
+    """evo_bwd with the library's built-in scratch array instead of a caller workspace."""
+    check(lib().evo_bwd_static_scratch(C.byref(dims), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
+                                       _ptr(o), _ptr(o_resid), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk),
+                                       _ptr(dv), _ptr(dbias), float(scale), stream),
+          "evo_bwd_static_scratch")
 
 
 def device_status() -> int:

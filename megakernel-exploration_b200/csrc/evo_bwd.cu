@@ -43,6 +43,8 @@
 #include "evo_host.cuh"
 #include "evo_tiles.cuh"
 
+#include <mutex>
+
 namespace evo {
 
 constexpr int BWD_THREADS = 384;           // 3 warpgroups: 2 compute + (producer, mma, 2 idle warps)
@@ -730,6 +732,53 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
 }
 
 }  // namespace evo
+
+// ---------------------------------------------------------------------------
+// Backward with built-in scratch.  The workspace lives in a file-scope device
+// array, so the call allocates nothing.  In host code the array's name is only a
+// handle; its device address comes from cudaGetSymbolAddress, looked up once per
+// device (with that device current) and kept.
+// ---------------------------------------------------------------------------
+#ifndef EVO_STATIC_SCRATCH_BYTES
+#define EVO_STATIC_SCRATCH_BYTES (32u << 20)
+#endif
+static __device__ __align__(256) unsigned char g_bwd_scratch[EVO_STATIC_SCRATCH_BYTES];
+
+namespace evo {
+static int static_scratch(uint8_t** out) {
+    static std::mutex mu;
+    static uint8_t* cache[64] = {nullptr};
+    int dev = 0;
+    int rc = cuda_err(cudaGetDevice(&dev));
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return EVO_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev]) {
+        void* ptr = nullptr;
+        rc = cuda_err(cudaGetSymbolAddress(&ptr, g_bwd_scratch));
+        if (rc) return rc;
+        cache[dev] = static_cast<uint8_t*>(ptr);
+    }
+    *out = cache[dev];
+    return EVO_OK;
+}
+}  // namespace evo
+
+extern "C" size_t evo_bwd_static_scratch_capacity(void) { return EVO_STATIC_SCRATCH_BYTES; }
+
+extern "C" int evo_bwd_static_scratch(const EvoDims* dims, const void* q, const void* k, const void* v,
+                                      const void* pair_bias, const void* res_mask, const void* o,
+                                      const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk,
+                                      void* dv, float* dbias, float scale, void* stream) {
+    int rc = evo::check_dims(dims);
+    if (rc) return rc;
+    if (evo::bwd_workspace(dims).total > EVO_STATIC_SCRATCH_BYTES) return EVO_ERR_TOO_LARGE;
+    if ((rc = evo::ensure_context())) return rc;
+    uint8_t* scratch = nullptr;
+    if ((rc = evo::static_scratch(&scratch))) return rc;
+    return evo_bwd(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, scratch,
+                   EVO_STATIC_SCRATCH_BYTES, scale, stream);
+}
 
 extern "C" size_t evo_bwd_workspace_bytes(const EvoDims* dims) {
     if (evo::check_dims(dims) != EVO_OK) return 0;
