@@ -113,13 +113,14 @@ int evo_bwd_static_scratch(const EvoDims* dims, const void* q, const void* k, co
  * counterpart: its kernels wait without bound. */
 int evo_device_status(uint32_t* raw);
 
-/* Optional timing of the two main kernels with CUDA events recorded on the
+/* Optional timing of the three main kernels with CUDA events recorded on the
  * caller's stream around each launch (no counterpart in the reference, which
  * times whole calls from Python, evo_h100/benchmark.py:76-124).
  * evo_profile_enable(1) starts recording (at most 4096 launches per kernel are
  * kept), evo_profile_enable(0) stops.  evo_profile_read waits for the recorded
  * events, returns the summed milliseconds and the launch count of
- * kernel 0 (forward) or 1 (backward main kernel), and clears that record. */
+ * kernel 0 (forward), 1 (backward dQ/dK/dV kernel) or 2 (backward dBias kernel),
+ * and clears that record. */
 int evo_profile_enable(int on);
 int evo_profile_read(int kernel, float* total_ms, int* launches);
 

@@ -130,7 +130,7 @@ def profile_enable(on: bool) -> None:
 
 
 def profile_read(kernel: int):
-    """(total milliseconds, launches) of kernel 0 (forward) / 1 (backward main)."""
+    """(total milliseconds, launches) of kernel 0 (forward) / 1 (backward dQ,dK,dV) / 2 (backward dBias)."""
     ms, n = C.c_float(0.0), C.c_int(0)
     check(lib().evo_profile_read(kernel, C.byref(ms), C.byref(n)), "evo_profile_read")
     return ms.value, n.value

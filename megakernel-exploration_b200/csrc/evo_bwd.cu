@@ -8,22 +8,22 @@
 //   dV = P^T dO,  dK = scale * dS^T q,  dQ = scale * dS k
 //   dBias[b,h,q,kv] = sum over s of dS        (unscaled, tk_evoattention.cu:824-833)
 //
-// Three launches on one stream:
-//   1. bwd_prep_kernel   delta, -LSE*log2e and mask*log2e rows, padded to whole
-//                        tiles so the main kernel needs no edge predicates
-//   2. evo_bwd_kernel    the fused backward (below)
-//   3. cvt_dq_kernel     fp32 dQ accumulator -> bf16 dQ in the caller layout
+// Four launches on one stream:
+//   1. bwd_prep_kernel    delta, -LSE*log2e and mask*log2e rows, padded to whole
+//                         tiles so the main kernels need no edge predicates
+//   2. evo_dbias_kernel   dBias (evo_dbias.cu): one CTA per pair-bias tile keeps its
+//                         sum over the S rows in registers, no reduction traffic
+//   3. evo_bwd_kernel     dQ, dK, dV (below)
+//   4. cvt_dq_kernel      fp32 dQ accumulator -> bf16 dQ in the caller layout
 //
 // evo_bwd_kernel: one persistent CTA per SM walks items (chunk of RC consecutive
 // S rows, head h, kv tile j of 128 residues); per item it walks steps
-// (q tile i, row r of the chunk), r innermost.  dK/dV of every row of the chunk
-// stay in tensor memory for the whole item; dS of the RC rows that share one
-// pair-bias tile is summed in registers before it is added to dBias, where the
-// reference issues one scalar atomic per element per row
-// (tk_evoattention.cu:583-611).
+// (q tile i, row r of the chunk), r innermost, so that one pair-bias tile serves
+// RC steps.  dK/dV of every row of the chunk stay in tensor memory for the item.
 //
 //   warp 8 (producer)  TMA per step: Q, dO tiles and the -LSE / delta rows; K, V
-//                      tiles and the mask row per step (D=32) or per item (D=64)
+//                      tiles and the mask row per step (D=32) or per item (D=64);
+//                      the pair-bias tile per q tile
 //   warp 9 (mma)       tcgen05.mma, issued in whatever order operands become
 //                      ready: S = Q K^T and dP = dO V^T of the next step, or
 //                      dV += P^T dO, dK += dS^T Q, dQ = dS K of the current one
@@ -31,16 +31,15 @@
 //                      (thread = one q row).  Per step: P and dS from S and dP,
 //                      kept packed in registers until the previous step's
 //                      dV/dK/dQ MMAs have finished reading the P/dS tiles, then
-//                      written to shared memory as MMA operands.  The pair bias
-//                      of a thread's row and 64 columns is loaded straight from
-//                      global memory into registers, one q tile ahead.  Afterwards,
-//                      off the critical path and warp-locally (no barrier beyond
-//                      the warp): each warp stages its 32 rows of the previous
-//                      step's dQ and, after the last row of a chunk, of the dBias
-//                      sums in its own shared-memory slots and issues TMA
-//                      reduce-adds (fp32) for them; after an item, dK/dV go out as
+//                      written to shared memory as MMA operands.  Afterwards, off
+//                      the critical path and warp-locally (no barrier beyond the
+//                      warp): each warp stages its 32 rows of the previous step's
+//                      dQ in its own shared-memory slot and issues a TMA
+//                      reduce-add (fp32) for them; after an item, dK/dV go out as
 //                      bf16 stores.
+#include "evo_dbias.cuh"
 #include "evo_host.cuh"
+#include "evo_ptx.cuh"
 #include "evo_tiles.cuh"
 
 #include <mutex>
@@ -51,6 +50,8 @@ constexpr int BWD_THREADS = 384;           // 3 warpgroups: 2 compute + (produce
 constexpr uint32_t BWD_TMEM_COLS = 512;
 constexpr int BWD_REGS_COMPUTE = 224;
 constexpr int BWD_REGS_OTHER = 56;
+// the CTA's register pool is the launch count (cap for 384 threads: 168) times the threads
+static_assert(BWD_REGS_COMPUTE * 256 + BWD_REGS_OTHER * 128 <= 168 * BWD_THREADS, "register pool");
 
 template <int DH>
 struct BwdCfg {
@@ -72,16 +73,14 @@ struct BwdCfg {
     static constexpr uint32_t KV_TX = 2 * ROWT + 512;                       // per row of the chunk
     static constexpr uint32_t OFF_STAGE = 0;
     static constexpr uint32_t OFF_KV = OFF_STAGE + QS * STAGE_STRIDE;
-    static constexpr uint32_t OFF_P = OFF_KV + KV_BYTES;
+    static constexpr uint32_t OFF_BIAS = OFF_KV + KV_BYTES;
+    static constexpr uint32_t OFF_P = OFF_BIAS + SQ_BYTES;
     static constexpr uint32_t OFF_DS = OFF_P + SQ_BYTES;
-    // per warp: dQ slot [32 rows][HALF fp32], then dBias slot [32 rows][DBW fp32]
-    static constexpr int DBW = (DH == 32) ? 32 : 16;   // dBias columns per reduce
-    static constexpr uint32_t WQ_BYTES = 32 * HALF * 4;
-    static constexpr uint32_t WB_BYTES = 32 * DBW * 4;
-    static constexpr uint32_t WSTG_STRIDE = WQ_BYTES + WB_BYTES;
+    // per warp: dQ slot [32 rows][16 fp32]
+    static constexpr uint32_t WQ_BYTES = 32 * 16 * 4;
     static constexpr uint32_t OFF_WSTG = OFF_DS + SQ_BYTES;
-    static constexpr uint32_t OFF_BARS = OFF_WSTG + 8 * WSTG_STRIDE;
-    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 6;
+    static constexpr uint32_t OFF_BARS = OFF_WSTG + 8 * WQ_BYTES;
+    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 6;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
@@ -90,7 +89,7 @@ struct BwdCfg {
     static constexpr uint32_t TMEM_DKV = 256 + DH;                          // + r*2*DH (dK), + DH (dV)
     static_assert(TMEM_DKV + RC * 2 * DH <= BWD_TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
-    static_assert(OFF_KV % 1024 == 0 && OFF_P % 1024 == 0 && WQ_BYTES % 1024 == 0, "tile alignment");
+    static_assert(OFF_KV % 1024 == 0 && OFF_BIAS % 1024 == 0 && WQ_BYTES % 1024 == 0, "tile alignment");
 };
 
 struct BwdParams {
@@ -104,7 +103,6 @@ struct BwdParams {
     const float* nlse2;   // [B*S][H][NTP]  -LSE*log2e, -inf in the padding
     const float* delta;   // [B*S][H][NTP]  0 in the padding
     const float* maskl2;  // [B*S][NTP]     mask*log2e, -inf in the padding
-    const __nv_bfloat16* bias;   // [B][H][N][N]
     __nv_bfloat16* dk;    // [B*S][N][H][D]
     __nv_bfloat16* dv;
     unsigned int* status;
@@ -118,7 +116,7 @@ template <int DH>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-               const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dbias,
+               const __grid_constant__ CUtensorMap tm_bias, const __grid_constant__ CUtensorMap tm_dq,
                const BwdParams p) {
     using C = BwdCfg<DH>;
     using RT = RowTile<DH>;
@@ -132,7 +130,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* st_empty = st_full + QS;         // [QS]
     uint64_t* kv_full = st_empty + QS;         // resident K/V only
     uint64_t* kv_empty = kv_full + 1;
-    uint64_t* sdp_full = kv_empty + 1;
+    uint64_t* bias_full = kv_empty + 1;
+    uint64_t* bias_empty = bias_full + 1;
+    uint64_t* sdp_full = bias_empty + 1;
     uint64_t* sdp_free = sdp_full + 1;
     uint64_t* pds_ready = sdp_free + 1;
     uint64_t* dq_full = pds_ready + 1;
@@ -152,6 +152,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 9); }
         mbar_init(kv_full, 1);
         mbar_init(kv_empty, 9);
+        mbar_init(bias_full, 1);
+        mbar_init(bias_empty, 8);
         mbar_init(sdp_full, 1);
         mbar_init(sdp_free, 8);
         mbar_init(pds_ready, 8);
@@ -167,8 +169,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     if (warp == 8 && lane == 0) {
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
-        prefetch_tmap(&tm_dq); prefetch_tmap(&tm_dbias);
+        prefetch_tmap(&tm_bias); prefetch_tmap(&tm_dq);
     }
+    EVO_TRACE_INIT();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -200,7 +203,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (warp == 8 && lane == 0) {
             // ------------------------------ producer ------------------------------
             bool ok = true;
-            int gs = 0;
+            int gs = 0, gb = 0;
             for (int it = 0; it < n_items && ok; ++it) {
                 const BwdItem x = decode(it);
                 const int nsteps = NT * x.nr;
@@ -219,6 +222,15 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 for (int n = 0; n < nsteps && ok; ++n, ++gs) {
                     const int i = n / x.nr, r = n - i * x.nr;
                     const int st = gs % QS;
+                    if (r == 0) {
+                        if (gb > 0) ok = mbar_wait(bias_empty, (gb - 1) & 1, wc, 0x41);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(bias_full, SQ_BYTES);
+                        tma_load_4d(smem + C::OFF_BIAS, &tm_bias, bias_full, x.j * TILE, i * TILE, x.h, x.b);
+                        tma_load_4d(smem + C::OFF_BIAS + SQ_SUB_BYTES, &tm_bias, bias_full, x.j * TILE + 64,
+                                    i * TILE, x.h, x.b);
+                        ++gb;
+                    }
                     if (gs >= QS) ok = mbar_wait(&st_empty[st], ((gs / QS) - 1) & 1, wc, 0x42);
                     if (!ok) break;
                     const int bs = x.bs0 + r;
@@ -240,6 +252,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // Drain: the most recent loads have landed before the CTA exits.
             for (int k = (gs > QS ? gs - QS : 0); k < gs; ++k)
                 (void)mbar_wait(&st_full[k % QS], (k / QS) & 1, wc, 0x43);
+            if (gb > 0) (void)mbar_wait(bias_full, (gb - 1) & 1, wc, 0x44);
             if (KVR && n_items > 0) (void)mbar_wait(kv_full, (n_items - 1) & 1, wc, 0x45);
         } else if (warp == 9 && lane == 0) {
             // ------------------------------ mma issuer ------------------------------
@@ -357,34 +370,16 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(wrow0) << 16);
         uint8_t* sP = smem + C::OFF_P;
         uint8_t* sDS = smem + C::OFF_DS;
-        uint8_t* wq = smem + C::OFF_WSTG + warp * C::WSTG_STRIDE;   // this warp's dQ slot
-        uint8_t* wb = wq + C::WQ_BYTES;                              // this warp's dBias slot
+        uint8_t* wq = smem + C::OFF_WSTG + warp * C::WQ_BYTES;      // this warp's dQ slot
         bool ok = true;
-        int gs = 0;
+        int gs = 0, gb = 0;
 
-        // This thread's 64 pair-bias values (row `row` of q tile i, columns of kv tile x.j
-        // owned by this group), straight from global memory; zeros outside the matrix.
-        auto load_bias = [&](uint32_t (&pk)[32], const BwdItem& x, int i) {
-            const int q = i * TILE + row;
-            const int c0 = x.j * TILE + wg * 64;
-            const __nv_bfloat16* src = p.bias + ((static_cast<size_t>(x.b) * p.H + x.h) * p.N + q) * p.N + c0;
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (q < p.N && c0 + c8 * 8 + 8 <= p.N) v = __ldg(reinterpret_cast<const uint4*>(src + c8 * 8));
-                pk[c8 * 4 + 0] = v.x; pk[c8 * 4 + 1] = v.y; pk[c8 * 4 + 2] = v.z; pk[c8 * 4 + 3] = v.w;
-            }
-        };
-
-        float acc[64];                       // dBias partial sums of this thread's 64 columns
         uint32_t bias_pk[32];                // this thread's 64 bias values (bf16 pairs)
 
         // Work left over from earlier steps, done after this step's P/dS are out:
-        //   drain  dQ of step (px, pi, pr) from tensor memory -> fp32 reductions
-        //   flush  dBias sums of (fx, fi) -> fp32 reductions
+        //   drain  dQ of step (px, pi, pr) from tensor memory -> fp32 reduce-add
         //   dkv    dK/dV of item kx -> bf16 stores
-        auto post_step = [&](bool drain, const BwdItem& px, int pi, int pr, bool flush, const BwdItem& fx,
-                             int fi, bool dkv, const BwdItem& kx) {
+        auto post_step = [&](bool drain, const BwdItem& px, int pi, int pr, bool dkv, const BwdItem& kx) {
             EVO_TS(t_post);
             if (drain) {
                 float dqv[HALF];
@@ -394,40 +389,22 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dq_free);
                 if (pi * TILE + wrow0 < p.N) {     // warp-uniform
-                    // the slot is free once this lane-0's earlier bulk operations have read it
-                    if (lane == 0) tma_wait_group_read<0>();
-                    __syncwarp();
 #pragma unroll
-                    for (int cc = 0; cc < HALF / 4; ++cc)
-                        *reinterpret_cast<float4*>(wq + swz_off<HALF * 4>(lane, cc)) =
-                            make_float4(dqv[cc * 4 + 0] * p.scale, dqv[cc * 4 + 1] * p.scale,
-                                        dqv[cc * 4 + 2] * p.scale, dqv[cc * 4 + 3] * p.scale);
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_reduce_add_4d(&tm_dq, wq, wg * HALF, px.h, pi * TILE + wrow0, px.bs0 + pr);
-                        tma_commit_group();
-                    }
-                }
-            }
-            if (flush) {
-                const int q0 = fi * TILE + wrow0;
+                    for (int rd = 0; rd < HALF / 16; ++rd) {
+                        // the slot is free once this lane-0's earlier bulk operations have read it
+                        if (lane == 0) tma_wait_group_read<0>();
+                        __syncwarp();
 #pragma unroll
-                for (int rd = 0; rd < 64 / C::DBW; ++rd) {
-                    const int col = fx.j * TILE + wg * 64 + rd * C::DBW;
-                    if (q0 >= p.N || col >= p.N) break;            // warp-uniform
-                    if (lane == 0) tma_wait_group_read<0>();
-                    __syncwarp();
-#pragma unroll
-                    for (int cc = 0; cc < C::DBW / 4; ++cc)
-                        *reinterpret_cast<float4*>(wb + swz_off<C::DBW * 4>(lane, cc)) =
-                            make_float4(acc[rd * C::DBW + cc * 4 + 0], acc[rd * C::DBW + cc * 4 + 1],
-                                        acc[rd * C::DBW + cc * 4 + 2], acc[rd * C::DBW + cc * 4 + 3]);
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_reduce_add_4d(&tm_dbias, wb, col, q0, fx.h, fx.b);
-                        tma_commit_group();
+                        for (int cc = 0; cc < 4; ++cc)
+                            *reinterpret_cast<float4*>(wq + swz_off<64>(lane, cc)) =
+                                make_float4(dqv[rd * 16 + cc * 4 + 0] * p.scale, dqv[rd * 16 + cc * 4 + 1] * p.scale,
+                                            dqv[rd * 16 + cc * 4 + 2] * p.scale, dqv[rd * 16 + cc * 4 + 3] * p.scale);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_reduce_add_4d(&tm_dq, wq, wg * HALF + rd * 16, px.h, pi * TILE + wrow0, px.bs0 + pr);
+                            tma_commit_group();
+                        }
                     }
                 }
             }
@@ -462,7 +439,6 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool have_prev = false, prev_item_end = false;
         BwdItem prev_x{};                     // item of the previous step
         int prev_i = 0, prev_r = 0;
-        if (n_items > 0) load_bias(bias_pk, decode(0), 0);
 
         for (int it = 0; it < n_items && ok; ++it) {
             const BwdItem x = decode(it);
@@ -479,8 +455,18 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ok) break;
                 EVO_TS(t_cmp);
                 if (r == 0) {
+                    ok = warp_all(mbar_wait(bias_full, gb & 1, wc, 0x64));
+                    if (!ok) break;
+                    const uint8_t* sbias = smem + C::OFF_BIAS + wg * SQ_SUB_BYTES;
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) acc[c] = 0.f;
+                    for (int c8 = 0; c8 < 8; ++c8) {
+                        const uint4 bv = *reinterpret_cast<const uint4*>(sbias + swz_off<128>(row, c8));
+                        bias_pk[c8 * 4 + 0] = bv.x; bias_pk[c8 * 4 + 1] = bv.y;
+                        bias_pk[c8 * 4 + 2] = bv.z; bias_pk[c8 * 4 + 3] = bv.w;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bias_empty);
+                    ++gb;
                 }
                 ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x65));
                 if (!ok) break;
@@ -518,19 +504,10 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             const float2 x2 = fadd2(ffma2(u2f2(sv[c], sv[c + 1]), c1x2, t2), nl2);
                             const float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
                             const float2 ds2 = fmul2(p2, fadd2(u2f2(dv[c], dv[c + 1]), ndl2));
-                            const float2 a2 = fadd2(make_float2(acc[ch * 16 + c], acc[ch * 16 + c + 1]), ds2);
-                            acc[ch * 16 + c] = a2.x;
-                            acc[ch * 16 + c + 1] = a2.y;
                             pkp[ch * 8 + q4 * 2 + w] = pack_bf16(p2.x, p2.y);
                             pkd[ch * 8 + q4 * 2 + w] = pack_bf16(ds2.x, ds2.y);
                         }
                     }
-                }
-                if (r == x.nr - 1) {
-                    // bias of the next q tile (or of the next item's first one): the values of
-                    // this q tile are dead now; the loads land while the rest of the step runs
-                    if (n + 1 < nsteps) load_bias(bias_pk, x, i + 1);
-                    else if (it + 1 < n_items) load_bias(bias_pk, decode(it + 1), 0);
                 }
                 __syncwarp();
                 if (lane == 0) {
@@ -556,7 +533,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pds_ready);
 
-                post_step(have_prev, prev_x, prev_i, prev_r, r == x.nr - 1, x, i, have_prev && prev_item_end, prev_x);
+                post_step(have_prev, prev_x, prev_i, prev_r, have_prev && prev_item_end, prev_x);
                 have_prev = true;
                 prev_x = x; prev_i = i; prev_r = r;
                 prev_item_end = (n == nsteps - 1);
@@ -565,7 +542,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (ok && have_prev) {
             // the very last step: its dQ, and the last item's dK/dV
             ok = warp_all(mbar_wait(dq_full, (gs - 1) & 1, wc, 0x66));
-            if (ok) post_step(true, prev_x, prev_i, prev_r, false, prev_x, 0, true, prev_x);
+            if (ok) post_step(true, prev_x, prev_i, prev_r, true, prev_x);
         }
         if (lane == 0) tma_wait_group<0>();
     }
@@ -573,6 +550,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tid == 0) EVO_TE(t_kernel, p.status, 0x7f);
     tc_fence_before();
     __syncthreads();
+    EVO_TRACE_FLUSH(p.status);
     if (warp == 9) tmem_dealloc(tmem, BWD_TMEM_COLS);
 }
 
@@ -680,14 +658,14 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     float* maskl2 = reinterpret_cast<float*>(ws + w.off_maskl2);
     float* dq_acc = reinterpret_cast<float*>(ws + w.off_dq);
 
-    CUtensorMap tq, tk, tv, tdo, tdq, tdb;
+    CUtensorMap tq, tk, tv, tdo, tb, tdq;
     int rc;
     if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, C::HALF, 32))) return rc;
-    if ((rc = make_tmap_dbias_box(&tdb, dbias, d->B, d->H, d->N, C::DBW, 32))) return rc;
+    if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
+    if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 16, 32))) return rc;
 
     BwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
@@ -698,7 +676,6 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     p.scale = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH));
     p.c1 = p.scale * LOG2E;
     p.nlse2 = nlse2; p.delta = delta; p.maskl2 = maskl2;
-    p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
@@ -718,12 +695,14 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
         maskl2, BS, d->N, d->H, p.NTP);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 
+    if ((rc = launch_dbias(d, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st))) return rc;
+
     if ((rc = cuda_err(cudaFuncSetAttribute(evo_bwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(C::SMEM_BYTES)))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
     prof_begin(1, st);
-    evo_bwd_kernel<DH><<<grid, BWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, tdb, p);
+    evo_bwd_kernel<DH><<<grid, BWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tb, tdq, p);
     prof_end(1, st);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 

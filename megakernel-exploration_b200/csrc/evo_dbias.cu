@@ -1,0 +1,369 @@
+// Pair-bias gradient for sm_100a.
+//
+//   dBias[b,h,i,j] = sum_s dS[b,s,h,i,j],   dS = P o (dP - delta),
+//   P = exp(scale * Q K^T + bias + mask - LSE),   dP = dO V^T
+//
+// The reference accumulates this sum with fp32 atomics from inside its backward
+// kernel (evo_h100/tk_evoattention.cu:806-813 in bwd_attend_ker).  Here the sum
+// is turned inside out: a CTA owns one [128 x 128] tile of the pair bias for a
+// slice of the S rows and keeps the running sum in registers, so the only
+// traffic of the reduction is one write (or one vector atomic per slice) of the
+// finished tile.  S and dP are recomputed for that (the dQ/dK/dV kernel computes
+// them too); the recompute costs two small MMAs per step, and the elementwise
+// work runs without the shared-memory round trips the dQ/dK/dV kernel needs
+// for its operands.
+//
+//   warp NCW   (producer)  TMA per step (one S row): Q, dO tiles of q tile i,
+//                          K, V tiles of kv tile j, the -LSE / delta rows of i and
+//                          the mask row of j
+//   warp NCW+1 (mma)       S = Q K^T and dP = dO V^T into one of two tensor
+//                          memory buffers, so the MMAs of step n+1 overlap the
+//                          elementwise work of step n
+//   warps 0..NCW-1         NG compute groups of four warps; group g owns kv
+//                          columns g*CW .. g*CW+CW-1 of the tile, thread = q row.
+//                          Bias (bf16 pairs) and the running sum stay in
+//                          registers for the whole item.
+#include "evo_dbias.cuh"
+#include "evo_ptx.cuh"
+#include "evo_tiles.cuh"
+
+namespace evo {
+
+template <int DH, int NG>
+struct DbCfg {
+    static constexpr int CW = TILE / NG;                  // kv columns per thread
+    static constexpr int NCW = NG * 4;                    // compute warps
+    static constexpr int THREADS = (NCW + 4) * 32;        // + one warpgroup: producer, mma, two idle warps
+    // setmaxnreg budgets.  The CTA's register pool is what it was launched with
+    // (the per-thread cap ptxas derives from the launch bound, times THREADS); an
+    // increase blocks until the pool has room, for ever if it never can.
+    static constexpr int REGS_LAUNCH = (65536 / THREADS) & ~7;
+    static constexpr int REGS_COMPUTE = (NG == 2) ? 224 : 112;
+    static constexpr int REGS_OTHER = (NG == 2) ? 56 : 32;
+    static_assert(REGS_COMPUTE * NCW * 32 + REGS_OTHER * 128 <= REGS_LAUNCH * THREADS, "register pool");
+    static constexpr int QS = (DH == 32) ? 6 : 3;         // load stages
+    static constexpr uint32_t ROWT = RowTile<DH>::BYTES;
+    static constexpr uint32_t ST_Q = 0, ST_DO = ROWT, ST_K = 2 * ROWT, ST_V = 3 * ROWT;
+    static constexpr uint32_t ST_ROWV = 4 * ROWT, ST_MASK = ST_ROWV + 1024;
+    static constexpr uint32_t STAGE_TX = 4 * ROWT + 1536;
+    static constexpr uint32_t STAGE_STRIDE = 4 * ROWT + 2048;
+    static constexpr uint32_t OFF_BARS = QS * STAGE_STRIDE;
+    static constexpr uint32_t NUM_BARS = 2 * QS + 4;
+    static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
+    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;
+    static constexpr uint32_t TMEM_COLS = 512;            // two buffers of S[128] | dP[128]
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+    static_assert(CW % 16 == 0, "columns per thread");
+};
+
+struct DbParams {
+    int B, S, N, H;
+    int NT, NTP;
+    int Z, SL;            // S slices, rows per slice
+    int total_items;      // Z * B * H * NT * NT
+    float c1;             // scale * log2(e)
+    const float* nlse2;   // [B*S][H][NTP]
+    const float* delta;   // [B*S][H][NTP]
+    const float* maskl2;  // [B*S][NTP]
+    const __nv_bfloat16* bias;   // [B][H][N][N]
+    float* dbias;                // [B][H][N][N]
+    unsigned int* status;
+};
+
+struct DbItem {
+    int b, h, i, j, s0, ns;
+};
+
+template <int DH, int NG>
+__global__ void __launch_bounds__(DbCfg<DH, NG>::THREADS, 1)
+evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                 const DbParams p) {
+    using C = DbCfg<DH, NG>;
+    using RT = RowTile<DH>;
+    constexpr int QS = C::QS, CW = C::CW, NCW = C::NCW;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BARS);
+    uint64_t* st_full = bars;                 // [QS]
+    uint64_t* st_empty = st_full + QS;        // [QS]
+    uint64_t* sdp_full = st_empty + QS;       // [2]
+    uint64_t* sdp_free = sdp_full + 2;        // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int NT = p.NT;
+    WaitCtx wc{abort_flag, p.status};
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1 + NCW); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], NCW); }
+        fence_mbar_init();
+        fence_async_smem();
+    }
+    if (warp == NCW + 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp == NCW && lane == 0) {
+        prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int first = blockIdx.x;
+    const int stride = gridDim.x;
+    const int n_items = (p.total_items > first) ? (p.total_items - first + stride - 1) / stride : 0;
+
+    // item index -> (slice, batch, head, q tile, kv tile); kv tile fastest, so CTAs
+    // that run side by side read the same S rows of the same head
+    auto decode = [&](int it) -> DbItem {
+        DbItem x;
+        int w = first + it * stride;
+        x.j = w % NT; w /= NT;
+        x.i = w % NT; w /= NT;
+        x.h = w % p.H; w /= p.H;
+        x.b = w % p.B; w /= p.B;
+        x.s0 = w * p.SL;
+        x.ns = (p.S - x.s0 < p.SL) ? (p.S - x.s0) : p.SL;
+        return x;
+    };
+
+    if (warp >= NCW) {
+        reg_dec<C::REGS_OTHER>();
+        if (warp == NCW) {
+            if (lane == 0) {
+                // ------------------------------ producer ------------------------------
+                bool ok = true;
+                int gs = 0;
+                for (int it = 0; it < n_items && ok; ++it) {
+                    const DbItem x = decode(it);
+                    for (int n = 0; n < x.ns && ok; ++n, ++gs) {
+                        const int st = gs % QS;
+                        if (gs >= QS) ok = mbar_wait(&st_empty[st], ((gs / QS) - 1) & 1, wc, 0x82);
+                        if (!ok) break;
+                        const int bs = x.b * p.S + x.s0 + n;
+                        uint8_t* sb = smem + st * C::STAGE_STRIDE;
+                        mbar_arrive_expect_tx(&st_full[st], C::STAGE_TX);
+                        tma_load_4d(sb + C::ST_Q, &tm_q, &st_full[st], 0, x.h, x.i * TILE, bs);
+                        tma_load_4d(sb + C::ST_K, &tm_k, &st_full[st], 0, x.h, x.j * TILE, bs);
+                        tma_load_4d(sb + C::ST_DO, &tm_do, &st_full[st], 0, x.h, x.i * TILE, bs);
+                        tma_load_4d(sb + C::ST_V, &tm_v, &st_full[st], 0, x.h, x.j * TILE, bs);
+                        const size_t ro = (static_cast<size_t>(bs) * p.H + x.h) * p.NTP + x.i * TILE;
+                        bulk_load(sb + C::ST_ROWV, p.nlse2 + ro, 512, &st_full[st]);
+                        bulk_load(sb + C::ST_ROWV + 512, p.delta + ro, 512, &st_full[st]);
+                        bulk_load(sb + C::ST_MASK, p.maskl2 + static_cast<size_t>(bs) * p.NTP + x.j * TILE, 512,
+                                  &st_full[st]);
+                    }
+                }
+                // the most recent loads have landed before the CTA exits
+                for (int k = (gs > QS ? gs - QS : 0); k < gs; ++k)
+                    (void)mbar_wait(&st_full[k % QS], (k / QS) & 1, wc, 0x83);
+            }
+        } else if (warp == NCW + 1) {
+            if (lane == 0) {
+                // ------------------------------ mma issuer ------------------------------
+                constexpr uint32_t IDESC = make_idesc_bf16(128, 128, 0, 0);
+                const uint32_t aSt = smem_u32(smem);
+                bool ok = true;
+                int gs = 0;
+                for (int it = 0; it < n_items && ok; ++it) {
+                    const DbItem x = decode(it);
+                    for (int n = 0; n < x.ns && ok; ++n, ++gs) {
+                        const int st = gs % QS, buf = gs & 1;
+                        ok = mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x90);
+                        if (ok && gs >= 2) ok = mbar_wait(&sdp_free[buf], ((gs >> 1) - 1) & 1, wc, 0x91);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t sb = aSt + st * C::STAGE_STRIDE;
+                        const uint32_t t0 = tmem + buf * 256;
+    #pragma unroll
+                        for (int kk = 0; kk < RT::KBLOCKS; ++kk)
+                            umma_ss(t0, RT::kmajor(sb + C::ST_Q, kk), RT::kmajor(sb + C::ST_K, kk), IDESC, kk > 0);
+    #pragma unroll
+                        for (int kk = 0; kk < RT::KBLOCKS; ++kk)
+                            umma_ss(t0 + 128, RT::kmajor(sb + C::ST_DO, kk), RT::kmajor(sb + C::ST_V, kk), IDESC,
+                                    kk > 0);
+                        umma_commit(&sdp_full[buf]);
+                        umma_commit(&st_empty[st]);
+                    }
+                }
+            }
+        }
+    } else {
+        reg_inc<C::REGS_COMPUTE>();
+        // ------------------------------ compute groups ------------------------------
+        const int g = warp >> 2;                   // kv columns g*CW .. of the tile
+        const int wrow0 = (warp & 3) * 32;
+        const int row = wrow0 + lane;              // q row within the tile == TMEM lane
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(wrow0) << 16) + g * CW;
+        bool ok = true;
+        int gs = 0;
+        const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
+
+        for (int it = 0; it < n_items && ok; ++it) {
+            const DbItem x = decode(it);
+            const int qrow = x.i * TILE + row;
+            const int col0 = x.j * TILE + g * CW;
+            const size_t tile_off = ((static_cast<size_t>(x.b) * p.H + x.h) * p.N + qrow) * p.N + col0;
+
+            uint32_t bias_pk[CW / 2];
+            float acc[CW];
+#pragma unroll
+            for (int c8 = 0; c8 < CW / 8; ++c8) {
+                uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+                if (qrow < p.N && col0 + c8 * 8 < p.N)
+                    bv = __ldg(reinterpret_cast<const uint4*>(p.bias + tile_off + c8 * 8));
+                bias_pk[c8 * 4 + 0] = bv.x; bias_pk[c8 * 4 + 1] = bv.y;
+                bias_pk[c8 * 4 + 2] = bv.z; bias_pk[c8 * 4 + 3] = bv.w;
+            }
+#pragma unroll
+            for (int c = 0; c < CW; ++c) acc[c] = 0.f;
+
+            for (int n = 0; n < x.ns && ok; ++n, ++gs) {
+                const int st = gs % QS, buf = gs & 1;
+                const uint8_t* sb = smem + st * C::STAGE_STRIDE;
+                ok = warp_all(mbar_wait(&sdp_full[buf], (gs >> 1) & 1, wc, 0xa0));
+                if (!ok) break;
+                ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0xa1));
+                if (!ok) break;
+                const float* rowv = reinterpret_cast<const float*>(sb + C::ST_ROWV);
+                const float nl = rowv[row];          // -LSE*log2e (-inf for padded rows)
+                const float dl = rowv[128 + row];    // delta
+                const float* mrow = reinterpret_cast<const float*>(sb + C::ST_MASK) + g * CW;
+                const float2 nl2 = make_float2(nl, nl), ndl2 = make_float2(-dl, -dl);
+                tc_fence_after();
+#pragma unroll
+                for (int ch = 0; ch < CW / 16; ++ch) {
+                    uint32_t sv[16], dv[16];
+                    tmem_ld16(lane_base + buf * 256 + 16 * ch, sv);
+                    tmem_ld16(lane_base + buf * 256 + 128 + 16 * ch, dv);
+                    tmem_wait_ld();
+                    if (ch == CW / 16 - 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sdp_free[buf]);
+                    }
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 mv = *reinterpret_cast<const float4*>(mrow + 16 * ch + q4 * 4);
+                        const float2 mm[2] = {make_float2(mv.x, mv.y), make_float2(mv.z, mv.w)};
+#pragma unroll
+                        for (int w = 0; w < 2; ++w) {
+                            const int c = q4 * 4 + 2 * w;
+                            // x = S*c1 + (bias + mask)*log2e - LSE*log2e, P = exp2(x), dS = P (dP - delta)
+                            const float2 t2 = ffma2(bf16x2_f2(bias_pk[ch * 8 + q4 * 2 + w]), l2e2, mm[w]);
+                            const float2 x2 = fadd2(ffma2(u2f2(sv[c], sv[c + 1]), c1x2, t2), nl2);
+                            const float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
+                            const float2 a2 = ffma2(p2, fadd2(u2f2(dv[c], dv[c + 1]), ndl2),
+                                                    make_float2(acc[ch * 16 + c], acc[ch * 16 + c + 1]));
+                            acc[ch * 16 + c] = a2.x;
+                            acc[ch * 16 + c + 1] = a2.y;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&st_empty[st]);
+            }
+            if (!ok) break;
+
+            // the finished tile: plain stores when this CTA saw every S row, else atomics
+            if (qrow < p.N) {
+                float* out = p.dbias + tile_off;
+#pragma unroll
+                for (int c4 = 0; c4 < CW / 4; ++c4) {
+                    if (col0 + c4 * 4 < p.N) {
+                        if (p.Z == 1) {
+                            *reinterpret_cast<float4*>(out + c4 * 4) =
+                                make_float4(acc[c4 * 4], acc[c4 * 4 + 1], acc[c4 * 4 + 2], acc[c4 * 4 + 3]);
+                        } else {
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c4 * 4),
+                                         "f"(acc[c4 * 4]), "f"(acc[c4 * 4 + 1]), "f"(acc[c4 * 4 + 2]),
+                                         "f"(acc[c4 * 4 + 3])
+                                         : "memory");
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == NCW + 1) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+#ifndef EVO_DBIAS_GROUPS
+#define EVO_DBIAS_GROUPS 2
+#endif
+
+template <int DH>
+static int launch_dbias_t(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
+                          const void* d_o, const float* nlse2, const float* delta, const float* maskl2,
+                          float* dbias, float scale, int sms, cudaStream_t st) {
+    constexpr int NG = EVO_DBIAS_GROUPS;
+    using C = DbCfg<DH, NG>;
+    const int BS = d->B * d->S;
+    const int NT = (d->N + TILE - 1) / TILE;
+
+    CUtensorMap tq, tk, tv, tdo;
+    int rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE))) return rc;
+
+    // Slices of S: enough items to fill the SMs evenly, each long enough that the
+    // per-item set-up (bias load, pipeline fill, tile write) stays small.
+    const long base = static_cast<long>(d->B) * d->H * NT * NT;
+    int best_z = 1;
+    long best_cost = -1;
+    const int zmax = d->S < 64 ? d->S : 64;
+    for (int z = 1; z <= zmax; ++z) {
+        const int sl = (d->S + z - 1) / z;
+        const int zz = (d->S + sl - 1) / sl;
+        const long waves = (base * zz + sms - 1) / sms;
+        const long cost = waves * (sl + 6);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_z = zz; }
+    }
+
+    DbParams p;
+    p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
+    p.NT = NT; p.NTP = NT * TILE;
+    p.SL = (d->S + best_z - 1) / best_z;
+    p.Z = (d->S + p.SL - 1) / p.SL;
+    p.total_items = static_cast<int>(base * p.Z);
+    const float sc = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH));
+    p.c1 = sc * LOG2E;
+    p.nlse2 = nlse2; p.delta = delta; p.maskl2 = maskl2;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.dbias = dbias;
+    p.status = status_word();
+    if (!p.status) return EVO_ERR_CUDA;
+
+    if ((rc = cuda_err(cudaFuncSetAttribute(evo_dbias_kernel<DH, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(C::SMEM_BYTES)))))
+        return rc;
+    const int grid = p.total_items < sms ? p.total_items : sms;
+    prof_begin(2, st);
+    evo_dbias_kernel<DH, NG><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    prof_end(2, st);
+    return cuda_err(cudaGetLastError());
+}
+
+int launch_dbias(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
+                 const void* d_o, const float* nlse2, const float* delta, const float* maskl2, float* dbias,
+                 float scale, int sms, cudaStream_t st) {
+    if (d->D == 32)
+        return launch_dbias_t<32>(d, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st);
+    return launch_dbias_t<64>(d, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st);
+}
+
+}  // namespace evo

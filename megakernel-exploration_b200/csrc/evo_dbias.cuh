@@ -1,0 +1,15 @@
+// Launcher of the pair-bias gradient kernel (evo_dbias.cu), called by the
+// backward launcher between its prep kernel and the dQ/dK/dV kernel.
+#pragma once
+#include "evo_host.cuh"
+
+namespace evo {
+
+// dbias [B][H][N][N] fp32 must be zeroed on `st` before the call.  nlse2, delta
+// and maskl2 are the tile-padded rows the prep kernel writes (see evo_bwd.cu).
+// D is 32 or 64.
+int launch_dbias(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
+                 const void* d_o, const float* nlse2, const float* delta, const float* maskl2, float* dbias,
+                 float scale, int sms, cudaStream_t st);
+
+}  // namespace evo

@@ -38,8 +38,10 @@
 namespace evo {
 
 constexpr int FWD_THREADS = 384;           // 3 warpgroups: 2 softmax + (producer, mma, 2 idle warps)
-constexpr int FWD_REGS_SOFTMAX = 224;
-constexpr int FWD_REGS_OTHER = 56;
+constexpr int FWD_REGS_SOFTMAX = 208;
+constexpr int FWD_REGS_OTHER = 88;
+// the CTA's register pool is the launch count (cap for 384 threads: 168) times the threads
+static_assert(FWD_REGS_SOFTMAX * 256 + FWD_REGS_OTHER * 128 <= 168 * FWD_THREADS, "register pool");
 
 template <int DH>
 struct FwdCfg {
@@ -134,6 +136,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
         prefetch_tmap(&tm_bias); prefetch_tmap(&tm_o);
     }
+    EVO_TRACE_INIT();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -502,6 +505,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tid == 0) EVO_TE(t_kernel, p.status, 0x7e);
     tc_fence_before();
     __syncthreads();
+    EVO_TRACE_FLUSH(p.status);
     if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 

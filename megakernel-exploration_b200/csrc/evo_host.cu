@@ -157,7 +157,7 @@ struct ProfRec {
 };
 std::mutex g_prof_mu;
 bool g_prof_on = false;
-ProfRec g_prof[2];
+ProfRec g_prof[3];
 constexpr size_t PROF_MAX = 4096;
 }  // namespace
 
@@ -238,7 +238,7 @@ int evo_profile_enable(int on) {
 }
 
 int evo_profile_read(int kernel, float* total_ms, int* launches) {
-    if (kernel < 0 || kernel > 1 || !total_ms || !launches) return EVO_ERR_NULL_PTR;
+    if (kernel < 0 || kernel > 2 || !total_ms || !launches) return EVO_ERR_NULL_PTR;
     std::lock_guard<std::mutex> lock(evo::g_prof_mu);
     evo::ProfRec& r = evo::g_prof[kernel];
     float sum = 0.f;

@@ -104,18 +104,39 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // Optional cycle accounting (builds with -DEVO_TRACE only): per wait site / code
 // region, summed over warps and CTAs, in the words that follow the status word.
 #ifdef EVO_TRACE
-__device__ __forceinline__ void trace_add(unsigned int* status, uint32_t site, long long dt) {
+// accumulators live in shared memory during the kernel and are added to the global
+// words once at the end, so that tracing perturbs the timing as little as possible
+__device__ __forceinline__ unsigned long long* trace_smem() {
+    __shared__ unsigned long long t[512];
+    return t;
+}
+__device__ __forceinline__ void trace_add(unsigned int*, uint32_t site, long long dt) {
     if ((threadIdx.x & 31u) == 0u) {
-        unsigned long long* t = reinterpret_cast<unsigned long long*>(status + 2);
+        unsigned long long* t = trace_smem();
         atomicAdd(&t[(site & 255u) * 2], static_cast<unsigned long long>(dt));
         atomicAdd(&t[(site & 255u) * 2 + 1], 1ull);
     }
 }
+// all threads, before the first and after the last traced region (with __syncthreads around)
+__device__ __forceinline__ void trace_init() {
+    unsigned long long* t = trace_smem();
+    for (int i = threadIdx.x; i < 512; i += blockDim.x) t[i] = 0ull;
+}
+__device__ __forceinline__ void trace_flush(unsigned int* status) {
+    unsigned long long* t = trace_smem();
+    unsigned long long* g = reinterpret_cast<unsigned long long*>(status + 2);
+    for (int i = threadIdx.x; i < 512; i += blockDim.x)
+        if (t[i]) atomicAdd(&g[i], t[i]);
+}
+#define EVO_TRACE_INIT() trace_init()
+#define EVO_TRACE_FLUSH(status) trace_flush(status)
 #define EVO_T0() const long long evo_t0_ = clock64()
 #define EVO_T1(status, site) trace_add((status), (site), clock64() - evo_t0_)
 #define EVO_TS(var) const long long var = clock64()
 #define EVO_TE(var, status, site) trace_add((status), (site), clock64() - var)
 #else
+#define EVO_TRACE_INIT() do {} while (0)
+#define EVO_TRACE_FLUSH(status) do {} while (0)
 #define EVO_T0() do {} while (0)
 #define EVO_T1(status, site) do {} while (0)
 #define EVO_TS(var) do {} while (0)
