@@ -13,7 +13,7 @@ NCCL all-reduce of dBias in backward: "weak" keeps S rows per GPU fixed,
 value      whole-job TFLOP/s, algorithmic FLOPs 14*B*S*H*N^2*D, inputs resident in HBM
 e2e        same metric with host (pinned) buffers: H2D of q,k,v,dO,mask,bias and
            D2H of O,dQ,dK,dV,dBias inside the timed region
-roofline   backward main kernel: its 10*B*S*H*N^2*D FLOPs / its CUDA-event time,
+roofline   backward dQ/dK/dV kernel: its 10*B*S*H*N^2*D FLOPs / its CUDA-event time,
            against the measured sustained bf16 GEMM peak
 cpu_baseline / --impl reference   the eager PyTorch restatement on the host cores
 """
@@ -247,6 +247,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     _evoattn.profile_enable(False)
     fwd_ms, fwd_n = _evoattn.profile_read(0)
     bwd_ms, bwd_n = _evoattn.profile_read(1)
+    db_ms, db_n = _evoattn.profile_read(2)
     _evoattn.device_status()
 
     e2e_steps = max(3, min(args.steps, 10))
@@ -270,6 +271,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "avg_launch_ms": bwd_avg_ms, "launches_timed": bwd_n,
         "fwd_kernel": {"avg_launch_ms": fwd_ms / max(fwd_n, 1), "launches_timed": fwd_n,
                        "achieved": (4.0 * B * rows * H * N * N * D) / (fwd_ms / max(fwd_n, 1) * 1e-3) / 1e12 if fwd_n else None},
+        "dbias_kernel": {"avg_launch_ms": db_ms / max(db_n, 1), "launches_timed": db_n,
+                         "achieved": (4.0 * B * rows * H * N * N * D) / (db_ms / max(db_n, 1) * 1e-3) / 1e12 if db_n else None},
     }
 
     cpu = None
@@ -292,7 +295,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "clocks": cs.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": 5 * args.steps,   # forward; backward: prep, dBias, dQ/dK/dV, dQ conversion
             "roofline": roofline,
         }
         if cpu is not None:

@@ -21,22 +21,22 @@
 // (q tile i, row r of the chunk), r innermost, so that one pair-bias tile serves
 // RC steps.  dK/dV of every row of the chunk stay in tensor memory for the item.
 //
-//   warp 8 (producer)  TMA per step: Q, dO tiles and the -LSE / delta rows; K, V
-//                      tiles and the mask row per step (D=32) or per item (D=64);
-//                      the pair-bias tile per q tile
-//   warp 9 (mma)       tcgen05.mma, issued in whatever order operands become
-//                      ready: S = Q K^T and dP = dO V^T of the next step, or
-//                      dV += P^T dO, dK += dS^T Q, dQ = dS K of the current one
 //   warps 0-3, 4-7     two compute groups; group g owns kv columns 64g..64g+63
 //                      (thread = one q row).  Per step: P and dS from S and dP,
 //                      kept packed in registers until the previous step's
 //                      dV/dK/dQ MMAs have finished reading the P/dS tiles, then
-//                      written to shared memory as MMA operands.  Afterwards, off
-//                      the critical path and warp-locally (no barrier beyond the
-//                      warp): each warp stages its 32 rows of the previous step's
-//                      dQ in its own shared-memory slot and issues a TMA
-//                      reduce-add (fp32) for them; after an item, dK/dV go out as
-//                      bf16 stores.
+//                      written to shared memory as MMA operands.
+//   warps 8-11 (drain) warp w owns tensor-memory lanes 32(w-8)..: after every step
+//                      it stages its 32 rows of dQ (one of two accumulators) in its
+//                      own shared-memory slot and issues a TMA reduce-add (fp32)
+//                      for them; after an item, dK/dV go out as bf16 stores.  None
+//                      of this is on the compute groups' path.
+//   warp 12 (producer) TMA per step: Q, dO tiles and the -LSE / delta rows; K, V
+//                      tiles and the mask row per step (D=32) or per item (D=64);
+//                      the pair-bias tile per q tile
+//   warp 13 (mma)      tcgen05.mma, issued in whatever order operands become
+//                      ready: S = Q K^T and dP = dO V^T of the next step, or
+//                      dV += P^T dO, dK += dS^T Q, dQ = dS K of the current one
 #include "evo_dbias.cuh"
 #include "evo_host.cuh"
 #include "evo_ptx.cuh"
@@ -44,14 +44,19 @@
 
 #include <mutex>
 
+
 namespace evo {
 
-constexpr int BWD_THREADS = 384;           // 3 warpgroups: 2 compute + (producer, mma, 2 idle warps)
+// 4 warpgroups: 2 compute, drain, (producer, mma, 2 idle warps)
+constexpr int BWD_THREADS = 512;
+constexpr int BWD_WARP_DRAIN = 8, BWD_WARP_PRODUCER = 12, BWD_WARP_MMA = 13;
 constexpr uint32_t BWD_TMEM_COLS = 512;
-constexpr int BWD_REGS_COMPUTE = 224;
-constexpr int BWD_REGS_OTHER = 56;
-// the CTA's register pool is the launch count (cap for 384 threads: 168) times the threads
-static_assert(BWD_REGS_COMPUTE * 256 + BWD_REGS_OTHER * 128 <= 168 * BWD_THREADS, "register pool");
+constexpr int BWD_REGS_COMPUTE = 192;
+constexpr int BWD_REGS_OTHER = 64;
+constexpr int BWD_DQ_BUFS = 2;             // dQ accumulators in tensor memory
+// the CTA's register pool is the launch count (cap for 512 threads: 128) times the threads;
+// a setmaxnreg increase that the pool cannot satisfy blocks for ever
+static_assert(BWD_REGS_COMPUTE * 256 + BWD_REGS_OTHER * 256 <= 128 * BWD_THREADS, "register pool");
 
 template <int DH>
 struct BwdCfg {
@@ -76,17 +81,17 @@ struct BwdCfg {
     static constexpr uint32_t OFF_BIAS = OFF_KV + KV_BYTES;
     static constexpr uint32_t OFF_P = OFF_BIAS + SQ_BYTES;
     static constexpr uint32_t OFF_DS = OFF_P + SQ_BYTES;
-    // per warp: dQ slot [32 rows][16 fp32]
-    static constexpr uint32_t WQ_BYTES = 32 * 16 * 4;
+    // per drain warp: dQ slot [32 rows][32 fp32]
+    static constexpr uint32_t WQ_BYTES = 32 * 32 * 4;
     static constexpr uint32_t OFF_WSTG = OFF_DS + SQ_BYTES;
-    static constexpr uint32_t OFF_BARS = OFF_WSTG + 8 * WQ_BYTES;
-    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 6;
+    static constexpr uint32_t OFF_BARS = OFF_WSTG + 4 * WQ_BYTES;
+    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 8;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
     static constexpr uint32_t TMEM_DP = 128;
-    static constexpr uint32_t TMEM_DQ = 256;
-    static constexpr uint32_t TMEM_DKV = 256 + DH;                          // + r*2*DH (dK), + DH (dV)
+    static constexpr uint32_t TMEM_DQ = 256;                                // two accumulators, + (step & 1)*DH
+    static constexpr uint32_t TMEM_DKV = 256 + 2 * DH;                      // + r*2*DH (dK), + DH (dV)
     static_assert(TMEM_DKV + RC * 2 * DH <= BWD_TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
     static_assert(OFF_KV % 1024 == 0 && OFF_BIAS % 1024 == 0 && WQ_BYTES % 1024 == 0, "tile alignment");
@@ -120,7 +125,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                const BwdParams p) {
     using C = BwdCfg<DH>;
     using RT = RowTile<DH>;
-    constexpr int RC = C::RC, QS = C::QS, HALF = C::HALF;
+    using RD = RowDesc<DH>;
+    constexpr int RC = C::RC, QS = C::QS;
     constexpr bool KVR = C::KV_RESIDENT;
 
     extern __shared__ uint8_t smem_raw[];
@@ -135,9 +141,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* sdp_full = bias_empty + 1;
     uint64_t* sdp_free = sdp_full + 1;
     uint64_t* pds_ready = sdp_free + 1;
-    uint64_t* dq_full = pds_ready + 1;
-    uint64_t* dq_free = dq_full + 1;
-    uint64_t* dkv_free = dq_free + 1;
+    uint64_t* dq_full = pds_ready + 1;         // [2]
+    uint64_t* dq_free = dq_full + 2;           // [2]
+    uint64_t* dkv_free = dq_free + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -157,17 +163,16 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(sdp_full, 1);
         mbar_init(sdp_free, 8);
         mbar_init(pds_ready, 8);
-        mbar_init(dq_full, 1);
-        mbar_init(dq_free, 8);
-        mbar_init(dkv_free, 8);
+        for (int i = 0; i < 2; ++i) { mbar_init(&dq_full[i], 1); mbar_init(&dq_free[i], 4); }
+        mbar_init(dkv_free, 4);
         fence_mbar_init();
         fence_async_smem();
     }
-    if (warp == 9) {
+    if (warp == BWD_WARP_MMA) {
         tmem_alloc(tmem_slot, BWD_TMEM_COLS);
         tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == BWD_WARP_PRODUCER && lane == 0) {
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
         prefetch_tmap(&tm_bias); prefetch_tmap(&tm_dq);
     }
@@ -198,9 +203,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         return x;
     };
 
-    if (warp >= 8) {
+    if (warp >= BWD_WARP_DRAIN) {
         reg_dec<BWD_REGS_OTHER>();
-        if (warp == 8 && lane == 0) {
+        if (warp == BWD_WARP_PRODUCER && lane == 0) {
             // ------------------------------ producer ------------------------------
             bool ok = true;
             int gs = 0, gb = 0;
@@ -254,13 +259,15 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 (void)mbar_wait(&st_full[k % QS], (k / QS) & 1, wc, 0x43);
             if (gb > 0) (void)mbar_wait(bias_full, (gb - 1) & 1, wc, 0x44);
             if (KVR && n_items > 0) (void)mbar_wait(kv_full, (n_items - 1) & 1, wc, 0x45);
-        } else if (warp == 9 && lane == 0) {
+        } else if (warp == BWD_WARP_MMA && lane == 0) {
             // ------------------------------ mma issuer ------------------------------
             constexpr uint32_t IDESC_SDP = make_idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t IDESC_DKV = make_idesc_bf16(128, DH, 1, 1);
             constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, DH, 0, 1);
             const uint32_t aSt = smem_u32(smem + C::OFF_STAGE), aKV = smem_u32(smem + C::OFF_KV);
-            const uint32_t aP = smem_u32(smem + C::OFF_P), aDS = smem_u32(smem + C::OFF_DS);
+            const uint32_t p_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_P));
+            const uint32_t ds_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_DS));
+            const uint32_t ds_k_lo = SqDesc::kmajor_lo(smem_u32(smem + C::OFF_DS));
 
             struct Cursor {
                 int it, n, gs, nsteps;
@@ -292,13 +299,14 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tc_fence_after();
                 const int r = c.n % c.x.nr;
                 const uint32_t sb = aSt + st * C::STAGE_STRIDE;
-                const uint32_t kt = k_tile(c, r), vt = v_tile(c, r);
+                const uint32_t q_lo = RD::kmajor_lo(sb + C::ST_Q), do_lo = RD::kmajor_lo(sb + C::ST_DO);
+                const uint32_t k_lo = RD::kmajor_lo(k_tile(c, r)), v_lo = RD::kmajor_lo(v_tile(c, r));
 #pragma unroll
                 for (int kk = 0; kk < RT::KBLOCKS; ++kk)
-                    umma_ss(tmem + C::TMEM_S, RT::kmajor(sb + C::ST_Q, kk), RT::kmajor(kt, kk), IDESC_SDP, kk > 0);
+                    umma_ss(tmem + C::TMEM_S, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC_SDP, kk > 0);
 #pragma unroll
                 for (int kk = 0; kk < RT::KBLOCKS; ++kk)
-                    umma_ss(tmem + C::TMEM_DP, RT::kmajor(sb + C::ST_DO, kk), RT::kmajor(vt, kk), IDESC_SDP, kk > 0);
+                    umma_ss(tmem + C::TMEM_DP, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC_SDP, kk > 0);
                 umma_commit(sdp_full);
                 return true;
             };
@@ -307,22 +315,27 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int st = c.gs % QS;
                 const int i = c.n / c.x.nr, r = c.n - i * c.x.nr;
                 if (!mbar_test(pds_ready, c.gs & 1)) return false;
-                if (c.gs > 0 && !mbar_test(dq_free, (c.gs - 1) & 1)) return false;
+                if (c.gs >= BWD_DQ_BUFS &&
+                    !mbar_test(&dq_free[c.gs % BWD_DQ_BUFS], ((c.gs / BWD_DQ_BUFS) - 1) & 1))
+                    return false;
                 if (c.n == 0 && c.it > 0 && !mbar_test(dkv_free, (c.it - 1) & 1)) return false;
                 tc_fence_after();
                 const uint32_t sb = aSt + st * C::STAGE_STRIDE;
-                const uint32_t kt = k_tile(c, r);
+                const uint32_t q_lo = RD::mnmajor_lo(sb + C::ST_Q), do_lo = RD::mnmajor_lo(sb + C::ST_DO);
+                const uint32_t k_lo = RD::mnmajor_lo(k_tile(c, r));
                 const uint32_t t_dk = tmem + C::TMEM_DKV + r * 2 * DH, t_dv = t_dk + DH;
+                const uint32_t t_dq = tmem + C::TMEM_DQ + (c.gs % BWD_DQ_BUFS) * DH;
+                const uint32_t acc = (i > 0) ? 1u : 0u;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
-                    umma_ss(t_dv, sq_mnmajor(aP, kk), RT::mnmajor(sb + C::ST_DO, kk), IDESC_DKV, (i > 0 || kk > 0));
+                    umma_ss(t_dv, SqDesc::mnmajor(p_mn_lo, kk), RD::mnmajor(do_lo, kk), IDESC_DKV, kk > 0 ? 1u : acc);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
-                    umma_ss(t_dk, sq_mnmajor(aDS, kk), RT::mnmajor(sb + C::ST_Q, kk), IDESC_DKV, (i > 0 || kk > 0));
+                    umma_ss(t_dk, SqDesc::mnmajor(ds_mn_lo, kk), RD::mnmajor(q_lo, kk), IDESC_DKV, kk > 0 ? 1u : acc);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
-                    umma_ss(tmem + C::TMEM_DQ, sq_kmajor(aDS, kk), RT::mnmajor(kt, kk), IDESC_DQ, kk > 0);
-                umma_commit(dq_full);
+                    umma_ss(t_dq, SqDesc::kmajor(ds_k_lo, kk), RD::mnmajor(k_lo, kk), IDESC_DQ, kk > 0);
+                umma_commit(&dq_full[c.gs % BWD_DQ_BUFS]);
                 umma_commit(&st_empty[st]);
                 if (KVR && c.n == c.nsteps - 1) umma_commit(kv_empty);
                 return true;
@@ -360,6 +373,81 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
             }
+        } else if (warp < BWD_WARP_DRAIN + 4) {
+            // ------------------------------ drain warps ------------------------------
+            const int wrow0 = (warp & 3) * 32;   // tensor-memory lanes (tile rows) of this warp
+            const uint32_t lane_base = tmem + (static_cast<uint32_t>(wrow0) << 16);
+            uint8_t* wq = smem + C::OFF_WSTG + (warp & 3) * C::WQ_BYTES;
+            bool ok = true;
+            int gs = 0;
+            for (int it = 0; it < n_items && ok; ++it) {
+                const BwdItem x = decode(it);
+                const int nsteps = NT * x.nr;
+                int i = 0, r = 0;
+                for (int n = 0; n < nsteps && ok; ++n, ++gs) {
+                    const int b = gs % BWD_DQ_BUFS;
+                    ok = warp_all(mbar_wait(&dq_full[b], (gs / BWD_DQ_BUFS) & 1, wc, 0x68));
+                    if (!ok) break;
+                    tc_fence_after();
+                    // dQ of this step: tensor memory -> this warp's slot -> fp32 reduce-add
+#pragma unroll
+                    for (int rd = 0; rd < DH / 32; ++rd) {
+                        float dqv[32];
+                        tmem_ld_f32<32>(lane_base + C::TMEM_DQ + b * DH + rd * 32, dqv);
+                        if (rd == DH / 32 - 1) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&dq_free[b]);
+                        }
+                        if (i * TILE + wrow0 < p.N) {     // warp-uniform
+                            // the slot is free once lane 0's earlier bulk operations have read it
+                            if (lane == 0) tma_wait_group_read<0>();
+                            __syncwarp();
+#pragma unroll
+                            for (int cc = 0; cc < 8; ++cc)
+                                *reinterpret_cast<float4*>(wq + swz_off<128>(lane, cc)) =
+                                    make_float4(dqv[cc * 4 + 0] * p.scale, dqv[cc * 4 + 1] * p.scale,
+                                                dqv[cc * 4 + 2] * p.scale, dqv[cc * 4 + 3] * p.scale);
+                            fence_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_reduce_add_4d(&tm_dq, wq, rd * 32, x.h, i * TILE + wrow0, x.bs0 + r);
+                                tma_commit_group();
+                            }
+                        }
+                    }
+                    if (n == nsteps - 1) {
+                        // the item's last MMAs are done: dK/dV -> bf16 stores
+                        const int kvrow = x.j * TILE + wrow0 + lane;
+                        for (int t = 0; t < 2 * x.nr; ++t) {      // 2*r: dK of row r, 2*r+1: dV
+                            const float sc = (t & 1) ? 1.0f : p.scale;
+                            __nv_bfloat16* out = ((t & 1) ? p.dv : p.dk) +
+                                ((static_cast<size_t>(x.bs0 + (t >> 1)) * p.N + kvrow) * p.H + x.h) * DH;
+#pragma unroll
+                            for (int hf = 0; hf < DH / 32; ++hf) {
+                                float v[32];
+                                tmem_ld_f32<32>(lane_base + C::TMEM_DKV + (t >> 1) * 2 * DH + (t & 1) * DH + hf * 32, v);
+                                if (kvrow < p.N) {
+#pragma unroll
+                                    for (int c8 = 0; c8 < 4; ++c8) {
+                                        uint4 u;
+                                        u.x = pack_bf16(v[c8 * 8 + 0] * sc, v[c8 * 8 + 1] * sc);
+                                        u.y = pack_bf16(v[c8 * 8 + 2] * sc, v[c8 * 8 + 3] * sc);
+                                        u.z = pack_bf16(v[c8 * 8 + 4] * sc, v[c8 * 8 + 5] * sc);
+                                        u.w = pack_bf16(v[c8 * 8 + 6] * sc, v[c8 * 8 + 7] * sc);
+                                        *reinterpret_cast<uint4*>(out + hf * 32 + c8 * 8) = u;
+                                    }
+                                }
+                            }
+                        }
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(dkv_free);
+                    }
+                    if (++r == x.nr) { r = 0; ++i; }
+                }
+            }
+            if (lane == 0) tma_wait_group<0>();
         }
     } else {
         reg_inc<BWD_REGS_COMPUTE>();
@@ -370,75 +458,10 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(wrow0) << 16);
         uint8_t* sP = smem + C::OFF_P;
         uint8_t* sDS = smem + C::OFF_DS;
-        uint8_t* wq = smem + C::OFF_WSTG + warp * C::WQ_BYTES;      // this warp's dQ slot
         bool ok = true;
         int gs = 0, gb = 0;
 
         uint32_t bias_pk[32];                // this thread's 64 bias values (bf16 pairs)
-
-        // Work left over from earlier steps, done after this step's P/dS are out:
-        //   drain  dQ of step (px, pi, pr) from tensor memory -> fp32 reduce-add
-        //   dkv    dK/dV of item kx -> bf16 stores
-        auto post_step = [&](bool drain, const BwdItem& px, int pi, int pr, bool dkv, const BwdItem& kx) {
-            EVO_TS(t_post);
-            if (drain) {
-                float dqv[HALF];
-                tc_fence_after();
-                tmem_ld_f32<HALF>(lane_base + C::TMEM_DQ + wg * HALF, dqv);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(dq_free);
-                if (pi * TILE + wrow0 < p.N) {     // warp-uniform
-#pragma unroll
-                    for (int rd = 0; rd < HALF / 16; ++rd) {
-                        // the slot is free once this lane-0's earlier bulk operations have read it
-                        if (lane == 0) tma_wait_group_read<0>();
-                        __syncwarp();
-#pragma unroll
-                        for (int cc = 0; cc < 4; ++cc)
-                            *reinterpret_cast<float4*>(wq + swz_off<64>(lane, cc)) =
-                                make_float4(dqv[rd * 16 + cc * 4 + 0] * p.scale, dqv[rd * 16 + cc * 4 + 1] * p.scale,
-                                            dqv[rd * 16 + cc * 4 + 2] * p.scale, dqv[rd * 16 + cc * 4 + 3] * p.scale);
-                        fence_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            tma_reduce_add_4d(&tm_dq, wq, wg * HALF + rd * 16, px.h, pi * TILE + wrow0, px.bs0 + pr);
-                            tma_commit_group();
-                        }
-                    }
-                }
-            }
-            if (dkv) {
-                tc_fence_after();
-                const int kvrow = kx.j * TILE + row;
-                for (int t = 0; t < 2 * kx.nr; ++t) {      // 2*r: dK of row r, 2*r+1: dV
-                    float v[HALF];
-                    tmem_ld_f32<HALF>(lane_base + C::TMEM_DKV + (t >> 1) * 2 * DH + (t & 1) * DH + wg * HALF, v);
-                    const float sc = (t & 1) ? 1.0f : p.scale;
-                    if (kvrow < p.N) {
-                        __nv_bfloat16* out = ((t & 1) ? p.dv : p.dk) +
-                            ((static_cast<size_t>(kx.bs0 + (t >> 1)) * p.N + kvrow) * p.H + kx.h) * DH + wg * HALF;
-#pragma unroll
-                        for (int c8 = 0; c8 < HALF / 8; ++c8) {
-                            uint4 u;
-                            u.x = pack_bf16(v[c8 * 8 + 0] * sc, v[c8 * 8 + 1] * sc);
-                            u.y = pack_bf16(v[c8 * 8 + 2] * sc, v[c8 * 8 + 3] * sc);
-                            u.z = pack_bf16(v[c8 * 8 + 4] * sc, v[c8 * 8 + 5] * sc);
-                            u.w = pack_bf16(v[c8 * 8 + 6] * sc, v[c8 * 8 + 7] * sc);
-                            *reinterpret_cast<uint4*>(out + c8 * 8) = u;
-                        }
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(dkv_free);
-            }
-            EVO_TE(t_post, p.status, 0x71);
-        };
-
-        bool have_prev = false, prev_item_end = false;
-        BwdItem prev_x{};                     // item of the previous step
-        int prev_i = 0, prev_r = 0;
 
         for (int it = 0; it < n_items && ok; ++it) {
             const BwdItem x = decode(it);
@@ -447,8 +470,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 ok = warp_all(mbar_wait(kv_full, it & 1, wc, 0x62));     // mask rows of this item
                 if (!ok) break;
             }
+            int r = 0;                       // row of the chunk, innermost
             for (int n = 0; n < nsteps && ok; ++n, ++gs) {
-                const int i = n / x.nr, r = n - i * x.nr;
                 const int st = gs % QS;
                 const uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
                 ok = warp_all(mbar_wait(sdp_full, gs & 1, wc, 0x63));
@@ -464,8 +487,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         bias_pk[c8 * 4 + 0] = bv.x; bias_pk[c8 * 4 + 1] = bv.y;
                         bias_pk[c8 * 4 + 2] = bv.z; bias_pk[c8 * 4 + 3] = bv.w;
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bias_empty);
+                    mbar_release_after_reads(bias_empty);     // the tile now lives in registers
                     ++gb;
                 }
                 ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x65));
@@ -509,16 +531,18 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         }
                     }
                 }
+                // the rows (and mask) of the stage and the resident mask rows are read
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&st_empty[st]);                          // rows (and mask) of this stage are read
-                    if (KVR && n == nsteps - 1) mbar_arrive(kv_empty);   // resident mask rows are read
+                    __threadfence_block();     // see mbar_release_after_reads
+                    mbar_arrive(&st_empty[st]);
+                    if (KVR && n == nsteps - 1) mbar_arrive(kv_empty);
                 }
                 EVO_TE(t_cmp, p.status, 0x70);
 
                 // the P / dS tiles are free once the previous step's dV/dK/dQ MMAs are done
-                if (have_prev) {
-                    ok = warp_all(mbar_wait(dq_full, (gs - 1) & 1, wc, 0x61));
+                if (gs > 0) {
+                    ok = warp_all(mbar_wait(&dq_full[(gs - 1) % BWD_DQ_BUFS], ((gs - 1) / BWD_DQ_BUFS) & 1, wc, 0x61));
                     if (!ok) break;
                 }
 #pragma unroll
@@ -532,26 +556,16 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pds_ready);
-
-                post_step(have_prev, prev_x, prev_i, prev_r, have_prev && prev_item_end, prev_x);
-                have_prev = true;
-                prev_x = x; prev_i = i; prev_r = r;
-                prev_item_end = (n == nsteps - 1);
+                if (++r == x.nr) r = 0;
             }
         }
-        if (ok && have_prev) {
-            // the very last step: its dQ, and the last item's dK/dV
-            ok = warp_all(mbar_wait(dq_full, (gs - 1) & 1, wc, 0x66));
-            if (ok) post_step(true, prev_x, prev_i, prev_r, true, prev_x);
-        }
-        if (lane == 0) tma_wait_group<0>();
     }
 
     if (tid == 0) EVO_TE(t_kernel, p.status, 0x7f);
     tc_fence_before();
     __syncthreads();
     EVO_TRACE_FLUSH(p.status);
-    if (warp == 9) tmem_dealloc(tmem, BWD_TMEM_COLS);
+    if (warp == BWD_WARP_MMA) tmem_dealloc(tmem, BWD_TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------
@@ -665,7 +679,7 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
-    if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 16, 32))) return rc;
+    if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 32, 32))) return rc;
 
     BwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;

@@ -113,10 +113,12 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (warp == NCW && lane == 0) {
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
     }
+    EVO_TRACE_INIT();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    EVO_TS(t_kernel);
 
     const int first = blockIdx.x;
     const int stride = gridDim.x;
@@ -234,43 +236,57 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (!ok) break;
                 ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0xa1));
                 if (!ok) break;
+                EVO_TS(t_math);
                 const float* rowv = reinterpret_cast<const float*>(sb + C::ST_ROWV);
                 const float nl = rowv[row];          // -LSE*log2e (-inf for padded rows)
                 const float dl = rowv[128 + row];    // delta
                 const float* mrow = reinterpret_cast<const float*>(sb + C::ST_MASK) + g * CW;
                 const float2 nl2 = make_float2(nl, nl), ndl2 = make_float2(-dl, -dl);
                 tc_fence_after();
+                // Chunks of 16 columns.  The tensor-memory loads of chunk ch+1 are in flight
+                // during the arithmetic of chunk ch, and the arithmetic goes stage by stage over
+                // the eight column pairs of the chunk so that neighbouring instructions are
+                // independent.
+                uint32_t sv[2][16], dv[2][16];
+                tmem_ld16(lane_base + buf * 256, sv[0]);
+                tmem_ld16(lane_base + buf * 256 + 128, dv[0]);
 #pragma unroll
                 for (int ch = 0; ch < CW / 16; ++ch) {
-                    uint32_t sv[16], dv[16];
-                    tmem_ld16(lane_base + buf * 256 + 16 * ch, sv);
-                    tmem_ld16(lane_base + buf * 256 + 128 + 16 * ch, dv);
+                    const int cb = ch & 1;
                     tmem_wait_ld();
-                    if (ch == CW / 16 - 1) {
+                    if (ch + 1 < CW / 16) {
+                        tmem_ld16(lane_base + buf * 256 + 16 * (ch + 1), sv[cb ^ 1]);
+                        tmem_ld16(lane_base + buf * 256 + 128 + 16 * (ch + 1), dv[cb ^ 1]);
+                    } else {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&sdp_free[buf]);
                     }
+                    // x = S*c1 + (bias + mask)*log2e - LSE*log2e, P = exp2(x), dS = P (dP - delta)
+                    float2 t2[8], p2[8];
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const float4 mv = *reinterpret_cast<const float4*>(mrow + 16 * ch + q4 * 4);
-                        const float2 mm[2] = {make_float2(mv.x, mv.y), make_float2(mv.z, mv.w)};
+                    for (int k = 0; k < 8; k += 2) {
+                        const float4 mv = *reinterpret_cast<const float4*>(mrow + 16 * ch + 2 * k);
+                        t2[k] = ffma2(bf16x2_f2(bias_pk[ch * 8 + k]), l2e2, make_float2(mv.x, mv.y));
+                        t2[k + 1] = ffma2(bf16x2_f2(bias_pk[ch * 8 + k + 1]), l2e2, make_float2(mv.z, mv.w));
+                    }
 #pragma unroll
-                        for (int w = 0; w < 2; ++w) {
-                            const int c = q4 * 4 + 2 * w;
-                            // x = S*c1 + (bias + mask)*log2e - LSE*log2e, P = exp2(x), dS = P (dP - delta)
-                            const float2 t2 = ffma2(bf16x2_f2(bias_pk[ch * 8 + q4 * 2 + w]), l2e2, mm[w]);
-                            const float2 x2 = fadd2(ffma2(u2f2(sv[c], sv[c + 1]), c1x2, t2), nl2);
-                            const float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
-                            const float2 a2 = ffma2(p2, fadd2(u2f2(dv[c], dv[c + 1]), ndl2),
-                                                    make_float2(acc[ch * 16 + c], acc[ch * 16 + c + 1]));
-                            acc[ch * 16 + c] = a2.x;
-                            acc[ch * 16 + c + 1] = a2.y;
-                        }
+                    for (int k = 0; k < 8; ++k)
+                        t2[k] = fadd2(ffma2(u2f2(sv[cb][2 * k], sv[cb][2 * k + 1]), c1x2, t2[k]), nl2);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) p2[k] = make_float2(ex2(t2[k].x), ex2(t2[k].y));
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) t2[k] = fadd2(u2f2(dv[cb][2 * k], dv[cb][2 * k + 1]), ndl2);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const float2 a2 =
+                            ffma2(p2[k], t2[k], make_float2(acc[ch * 16 + 2 * k], acc[ch * 16 + 2 * k + 1]));
+                        acc[ch * 16 + 2 * k] = a2.x;
+                        acc[ch * 16 + 2 * k + 1] = a2.y;
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&st_empty[st]);
+                mbar_release_after_reads(&st_empty[st]);      // row vectors and mask row are read
+                EVO_TE(t_math, p.status, 0xa8);
             }
             if (!ok) break;
 
@@ -295,8 +311,10 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     }
 
+    if (tid == 0) EVO_TE(t_kernel, p.status, 0xaf);
     tc_fence_before();
     __syncthreads();
+    EVO_TRACE_FLUSH(p.status);
     if (warp == NCW + 1) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 

@@ -418,8 +418,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tmx[w] = fmax3(tmx[w], x2.x, x2.y);
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&kv_empty[st]);
+                mbar_release_after_reads(&kv_empty[st]);      // bias tile and mask row are read
 
                 const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
                 const float m_new = fmaxf(m, tmax);

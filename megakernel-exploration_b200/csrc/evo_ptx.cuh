@@ -189,6 +189,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 // so that .sync.aligned instructions after a bounded wait stay convergent.
 __device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok) != 0; }
 
+// Hands a shared-memory buffer that this (converged) warp has READ with ordinary
+// loads back to the producer that will overwrite it through TMA.  An arrive does
+// not wait for the warp's earlier shared-memory loads to return: measured on
+// B200, a warp's loads queued behind heavy barrier polling were still pending
+// when its arrive let the producer refill the buffer, and they returned the new
+// tile.  The fence makes lane 0 wait for the warp's outstanding loads (a load
+// instruction completes for all lanes together) before the arrive.
+__device__ __forceinline__ void mbar_release_after_reads(uint64_t* bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31u) == 0u) {
+        __threadfence_block();
+        mbar_arrive(bar);
+    }
+}
+
 // ---- TMA --------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

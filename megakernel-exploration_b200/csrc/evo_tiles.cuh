@@ -56,4 +56,44 @@ __device__ __forceinline__ uint64_t sq_mnmajor(uint32_t saddr, int kb) {
     return make_smem_desc(saddr + kb * 16 * 128, SQ_SUB_BYTES, 1024, SWZ_128B);
 }
 
+// ---- split descriptors -------------------------------------------------------------
+// The thread that issues MMAs is a single thread: every integer instruction it
+// spends on building a descriptor delays the next MMA.  A descriptor's upper
+// word is a compile-time constant per operand kind, and its lower word is
+// (address >> 4) plus a constant, so an operand is addressed by ONE add on a
+// lower word prepared once per tile:  desc = {hi, lo_base + (byte offset >> 4)}.
+// (Shared-memory addresses are below 2^18, so address >> 4 fits the 14-bit field.)
+__device__ __forceinline__ uint64_t desc_join(uint32_t lo, uint32_t hi) {
+    return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes, uint32_t swz) {
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | ((swz & 7u) << 29);
+}
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return (saddr >> 4) | ((lbo_bytes >> 4) << 16);
+}
+
+template <int DH>
+struct RowDesc {
+    using RT = RowTile<DH>;
+    static constexpr uint32_t HI = desc_hi(RT::SBO, RT::SWZ);
+    __device__ static __forceinline__ uint32_t kmajor_lo(uint32_t saddr) { return desc_lo(saddr, 16); }
+    __device__ static __forceinline__ uint32_t mnmajor_lo(uint32_t saddr) { return desc_lo(saddr, RT::BYTES); }
+    // contraction block kb of an operand whose lower word is `lo`
+    __device__ static __forceinline__ uint64_t kmajor(uint32_t lo, int kb) { return desc_join(lo + kb * 2, HI); }
+    __device__ static __forceinline__ uint64_t mnmajor(uint32_t lo, int kb) {
+        return desc_join(lo + kb * static_cast<int>(RT::ROW_BYTES), HI);
+    }
+};
+
+struct SqDesc {
+    static constexpr uint32_t HI = desc_hi(1024, SWZ_128B);
+    __device__ static __forceinline__ uint32_t kmajor_lo(uint32_t saddr) { return desc_lo(saddr, 16); }
+    __device__ static __forceinline__ uint32_t mnmajor_lo(uint32_t saddr) { return desc_lo(saddr, SQ_SUB_BYTES); }
+    __device__ static __forceinline__ uint64_t kmajor(uint32_t lo, int kb) {
+        return desc_join(lo + (kb >> 2) * static_cast<int>(SQ_SUB_BYTES >> 4) + (kb & 3) * 2, HI);
+    }
+    __device__ static __forceinline__ uint64_t mnmajor(uint32_t lo, int kb) { return desc_join(lo + kb * 128, HI); }
+};
+
 }  // namespace evo
