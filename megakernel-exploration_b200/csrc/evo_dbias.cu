@@ -81,6 +81,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const DbParams p) {
     using C = DbCfg<DH, NG>;
     using RT = RowTile<DH>;
+    using RD = RowDesc<DH>;
     constexpr int QS = C::QS, CW = C::CW, NCW = C::NCW;
 
     extern __shared__ uint8_t smem_raw[];
@@ -186,13 +187,14 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         tc_fence_after();
                         const uint32_t sb = aSt + st * C::STAGE_STRIDE;
                         const uint32_t t0 = tmem + buf * 256;
-    #pragma unroll
-                        for (int kk = 0; kk < RT::KBLOCKS; ++kk)
-                            umma_ss(t0, RT::kmajor(sb + C::ST_Q, kk), RT::kmajor(sb + C::ST_K, kk), IDESC, kk > 0);
-    #pragma unroll
-                        for (int kk = 0; kk < RT::KBLOCKS; ++kk)
-                            umma_ss(t0 + 128, RT::kmajor(sb + C::ST_DO, kk), RT::kmajor(sb + C::ST_V, kk), IDESC,
-                                    kk > 0);
+                        const uint32_t q_lo = RD::kmajor_lo(sb + C::ST_Q), k_lo = RD::kmajor_lo(sb + C::ST_K);
+                        const uint32_t do_lo = RD::kmajor_lo(sb + C::ST_DO), v_lo = RD::kmajor_lo(sb + C::ST_V);
+                        // two interleaved chains: consecutive MMAs use different accumulators
+#pragma unroll
+                        for (int kk = 0; kk < RT::KBLOCKS; ++kk) {
+                            umma_ss(t0, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC, kk > 0);
+                            umma_ss(t0 + 128, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC, kk > 0);
+                        }
                         umma_commit(&sdp_full[buf]);
                         umma_commit(&st_empty[st]);
                     }
