@@ -37,6 +37,10 @@ for _p in (ROOT, PKG):
 
 import evo_workloads as wl  # noqa: E402
 
+# DRAM bytes per S row of one evo_bwd_kernel launch, from the ncu capture summarised under profiles/
+# (156.77 MB read + 56.39 MB written at 128 rows of cfg2).
+NCU_DRAM_BYTES_PER_ROW = {"cfg2_msa_row": (156.77e6 + 56.39e6) / 128}
+
 METRIC = "EvoAttention fwd+bwd TFLOP/s"
 UNIT = "TFLOP/s"
 
@@ -267,7 +271,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     achieved = bwd_flops_launch / (bwd_avg_ms * 1e-3) / 1e12 if bwd_n else None
     roofline = {
         "kernel": "evo_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": (achieved / peak) if achieved else None, "traffic": None, "peak_source": peak_src,
+        "frac": (achieved / peak) if achieved else None,
+        "traffic": (NCU_DRAM_BYTES_PER_ROW[name] * rows) if name in NCU_DRAM_BYTES_PER_ROW else None,
+        "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 128 S rows "
+                          "(profiles/evo_bwd_kernel_cfg2_rows128.md), scaled by rows: every S row is touched once",
+        "peak_source": peak_src,
         "avg_launch_ms": bwd_avg_ms, "launches_timed": bwd_n,
         "fwd_kernel": {"avg_launch_ms": fwd_ms / max(fwd_n, 1), "launches_timed": fwd_n,
                        "achieved": (4.0 * B * rows * H * N * N * D) / (fwd_ms / max(fwd_n, 1) * 1e-3) / 1e12 if fwd_n else None},

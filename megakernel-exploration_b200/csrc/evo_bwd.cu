@@ -51,8 +51,8 @@ namespace evo {
 constexpr int BWD_THREADS = 512;
 constexpr int BWD_WARP_DRAIN = 8, BWD_WARP_PRODUCER = 12, BWD_WARP_MMA = 13;
 constexpr uint32_t BWD_TMEM_COLS = 512;
-constexpr int BWD_REGS_COMPUTE = 192;
-constexpr int BWD_REGS_OTHER = 64;
+constexpr int BWD_REGS_COMPUTE = 176;
+constexpr int BWD_REGS_OTHER = 80;
 constexpr int BWD_DQ_BUFS = 2;             // dQ accumulators in tensor memory
 // the CTA's register pool is the launch count (cap for 512 threads: 128) times the threads;
 // a setmaxnreg increase that the pool cannot satisfy blocks for ever
