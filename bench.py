@@ -11,8 +11,9 @@ NCCL all-reduce of dBias in backward: "weak" keeps S rows per GPU fixed,
 "strong" splits the workload's S over the ranks.
 
 value      whole-job TFLOP/s, algorithmic FLOPs 14*B*S*H*N^2*D, inputs resident in HBM
-e2e        same metric with host (pinned) buffers: H2D of q,k,v,dO,mask,bias and
-           D2H of O,dQ,dK,dV,dBias inside the timed region
+e2e        same metric with host (pinned) buffers through HostStreamedEvoAttention.run:
+           H2D of q,k,v,dO,mask,bias and D2H of O,dQ,dK,dV,dBias inside the timed
+           region, overlapped with the kernels chunk by chunk of S rows
 roofline   backward dQ/dK/dV kernel: its 10*B*S*H*N^2*D FLOPs / its CUDA-event time,
            against the measured sustained bf16 GEMM peak
 cpu_baseline / --impl reference   the eager PyTorch restatement on the host cores
@@ -194,7 +195,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     q, k, v, mask, bias, d_o = wl.make_workload(name, lo, lo + rows, S_override=S_total)
     bf = torch.bfloat16
     # host side: pinned bf16 / fp32 buffers (what a host-buffer caller would hold)
-    h_in = [t.to(bf).pin_memory() for t in (q, k, v, d_o)] + [mask.to(bf).pin_memory(), bias.pin_memory()]
+    h_in = [t.to(bf).pin_memory() for t in (q, k, v, d_o)] + [mask.to(bf).pin_memory(), bias.to(bf).pin_memory()]
     d_in = [t.to(dev, non_blocking=True) for t in h_in]
     Q, K, V, DO, M, PB = d_in
     for t in (Q, K, V, PB):
@@ -214,15 +215,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         O.backward(DO)
         return O
 
+    # host-buffer callers: the package's streamed entry point (H2D, kernels and D2H of S-row chunks overlap)
+    from tk_evo_attention_layer import HostStreamedEvoAttention
+    eng = HostStreamedEvoAttention(dev, chunk_rows=args.e2e_chunk_rows, process_group=pg)
+    e2e_out = dict(zip(("o", "dq", "dk", "dv", "dbias"), h_out))
+
     def step_e2e():
-        ins = [h.to(dev, non_blocking=True) for h in h_in]
-        q_, k_, v_, do_, m_, pb_ = ins
-        for t in (q_, k_, v_, pb_):
-            t.requires_grad_(True)
-        O = TKEvoAttention.apply(q_, k_, v_, m_, pb_) if pg is None else TKEvoAttention.apply(q_, k_, v_, m_, pb_, pg)
-        O.backward(do_)
-        for dst, src in zip(h_out, (O.detach(), q_.grad, k_.grad, v_.grad, pb_.grad)):
-            dst.copy_(src, non_blocking=True)
+        hq, hk, hv, hdo, hm, hb = h_in
+        eng.run(hq, hk, hv, hm, hb, hdo, e2e_out)
 
     def barrier():
         if world > 1:
@@ -319,6 +319,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-chunk-rows", type=int, default=64, help="S rows per chunk of the host-streamed e2e path")
     ap.add_argument("--workload", default="cfg2_msa_row", choices=sorted(wl.WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--cpu-rows", type=int, default=64, help="S rows per CPU pass (bounded sample)")

@@ -25,6 +25,10 @@ Differences from the reference, all internal:
     over ranks: every rank passes its own rows of Q/K/V/res_mask and the full
     (replicated) pair_bias, and backward all-reduces d_pair_bias over the group.
 
+HostStreamedEvoAttention (end of this file) is an addition without a reference
+counterpart: forward + backward for callers whose tensors live in host memory,
+with the copies overlapped with the kernels.
+
 There is no CPU or eager fallback: without libevoattn.so and a CUDA device this
 module raises.
 """
@@ -169,3 +173,114 @@ class EvoAttention(torch.nn.Module):
         if self.process_group is None:
             return TKEvoAttention.apply(Q, K, V, res_mask, pair_bias)
         return TKEvoAttention.apply(Q, K, V, res_mask, pair_bias, self.process_group)
+
+
+class HostStreamedEvoAttention:
+    """Forward + backward for callers whose tensors live in HOST memory.
+
+    The reference has no such entry point: its callers hold device tensors and its
+    benchmark times device-resident calls only (evo_h100/benchmark.py:76-124).  A
+    host-buffer caller that simply copies everything in, runs the layer and copies
+    everything out spends ten times longer on the two copies than on the kernels,
+    and the copies do not overlap.  Rows of N_SEQ are independent problems, so this
+    class cuts N_SEQ into chunks and runs three streams: chunk c+1 is copied in
+    while chunk c is computed and chunk c-1 is copied out (both PCIe directions
+    busy at once); d_pair_bias is summed over the chunks on the device and copied
+    out once.
+
+        eng = HostStreamedEvoAttention(device, chunk_rows=64)
+        eng.run(q, k, v, res_mask, pair_bias, dO, out)   # all host tensors
+
+    q, k, v, dO: bf16 (B, N_SEQ, N_CTX, H, D), D in (32, 64); res_mask: bf16
+    (B, N_SEQ, 1, 1, N_CTX) or (B, N_SEQ, N_CTX); pair_bias: bf16 (B, 1, H, N, N) or
+    (B, H, N, N).  `out` = dict(o, dq, dk, dv: bf16 like q; dbias: fp32 like
+    pair_bias).  Host tensors should be pinned (page-locked), otherwise the copies
+    are synchronous.  With `process_group`, every rank passes its own rows and the
+    full pair_bias; d_pair_bias is all-reduced before it is copied out.
+    """
+
+    def __init__(self, device, chunk_rows: int = 64, process_group=None):
+        self.dev = torch.device(device)
+        if self.dev.type != "cuda":
+            raise RuntimeError("HostStreamedEvoAttention needs a CUDA device: there is no CPU path")
+        self.chunk_rows = int(chunk_rows)
+        self.pg = process_group
+        self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
+        self._key = None
+
+    def _buffers(self, B, N, H, D):
+        key = (B, N, H, D)
+        if self._key == key:
+            return
+        R, dev, bf = self.chunk_rows, self.dev, torch.bfloat16
+        dims = _evoattn.EvoDims(1, R, N, H, D)
+        self.sets = []
+        for _ in range(2):
+            s = {n: torch.empty((1, R, N, H, D), dtype=bf, device=dev)
+                 for n in ("q", "k", "v", "do", "o", "ores", "dq", "dk", "dv")}
+            s["mask"] = torch.empty((1, R, N), dtype=bf, device=dev)
+            s["lse"] = torch.empty((1, R, H, N), dtype=torch.float32, device=dev)
+            s["dbias"] = torch.empty((1, H, N, N), dtype=torch.float32, device=dev)
+            s["ws"] = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=dev)
+            s["ev_in"], s["ev_cmp"], s["ev_out"] = (torch.cuda.Event() for _ in range(3))
+            self.sets.append(s)
+        self.bias = torch.empty((B, H, N, N), dtype=bf, device=dev)
+        self.dbias = torch.empty((B, H, N, N), dtype=torch.float32, device=dev)
+        self._key = key
+
+    def run(self, q, k, v, res_mask, pair_bias, d_o, out):
+        B, S, N, H, D = q.shape
+        if D not in TK_SUPPORTED_DIMS:
+            raise ValueError(f"head_dim {D}: the host-streamed path takes D in {TK_SUPPORTED_DIMS}")
+        for t in (q, k, v, d_o):
+            assert t.shape == (B, S, N, H, D) and t.dtype == torch.bfloat16 and not t.is_cuda
+        mask = res_mask.reshape(B, S, N)
+        bias = pair_bias.reshape(B, H, N, N)
+        assert mask.dtype == torch.bfloat16 and bias.dtype == torch.bfloat16
+        dbias_out = out["dbias"].reshape(B, H, N, N)
+        self._buffers(B, N, H, D)
+        R = self.chunk_rows
+        cur = torch.cuda.current_stream(self.dev)
+        for s_ in (self.s_in, self.s_cmp, self.s_out):
+            s_.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            self.bias.copy_(bias, non_blocking=True)
+        with torch.cuda.stream(self.s_cmp):
+            self.dbias.zero_()
+        c = 0
+        for b in range(B):
+            for s0 in range(0, S, R):
+                r = min(R, S - s0)
+                st = self.sets[c & 1]
+                dims = _evoattn.EvoDims(1, r, N, H, D)
+                with torch.cuda.stream(self.s_in):
+                    if c >= 2:
+                        self.s_in.wait_event(st["ev_out"])      # this set's previous results are out
+                    for n, h in (("q", q), ("k", k), ("v", v), ("do", d_o)):
+                        st[n][:, :r].copy_(h[b:b + 1, s0:s0 + r], non_blocking=True)
+                    st["mask"][:, :r].copy_(mask[b:b + 1, s0:s0 + r], non_blocking=True)
+                    st["ev_in"].record(self.s_in)
+                with torch.cuda.stream(self.s_cmp):
+                    self.s_cmp.wait_event(st["ev_in"])
+                    h_ = self.s_cmp.cuda_stream
+                    # a chunk with fewer rows uses the leading rows of the (contiguous) buffers
+                    _evoattn.fwd(dims, st["q"], st["k"], st["v"], self.bias[b:b + 1], st["mask"], st["o"],
+                                 st["ores"], st["lse"], 0.0, h_)
+                    _evoattn.bwd(dims, st["q"], st["k"], st["v"], self.bias[b:b + 1], st["mask"], st["o"],
+                                 st["ores"], st["lse"], st["do"], st["dq"], st["dk"], st["dv"], st["dbias"],
+                                 st["ws"], 0.0, h_)
+                    self.dbias[b:b + 1].add_(st["dbias"])
+                    st["ev_cmp"].record(self.s_cmp)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(st["ev_cmp"])
+                    for n in ("o", "dq", "dk", "dv"):
+                        out[n][b:b + 1, s0:s0 + r].copy_(st[n][:, :r], non_blocking=True)
+                    st["ev_out"].record(self.s_out)
+                c += 1
+        with torch.cuda.stream(self.s_cmp):
+            if self.pg is not None:
+                import torch.distributed as dist
+                dist.all_reduce(self.dbias, group=self.pg)
+            dbias_out.copy_(self.dbias, non_blocking=True)
+        for s_ in (self.s_in, self.s_cmp, self.s_out):
+            cur.wait_stream(s_)
