@@ -313,12 +313,78 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def run_reference_sweep(args):
+    """The reference's own benchmark shapes (evo_h100/benchmark.py:38-46 with the batch of its README
+    table, evo_h100/README.md:779-812): B=4, H=16, D=64, N_SEQ=1, N_CTX swept, forward / backward /
+    full through the Python operator, wrapper included, `.grad = None` before every backward, an L2
+    flush before every timed call, median of the per-call CUDA-event times.  One JSON line."""
+    from tk_evo_attention_layer import TKEvoAttention
+    import _evoattn
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, H, D, S = 4, 16, 64, 1
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1234)
+
+    def bench(fn, iters=60, warm=15):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    rows = []
+    for N in (128, 256, 384, 512, 640, 768, 1024):
+        mk = lambda *shape: torch.randn(shape, device=dev, generator=g).to(torch.bfloat16)
+        q, k, v = (mk(B, S, N, H, D) for _ in range(3))
+        bias = mk(B, 1, H, N, N)
+        # additive mask: 0 valid / -1e9 padded, residue 0 valid (the reference benchmark passes a bool
+        # tensor that its layer turns into +0/+1; the contract of the operator is the additive mask)
+        keep = torch.rand((B, S, 1, 1, N), device=dev, generator=g) < 0.5
+        keep[..., 0] = True
+        mask = torch.where(keep, 0.0, -1e9).to(torch.bfloat16)
+        d_o = mk(B, S, N, H, D)
+        with torch.no_grad():
+            ms_f = bench(lambda: TKEvoAttention.apply(q, k, v, mask, bias))
+        leaves = [t.clone().requires_grad_(True) for t in (q, k, v, bias)]
+        o = TKEvoAttention.apply(leaves[0], leaves[1], leaves[2], mask, leaves[3])
+
+        def bwd_only():
+            for t in leaves:
+                t.grad = None
+            o.backward(d_o, retain_graph=True)
+
+        def full():
+            for t in leaves:
+                t.grad = None
+            TKEvoAttention.apply(leaves[0], leaves[1], leaves[2], mask, leaves[3]).backward(d_o)
+
+        ms_b, ms_a = bench(bwd_only), bench(full)
+        unit = B * S * H * N * N * D / 1e12
+        rows.append({"N_CTX": N, "fwd_ms": ms_f, "bwd_ms": ms_b, "full_ms": ms_a,
+                     "fwd_tflops": 4 * unit / (ms_f * 1e-3), "bwd_tflops": 10 * unit / (ms_b * 1e-3),
+                     "full_tflops": 14 * unit / (ms_a * 1e-3)})
+    _evoattn.device_status()
+    print(json.dumps({"sweep": "reference benchmark shapes", "B": B, "H": H, "D": D, "N_SEQ": S, "dtype": "bf16",
+                      "timing": "median of 60 per-call CUDA-event times, L2 flushed before each, Python wrapper included",
+                      "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sweep-reference-shapes", action="store_true",
+                    help="time the reference benchmark's own shapes (B=4,H=16,D=64,N_SEQ=1) instead of the bench line")
     ap.add_argument("--e2e-chunk-rows", type=int, default=64, help="S rows per chunk of the host-streamed e2e path")
     ap.add_argument("--workload", default="cfg2_msa_row", choices=sorted(wl.WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
@@ -332,6 +398,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.sweep_reference_shapes:
+        run_reference_sweep(args)
         return
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")

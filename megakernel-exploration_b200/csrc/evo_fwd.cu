@@ -58,13 +58,14 @@ struct FwdCfg {
     static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
     static constexpr uint32_t OFF_WMASK = OFF_XCH + 128 * XCH_PITCH;       // 8 warps x 64 floats
     static constexpr uint32_t OFF_BARS = OFF_WMASK + 8 * 256;
-    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 4 + 2 + 2 + 3;
+    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 8 + 2 + 2 + 3;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
-    static constexpr uint32_t TMEM_S = 0;
-    static constexpr uint32_t TMEM_PV = 128;                       // + g * DH
-    static constexpr uint32_t TMEM_P = 128 + 2 * DH;               // + g * 32: 64 bf16 per lane
-    static constexpr uint32_t TMEM_COLS = (TMEM_P + 64 <= 256) ? 256 : 512;
+    static constexpr uint32_t TMEM_S = 0;                          // two buffers: + (tile & 1) * 128 + g * 64
+    static constexpr uint32_t TMEM_PV = 256;                       // + g * DH
+    static constexpr uint32_t TMEM_P = 256 + 2 * DH;               // + g * 32: 64 bf16 per lane
+    static constexpr uint32_t TMEM_COLS = 512;
+    static_assert(TMEM_P + 64 <= TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
     static_assert(OFF_STAGE % 1024 == 0 && STAGE_STRIDE % 1024 == 0 && OFF_O % 1024 == 0, "tile alignment");
 };
@@ -96,9 +97,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* q_empty = bars + 2;            // [2]
     uint64_t* kv_full = bars + 4;            // [ST]
     uint64_t* kv_empty = kv_full + ST;       // [ST]
-    uint64_t* s_full = kv_empty + ST;        // [2] per softmax group
-    uint64_t* s_free = s_full + 2;           // [2]
-    uint64_t* p_ready = s_free + 2;          // [2]
+    uint64_t* s_full = kv_empty + ST;        // [4]: softmax group + 2 * S buffer
+    uint64_t* s_free = s_full + 4;           // [4]
+    uint64_t* p_ready = s_free + 4;          // [2] per softmax group
     uint64_t* pv_full = p_ready + 2;         // [2]
     uint64_t* xch_full = pv_full + 2;        // group 1 has written its partial result
     uint64_t* xch_empty = xch_full + 1;      // group 0 has read it
@@ -116,12 +117,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
         for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 9); }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&s_full[i], 1);
-            mbar_init(&s_free[i], 4);
-            mbar_init(&p_ready[i], 4);
-            mbar_init(&pv_full[i], 1);
-        }
+        for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
         mbar_init(xch_full, 4);
         mbar_init(xch_empty, 4);
         mbar_init(g0_bar, 4);
@@ -213,18 +210,19 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const int g = s_next[w];
                         const int it = g / NT, j = g - it * NT;
                         const int qb = it & 1, st = g % ST;
+                        const int sb = w + 2 * (g & 1);          // S buffer of this tile: S runs one tile ahead
                         const bool rdy = (j != 0 || mbar_test(&q_full[qb], (it >> 1) & 1)) &&
                                          mbar_test(&kv_full[st], (g / ST) & 1) &&
-                                         (g == 0 || mbar_test(&s_free[w], (g - 1) & 1));
+                                         (g < 2 || mbar_test(&s_free[sb], ((g >> 1) - 1) & 1));
                         if (rdy) {
                             tc_fence_after();
                             // K rows 64w..64w+63 of the tile: 64 rows further into the K-major tile
                             const uint32_t kt = aSt + st * C::STAGE_STRIDE + C::ST_K + w * 64 * RT::ROW_BYTES;
 #pragma unroll
                             for (int kb = 0; kb < RT::KBLOCKS; ++kb)
-                                umma_ss(tmem + C::TMEM_S + 64 * w, RT::kmajor(aQ + qb * C::ROWT, kb),
+                                umma_ss(tmem + C::TMEM_S + (g & 1) * 128 + 64 * w, RT::kmajor(aQ + qb * C::ROWT, kb),
                                         RT::kmajor(kt, kb), IDESC_S, kb > 0);
-                            umma_commit(&s_full[w]);
+                            umma_commit(&s_full[sb]);
                             ++s_next[w];
                             // Q is free once both groups' S of the item's last tile are issued
                             if (j == NT - 1 && s_next[w ^ 1] > g) umma_commit(&q_empty[qb]);
@@ -368,7 +366,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int j = 0; j < NT && ok; ++j, ++g) {
                 const int st = g % ST;
                 const uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
-                ok = warp_all(mbar_wait(&s_full[wg], g & 1, wc, 0x31));
+                const int sbuf = wg + 2 * (g & 1);
+                ok = warp_all(mbar_wait(&s_full[sbuf], (g >> 1) & 1, wc, 0x31));
                 if (!ok) break;
                 EVO_TS(t_tile);
                 tc_fence_after();
@@ -376,13 +375,13 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 {
                     uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
                     uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
-                    tmem_ld32(lane_base + C::TMEM_S + 64 * wg, lo);
-                    tmem_ld32(lane_base + C::TMEM_S + 64 * wg + 32, hi);
+                    tmem_ld32(lane_base + C::TMEM_S + (g & 1) * 128 + 64 * wg, lo);
+                    tmem_ld32(lane_base + C::TMEM_S + (g & 1) * 128 + 64 * wg + 32, hi);
                     tmem_wait_ld();
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&s_free[wg]);
+                if (lane == 0) mbar_arrive(&s_free[sbuf]);
 
                 ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x32));
                 if (!ok) break;
