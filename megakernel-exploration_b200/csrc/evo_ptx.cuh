@@ -172,6 +172,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
             EVO_T1(w.status, site);
             return true;
         }
+#ifdef EVO_WAIT_BACKOFF_NS
+        __nanosleep(EVO_WAIT_BACKOFF_NS);
+#endif
         if ((it & 63u) == 63u) {
             if (*w.abort_flag) return false;
             const uint64_t now = global_ns();
