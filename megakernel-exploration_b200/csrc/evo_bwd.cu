@@ -85,7 +85,7 @@ struct BwdCfg {
     static constexpr uint32_t WQ_BYTES = 32 * 32 * 4;
     static constexpr uint32_t OFF_WSTG = OFF_DS + SQ_BYTES;
     static constexpr uint32_t OFF_BARS = OFF_WSTG + 4 * WQ_BYTES;
-    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 8;
+    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 7 + RC;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
@@ -143,7 +143,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* pds_ready = sdp_free + 1;
     uint64_t* dq_full = pds_ready + 1;         // [2]
     uint64_t* dq_free = dq_full + 2;           // [2]
-    uint64_t* dkv_free = dq_free + 2;
+    uint64_t* dkv_free = dq_free + 2;          // [RC]: accumulators of row r of the chunk are read out
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -164,7 +164,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(sdp_free, 8);
         mbar_init(pds_ready, 8);
         for (int i = 0; i < 2; ++i) { mbar_init(&dq_full[i], 1); mbar_init(&dq_free[i], 4); }
-        mbar_init(dkv_free, 4);
+        for (int i = 0; i < RC; ++i) mbar_init(&dkv_free[i], 4);
         fence_mbar_init();
         fence_async_smem();
     }
@@ -320,7 +320,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (c.gs >= BWD_DQ_BUFS &&
                     !mbar_test(&dq_free[c.gs % BWD_DQ_BUFS], ((c.gs / BWD_DQ_BUFS) - 1) & 1))
                     return false;
-                if (c.n == 0 && c.it > 0 && !mbar_test(dkv_free, (c.it - 1) & 1)) return false;
+                // the first MMA into row r's dK/dV of an item overwrites them: the previous item's must be out
+                if (i == 0 && c.it > 0 && !mbar_test(&dkv_free[r], (c.it - 1) & 1)) return false;
                 tc_fence_after();
                 const uint32_t sb = aSt + st * C::STAGE_STRIDE;
                 const uint32_t q_lo = RD::mnmajor_lo(sb + C::ST_Q), do_lo = RD::mnmajor_lo(sb + C::ST_DO);
@@ -416,32 +417,39 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         }
                     }
                     if (n == nsteps - 1) {
-                        // the item's last MMAs are done: dK/dV -> bf16 stores
+                        // the item's last MMAs are done: dK/dV -> bf16 stores, row by row of the chunk;
+                        // each row's accumulators are handed back as soon as they are read
                         const int kvrow = x.j * TILE + wrow0 + lane;
-                        for (int t = 0; t < 2 * x.nr; ++t) {      // 2*r: dK of row r, 2*r+1: dV
-                            const float sc = (t & 1) ? 1.0f : p.scale;
-                            __nv_bfloat16* out = ((t & 1) ? p.dv : p.dk) +
-                                ((static_cast<size_t>(x.bs0 + (t >> 1)) * p.N + kvrow) * p.H + x.h) * DH;
 #pragma unroll
-                            for (int hf = 0; hf < DH / 32; ++hf) {
-                                float v[32];
-                                tmem_ld_f32<32>(lane_base + C::TMEM_DKV + (t >> 1) * 2 * DH + (t & 1) * DH + hf * 32, v);
-                                if (kvrow < p.N) {
+                        for (int rr = 0; rr < RC; ++rr) {
+                            if (rr < x.nr) {
 #pragma unroll
-                                    for (int c8 = 0; c8 < 4; ++c8) {
-                                        uint4 u;
-                                        u.x = pack_bf16(v[c8 * 8 + 0] * sc, v[c8 * 8 + 1] * sc);
-                                        u.y = pack_bf16(v[c8 * 8 + 2] * sc, v[c8 * 8 + 3] * sc);
-                                        u.z = pack_bf16(v[c8 * 8 + 4] * sc, v[c8 * 8 + 5] * sc);
-                                        u.w = pack_bf16(v[c8 * 8 + 6] * sc, v[c8 * 8 + 7] * sc);
-                                        *reinterpret_cast<uint4*>(out + hf * 32 + c8 * 8) = u;
+                                for (int t = 0; t < 2; ++t) {      // 0: dK, 1: dV
+                                    const float sc = t ? 1.0f : p.scale;
+                                    __nv_bfloat16* out = (t ? p.dv : p.dk) +
+                                        ((static_cast<size_t>(x.bs0 + rr) * p.N + kvrow) * p.H + x.h) * DH;
+#pragma unroll
+                                    for (int hf = 0; hf < DH / 32; ++hf) {
+                                        float v[32];
+                                        tmem_ld_f32<32>(lane_base + C::TMEM_DKV + rr * 2 * DH + t * DH + hf * 32, v);
+                                        if (kvrow < p.N) {
+#pragma unroll
+                                            for (int c8 = 0; c8 < 4; ++c8) {
+                                                uint4 u;
+                                                u.x = pack_bf16(v[c8 * 8 + 0] * sc, v[c8 * 8 + 1] * sc);
+                                                u.y = pack_bf16(v[c8 * 8 + 2] * sc, v[c8 * 8 + 3] * sc);
+                                                u.z = pack_bf16(v[c8 * 8 + 4] * sc, v[c8 * 8 + 5] * sc);
+                                                u.w = pack_bf16(v[c8 * 8 + 6] * sc, v[c8 * 8 + 7] * sc);
+                                                *reinterpret_cast<uint4*>(out + hf * 32 + c8 * 8) = u;
+                                            }
+                                        }
                                     }
                                 }
                             }
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&dkv_free[rr]);
                         }
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(dkv_free);
                     }
                     if (++r == x.nr) { r = 0; ++i; }
                 }
