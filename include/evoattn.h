@@ -30,6 +30,16 @@ typedef struct EvoDims {
     int32_t B, S, N, H, D;
 } EvoDims;
 
+/* Element strides of the five-dimensional activation tensors (q, k, v, o, o_resid,
+ * d_o, dq, dk, dv) along B, N_SEQ, N_CTX and H; the head dimension is always
+ * contiguous.  The contiguous layout of the reference's callers
+ * (evo_h100/tk_evo_attention_layer.py:5-11) is {S*N*H*D, N*H*D, H*D, D}.  Every
+ * stride must be a multiple of 8 elements (16 bytes), and either B == 1 or
+ * b == S * s, so that (B, N_SEQ) flatten into one axis. */
+typedef struct EvoStrides {
+    int64_t b, s, n, h;
+} EvoStrides;
+
 enum {
     EVO_OK = 0,
     EVO_ERR_BAD_DIMS = -1,      /* unsupported D / N / non-positive extent        */
@@ -63,6 +73,22 @@ const char* evo_last_error_detail(void);
 int evo_fwd(const EvoDims* dims, const void* q, const void* k, const void* v,
             const void* pair_bias, const void* res_mask, void* o, void* o_resid, float* lse,
             float scale, void* stream);
+
+/* evo_fwd / evo_bwd for activation tensors that are views with the strides given
+ * (all nine tensors share them): what the reference's callers get by transposing
+ * and copying (evo_h100/tk_evo_attention_layer.py:81-102,146-173) -- for instance the
+ * "ending node" triangle attention, whose N_SEQ and N_CTX axes are swapped in memory --
+ * is read and written in place through the tensor maps.  pair_bias, res_mask, lse,
+ * dbias and the workspace are contiguous as in evo_fwd / evo_bwd.  strides == NULL
+ * means the contiguous layout.  EVO_ERR_BAD_DIMS for strides that break the rules
+ * given at EvoStrides. */
+int evo_fwd_strided(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                    const void* v, const void* pair_bias, const void* res_mask, void* o, void* o_resid,
+                    float* lse, float scale, void* stream);
+int evo_bwd_strided(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                    const void* v, const void* pair_bias, const void* res_mask, const void* o,
+                    const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk, void* dv,
+                    float* dbias, void* workspace, size_t workspace_bytes, float scale, void* stream);
 
 /* Bytes of scratch evo_bwd needs for these dims (delta rows + fp32 dQ accumulator). */
 size_t evo_bwd_workspace_bytes(const EvoDims* dims);

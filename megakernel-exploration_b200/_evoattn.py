@@ -12,12 +12,17 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libevoattn.so")
 
-ABI_VERSION = 101
+ABI_VERSION = 102
 
 
 class EvoDims(C.Structure):
     _fields_ = [("B", C.c_int32), ("S", C.c_int32), ("N", C.c_int32),
                 ("H", C.c_int32), ("D", C.c_int32)]
+
+
+class EvoStrides(C.Structure):
+    """Element strides of the activation tensors along B, N_SEQ, N_CTX, H (D is contiguous)."""
+    _fields_ = [("b", C.c_int64), ("s", C.c_int64), ("n", C.c_int64), ("h", C.c_int64)]
 
 
 class EvoAttnError(RuntimeError):
@@ -33,6 +38,9 @@ SYMBOLS = {
     "evo_last_cuda_error": (C.c_int, []),
     "evo_last_error_detail": (C.c_char_p, []),
     "evo_fwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 8 + [C.c_float, C.c_void_p]),
+    "evo_fwd_strided": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 8 + [C.c_float, C.c_void_p]),
+    "evo_bwd_strided": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 14
+                        + [C.c_size_t, C.c_float, C.c_void_p]),
     "evo_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
     "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 14 + [C.c_size_t, C.c_float, C.c_void_p]),
     "evo_bwd_static_scratch_capacity": (C.c_size_t, []),
@@ -91,6 +99,21 @@ def _ptr(t) -> int:
 def fwd(dims: EvoDims, q, k, v, bias, mask, o, o_resid, lse, scale: float, stream: int) -> None:
     check(lib().evo_fwd(C.byref(dims), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
                         _ptr(o), _ptr(o_resid), _ptr(lse), float(scale), stream), "evo_fwd")
+
+
+def fwd_strided(dims: EvoDims, strides: EvoStrides, q, k, v, bias, mask, o, o_resid, lse, scale: float,
+                stream: int) -> None:
+    """evo_fwd on activation views that share the element strides `strides`."""
+    check(lib().evo_fwd_strided(C.byref(dims), C.byref(strides), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
+                                _ptr(o), _ptr(o_resid), _ptr(lse), float(scale), stream), "evo_fwd_strided")
+
+
+def bwd_strided(dims: EvoDims, strides: EvoStrides, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+                workspace, scale: float, stream: int) -> None:
+    check(lib().evo_bwd_strided(C.byref(dims), C.byref(strides), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask),
+                                _ptr(o), _ptr(o_resid), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv),
+                                _ptr(dbias), _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                float(scale), stream), "evo_bwd_strided")
 
 
 def bwd_workspace_bytes(dims: EvoDims) -> int:

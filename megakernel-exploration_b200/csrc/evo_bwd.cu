@@ -108,8 +108,9 @@ struct BwdParams {
     const float* nlse2;   // [B*S][H][NTP]  -LSE*log2e, -inf in the padding
     const float* delta;   // [B*S][H][NTP]  0 in the padding
     const float* maskl2;  // [B*S][NTP]     mask*log2e, -inf in the padding
-    __nv_bfloat16* dk;    // [B*S][N][H][D]
+    __nv_bfloat16* dk;    // activation layout `lay`
     __nv_bfloat16* dv;
+    ActLayout lay;        // element strides of the activation tensors
     unsigned int* status;
 };
 
@@ -426,8 +427,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                                 for (int t = 0; t < 2; ++t) {      // 0: dK, 1: dV
                                     const float sc = t ? 1.0f : p.scale;
-                                    __nv_bfloat16* out = (t ? p.dv : p.dk) +
-                                        ((static_cast<size_t>(x.bs0 + rr) * p.N + kvrow) * p.H + x.h) * DH;
+                                    __nv_bfloat16* out = (t ? p.dv : p.dk) + (x.bs0 + rr) * p.lay.row +
+                                                         kvrow * p.lay.n + x.h * p.lay.h;
 #pragma unroll
                                     for (int hf = 0; hf < DH / 32; ++hf) {
                                         float v[32];
@@ -587,7 +588,7 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
                                 const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
                                 const __nv_bfloat16* __restrict__ mask, float* __restrict__ nlse2,
                                 float* __restrict__ delta, float* __restrict__ maskl2, int BS, int N, int H,
-                                int NTP) {
+                                int NTP, ActLayout lay) {
     const size_t rows = static_cast<size_t>(BS) * N * H;
     const size_t gstride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const size_t t0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -596,9 +597,10 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
         const size_t bn = idx / H;
         const int n = static_cast<int>(bn % N);
         const size_t bs = bn / N;
-        const uint4* po = reinterpret_cast<const uint4*>(o + idx * DH);
-        const uint4* pr = o_resid ? reinterpret_cast<const uint4*>(o_resid + idx * DH) : nullptr;
-        const uint4* pd = reinterpret_cast<const uint4*>(d_o + idx * DH);
+        const size_t off = bs * lay.row + static_cast<size_t>(n) * lay.n + static_cast<size_t>(h) * lay.h;
+        const uint4* po = reinterpret_cast<const uint4*>(o + off);
+        const uint4* pr = o_resid ? reinterpret_cast<const uint4*>(o_resid + off) : nullptr;
+        const uint4* pd = reinterpret_cast<const uint4*>(d_o + off);
         float s = 0.f;
 #pragma unroll
         for (int c = 0; c < DH / 8; ++c) {
@@ -636,8 +638,10 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
     }
 }
 
-// fp32 accumulator -> bf16, 8 elements per thread
-__global__ void cvt_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n8) {
+// fp32 accumulator [B*S][N][H][D] (contiguous) -> bf16 dQ in the activation layout, 8 elements per thread
+template <int DH>
+__global__ void cvt_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n8, int N, int H,
+                              ActLayout lay) {
     const size_t gstride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += gstride) {
         const float4 a = reinterpret_cast<const float4*>(src)[2 * i];
@@ -645,7 +649,12 @@ __global__ void cvt_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __re
         uint4 u;
         u.x = pack_bf16(a.x, a.y); u.y = pack_bf16(a.z, a.w);
         u.z = pack_bf16(b.x, b.y); u.w = pack_bf16(b.z, b.w);
-        reinterpret_cast<uint4*>(dst)[i] = u;
+        const size_t rowi = i / (DH / 8);                 // (bs, n, h) of this group of eight
+        const int d8 = static_cast<int>(i % (DH / 8));
+        const int h = static_cast<int>(rowi % H);
+        const size_t bn = rowi / H;
+        const size_t off = (bn / N) * lay.row + (bn % N) * lay.n + static_cast<size_t>(h) * lay.h + d8 * 8;
+        *reinterpret_cast<uint4*>(dst + off) = u;
     }
 }
 
@@ -667,7 +676,7 @@ static BwdWorkspace bwd_workspace(const EvoDims* d) {
 }
 
 template <int DH>
-static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
+static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
                       const void* mask, const void* o, const void* o_resid, const float* lse, const void* d_o,
                       void* dq, void* dk, void* dv, float* dbias, uint8_t* ws, float scale, cudaStream_t st) {
     using C = BwdCfg<DH>;
@@ -681,10 +690,10 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
 
     CUtensorMap tq, tk, tv, tdo, tb, tdq;
     int rc;
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE, lay))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
     if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 32, 32))) return rc;
 
@@ -698,6 +707,7 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     p.c1 = p.scale * LOG2E;
     p.nlse2 = nlse2; p.delta = delta; p.maskl2 = maskl2;
     p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
+    p.lay = lay;
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
@@ -713,10 +723,10 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
         static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), nlse2, delta,
-        maskl2, BS, d->N, d->H, p.NTP);
+        maskl2, BS, d->N, d->H, p.NTP, lay);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 
-    if ((rc = launch_dbias(d, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st))) return rc;
+    if ((rc = launch_dbias(d, lay, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st))) return rc;
 
     if ((rc = cuda_err(cudaFuncSetAttribute(evo_bwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(C::SMEM_BYTES)))))
@@ -727,7 +737,7 @@ static int launch_bwd(const EvoDims* d, const void* q, const void* k, const void
     prof_end(1, st);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 
-    cvt_dq_kernel<<<sms * 8, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), dq_bytes / 32);
+    cvt_dq_kernel<DH><<<sms * 8, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), dq_bytes / 32, d->N, d->H, lay);
     return cuda_err(cudaGetLastError());
 }
 
@@ -789,8 +799,19 @@ extern "C" int evo_bwd(const EvoDims* dims, const void* q, const void* k, const 
                        const void* pair_bias, const void* res_mask, const void* o, const void* o_resid,
                        const float* lse, const void* d_o, void* dq, void* dk, void* dv, float* dbias,
                        void* workspace, size_t workspace_bytes, float scale, void* stream) {
+    return evo_bwd_strided(dims, nullptr, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+                           workspace, workspace_bytes, scale, stream);
+}
+
+extern "C" int evo_bwd_strided(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                               const void* v, const void* pair_bias, const void* res_mask, const void* o,
+                               const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk,
+                               void* dv, float* dbias, void* workspace, size_t workspace_bytes, float scale,
+                               void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
+    evo::ActLayout lay;
+    if ((rc = evo::layout_from_strides(dims, strides, &lay))) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse || !d_o || !dq || !dk || !dv || !dbias ||
         !workspace)
         return EVO_ERR_NULL_PTR;
@@ -807,8 +828,8 @@ extern "C" int evo_bwd(const EvoDims* dims, const void* q, const void* k, const 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     if (dims->D == 32)
-        return evo::launch_bwd<32>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
-                                   scale, st);
-    return evo::launch_bwd<64>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
+        return evo::launch_bwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+                                   ws, scale, st);
+    return evo::launch_bwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
                                scale, st);
 }

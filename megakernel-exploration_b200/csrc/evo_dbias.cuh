@@ -7,8 +7,8 @@ namespace evo {
 
 // dbias [B][H][N][N] fp32 must be zeroed on `st` before the call.  nlse2, delta
 // and maskl2 are the tile-padded rows the prep kernel writes (see evo_bwd.cu).
-// D is 32 or 64.
-int launch_dbias(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
+// D is 32 or 64; `lay` gives the strides of q, k, v, d_o.
+int launch_dbias(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
                  const void* d_o, const float* nlse2, const float* delta, const float* maskl2, float* dbias,
                  float scale, int sms, cudaStream_t st);
 

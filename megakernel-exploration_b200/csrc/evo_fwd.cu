@@ -77,7 +77,8 @@ struct FwdParams {
     float c1;          // scale * log2(e)
     const __nv_bfloat16* mask;   // [B*S][N]
     float* lse;                  // [B*S][H][N]
-    __nv_bfloat16* o_resid;      // [B*S][N][H][D] or nullptr
+    __nv_bfloat16* o_resid;      // activation layout `lay`, or nullptr
+    ActLayout lay;               // element strides of the activation tensors
     unsigned int* status;
 };
 
@@ -338,7 +339,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]),
                                               outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
                         __nv_bfloat16* dst =
-                            p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + c8 * 8;
+                            p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + c8 * 8;
                         *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
                     }
                 }
@@ -508,19 +509,20 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 }
 
 template <int DH>
-static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void* v, const void* bias,
-                      const void* mask, void* o, void* o_resid, float* lse, float scale, cudaStream_t st) {
+static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v,
+                      const void* bias, const void* mask, void* o, void* o_resid, float* lse, float scale,
+                      cudaStream_t st) {
     using C = FwdCfg<DH>;
     const int BS = d->B * d->S;
     const int QT = (d->N + TILE - 1) / TILE;
 
     CUtensorMap tq, tk, tv, tb, to;
     int rc;
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE, lay))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
-    if ((rc = make_tmap_qkv(&to, o, BS, d->N, d->H, DH, TILE))) return rc;
+    if ((rc = make_tmap_qkv(&to, o, BS, d->N, d->H, DH, TILE, lay))) return rc;
 
     FwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
@@ -530,6 +532,7 @@ static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void
     p.mask = static_cast<const __nv_bfloat16*>(mask);
     p.lse = lse;
     p.o_resid = static_cast<__nv_bfloat16*>(o_resid);
+    p.lay = lay;
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
@@ -551,8 +554,16 @@ static int launch_fwd(const EvoDims* d, const void* q, const void* k, const void
 extern "C" int evo_fwd(const EvoDims* dims, const void* q, const void* k, const void* v,
                        const void* pair_bias, const void* res_mask, void* o, void* o_resid, float* lse,
                        float scale, void* stream) {
+    return evo_fwd_strided(dims, nullptr, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, stream);
+}
+
+extern "C" int evo_fwd_strided(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                               const void* v, const void* pair_bias, const void* res_mask, void* o,
+                               void* o_resid, float* lse, float scale, void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
+    evo::ActLayout lay;
+    if ((rc = evo::layout_from_strides(dims, strides, &lay))) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse) return EVO_ERR_NULL_PTR;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(pair_bias) |
@@ -562,6 +573,6 @@ extern "C" int evo_fwd(const EvoDims* dims, const void* q, const void* k, const 
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dims->D == 32)
-        return evo::launch_fwd<32>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
-    return evo::launch_fwd<64>(dims, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
+        return evo::launch_fwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
+    return evo::launch_fwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
 }

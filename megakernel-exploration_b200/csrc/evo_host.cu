@@ -61,15 +61,33 @@ int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int ra
     return EVO_ERR_TENSOR_MAP;
 }
 
-int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows) {
+int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows,
+                  const ActLayout& lay) {
     const uint64_t e = 2;
     TmapDim d[4] = {
         {static_cast<uint64_t>(D), 0, static_cast<uint32_t>(D)},
-        {static_cast<uint64_t>(H), D * e, 1},
-        {static_cast<uint64_t>(N), static_cast<uint64_t>(H) * D * e, static_cast<uint32_t>(rows)},
-        {static_cast<uint64_t>(BS), static_cast<uint64_t>(N) * H * D * e, 1},
+        {static_cast<uint64_t>(H), static_cast<uint64_t>(lay.h) * e, 1},
+        {static_cast<uint64_t>(N), static_cast<uint64_t>(lay.n) * e, static_cast<uint32_t>(rows)},
+        {static_cast<uint64_t>(BS), static_cast<uint64_t>(lay.row) * e, 1},
     };
     return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, d, row_swizzle(D));
+}
+
+int layout_from_strides(const EvoDims* d, const EvoStrides* s, ActLayout* out) {
+    if (!s) {
+        *out = contiguous_layout(d->N, d->H, d->D);
+        return EVO_OK;
+    }
+    const long long st[4] = {s->b, s->s, s->n, s->h};
+    const int ext[4] = {d->B, d->S, d->N, d->H};
+    for (int i = 0; i < 4; ++i)      // an axis of extent 1 may carry any stride
+        if (ext[i] > 1 && (st[i] <= 0 || st[i] % 8 != 0)) return EVO_ERR_BAD_DIMS;
+    if (d->B > 1 && d->S > 1 && s->b != static_cast<long long>(d->S) * s->s) return EVO_ERR_BAD_DIMS;
+    out->row = (d->S > 1) ? s->s : ((d->B > 1) ? s->b : static_cast<long long>(d->N) * d->H * d->D);
+    out->n = (d->N > 1) ? s->n : static_cast<long long>(d->H) * d->D;
+    out->h = (d->H > 1) ? s->h : static_cast<long long>(d->D);
+    if (out->row % 8 || out->n % 8 || out->h % 8) return EVO_ERR_BAD_DIMS;
+    return EVO_OK;
 }
 
 int make_tmap_bias(CUtensorMap* out, const void* base, int B, int H, int N) {
@@ -197,7 +215,7 @@ int check_dims(const EvoDims* d) {
 
 extern "C" {
 
-int evo_version(void) { return 101; }
+int evo_version(void) { return 102; }
 
 int evo_last_cuda_error(void) { return evo::t_last_cuda_error; }
 

@@ -34,9 +34,20 @@ inline CUtensorMapSwizzle row_swizzle(int D) {
     return D == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
 }
 
-// bf16 [BS][N][H][D] (contiguous) viewed as (D, H, N, BS); box = one head's
-// [rows x D] tile, swizzled by row.
-int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows);
+// Element strides of an activation tensor over (flattened B*S row, residue, head); D is contiguous.
+struct ActLayout {
+    long long row, n, h;
+};
+inline ActLayout contiguous_layout(int N, int H, int D) {
+    return ActLayout{static_cast<long long>(N) * H * D, static_cast<long long>(H) * D, static_cast<long long>(D)};
+}
+// Checks EvoStrides against the rules of the header and flattens (B, S); NULL = contiguous.
+int layout_from_strides(const EvoDims* d, const EvoStrides* s, ActLayout* out);
+
+// bf16 activation tensor viewed as (D, H, N, BS) with the strides of `lay`; box = one
+// head's [rows x D] tile, swizzled by row.
+int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows,
+                  const ActLayout& lay);
 // [BS][N][H][D] of `elem_bytes`-wide elements (2: bf16, 4: fp32) with a box of
 // [rows x box_cols]; the swizzle matches the box row (32, 64 or 128 bytes).
 int make_tmap_rows_box(CUtensorMap* out, const void* base, int elem_bytes, int BS, int N, int H, int D,

@@ -130,9 +130,9 @@ template <int DH>
 static int launch_selftest(const void* x, const void* y, const void* z, float* o0, float* o1,
                            float* o2, float* o3, cudaStream_t st) {
     CUtensorMap tm_y, tm_z;
-    int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128);
+    int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH));
     if (rc) return rc;
-    rc = make_tmap_qkv(&tm_z, z, 1, 128, 1, DH, 128);
+    rc = make_tmap_qkv(&tm_z, z, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH));
     if (rc) return rc;
     unsigned int* status = status_word();
     if (!status) return EVO_ERR_CUDA;

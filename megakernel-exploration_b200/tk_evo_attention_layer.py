@@ -66,6 +66,26 @@ def _bf16c(x: torch.Tensor) -> torch.Tensor:
     return x.contiguous()
 
 
+def _shared_view_strides(Q, K, V):
+    """Strides (elements) if Q, K, V are bf16 views that the kernels can read in place: identical
+    strides, contiguous head dim, 16-byte-aligned steps, (B, N_SEQ) flattenable.  None for
+    contiguous tensors (the plain path) and for anything else (which is copied)."""
+    if Q.is_contiguous() or any(t.dtype != torch.bfloat16 for t in (Q, K, V)):
+        return None
+    st = Q.stride()
+    if K.stride() != st or V.stride() != st or st[4] != 1:
+        return None
+    B, S = Q.shape[0], Q.shape[1]
+    for ext, s in zip(Q.shape[:4], st[:4]):
+        if ext > 1 and (s <= 0 or s % 8 != 0):
+            return None
+    if B > 1 and S > 1 and st[0] != S * st[1]:
+        return None
+    if any(t.data_ptr() % 16 for t in (Q, K, V)):
+        return None
+    return tuple(st)
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -98,7 +118,10 @@ class TKEvoAttention(torch.autograd.Function):
         if N_CTX % 8 != 0:
             raise ValueError(f"N_CTX must be a multiple of 8, got {N_CTX}")
 
-        q, k, v = _bf16c(Q), _bf16c(K), _bf16c(V)
+        # Views such as the "ending node" triangle attention (N_SEQ and N_CTX swapped in memory) are
+        # read and written in place; the reference transposes and copies (layer.py:81-102).
+        strides = _shared_view_strides(Q, K, V) if padded_D == D else None
+        q, k, v = (Q, K, V) if strides is not None else (_bf16c(Q), _bf16c(K), _bf16c(V))
         if padded_D != D:
             pad = padded_D - D
             q = F.pad(q, (0, pad)).contiguous()
@@ -110,13 +133,20 @@ class TKEvoAttention(torch.autograd.Function):
         # softmax_scale is 1/sqrt(true D), not 1/sqrt(padded D) (reference layer.py:105)
         softmax_scale = 1.0 / (D ** 0.5)
 
-        o = torch.empty_like(q)
+        like = (lambda: torch.empty_strided(q.shape, strides, dtype=q.dtype, device=q.device)) \
+            if strides is not None else (lambda: torch.empty_like(q))
+        o = like()
         # rounding residual of O, kept for backward only (accurate delta -> accurate dBias)
-        o_resid = torch.empty_like(q) if any(ctx.needs_input_grad) else None
+        o_resid = like() if any(ctx.needs_input_grad) else None
         lse = torch.empty((B, N_SEQ, H, N_CTX), dtype=torch.float32, device=q.device)
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
         with _device_ctx(q):
-            _evoattn.fwd(dims, q, k, v, bias, mask, o, o_resid, lse, softmax_scale, _stream())
+            if strides is not None:
+                _evoattn.fwd_strided(dims, _evoattn.EvoStrides(*strides[:4]), q, k, v, bias, mask, o, o_resid,
+                                     lse, softmax_scale, _stream())
+            else:
+                _evoattn.fwd(dims, q, k, v, bias, mask, o, o_resid, lse, softmax_scale, _stream())
+        ctx.strides = strides
 
         ctx.save_for_backward(q, k, v, bias, mask, o, o_resid, lse)
         ctx.softmax_scale = softmax_scale
@@ -134,19 +164,31 @@ class TKEvoAttention(torch.autograd.Function):
         B, N_SEQ, N_CTX, H = ctx.dims
         D, padded_D = ctx.true_D, ctx.padded_D
 
-        d_o = _bf16c(dO)
-        if padded_D != D:
-            d_o = F.pad(d_o, (0, padded_D - D)).contiguous()
+        strides = ctx.strides
+        if strides is not None:
+            like = lambda: torch.empty_strided(q.shape, strides, dtype=q.dtype, device=q.device)
+            if dO.dtype == torch.bfloat16 and tuple(dO.stride()) == strides and dO.data_ptr() % 16 == 0:
+                d_o = dO
+            else:
+                d_o = like()
+                d_o.copy_(dO)
+        else:
+            like = lambda: torch.empty_like(q)
+            d_o = _bf16c(dO)
+            if padded_D != D:
+                d_o = F.pad(d_o, (0, padded_D - D)).contiguous()
 
-        dq = torch.empty_like(q)
-        dk = torch.empty_like(q)
-        dv = torch.empty_like(q)
+        dq, dk, dv = like(), like(), like()
         dbias = torch.empty((B, H, N_CTX, N_CTX), dtype=torch.float32, device=q.device)
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
         ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=q.device)
         with _device_ctx(q):
-            _evoattn.bwd(dims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
-                         ctx.softmax_scale, _stream())
+            if strides is not None:
+                _evoattn.bwd_strided(dims, _evoattn.EvoStrides(*strides[:4]), q, k, v, bias, mask, o, o_resid, lse,
+                                     d_o, dq, dk, dv, dbias, ws, ctx.softmax_scale, _stream())
+            else:
+                _evoattn.bwd(dims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
+                             ctx.softmax_scale, _stream())
 
         if ctx.process_group is not None:
             # rows of N_SEQ are sharded over the group; pair_bias is replicated

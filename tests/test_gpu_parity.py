@@ -184,6 +184,46 @@ def test_host_streamed_matches_layer():
     assert (out["dbias"].float() - ref["dbias"].float()).abs().max().item() <= 1e-3
 
 
+def test_transposed_view_in_place():
+    """"Ending node" layout: Q/K/V stored [B][N_CTX][N_SEQ][H][D] and passed as permuted views.  The layer
+    reads and writes them in place (strided C-ABI entry points); results must equal the contiguous call
+    bit for bit (O, dK, dV) and the returned tensors must carry the view's strides."""
+    from tk_evo_attention_layer import TKEvoAttention
+    B, S, N, H, D = 1, 24, 200, 2, 32
+    q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "tail0to32", seed=21)
+    ref = run_layer(q, k, v, mask, bias, d_o)
+    bf, dev = torch.bfloat16, "cuda"
+    # storage order [B][N][S][H][D]; the operator sees the permuted (B, S, N, H, D) view
+    mk = lambda t: t.to(dev, bf).permute(0, 2, 1, 3, 4).contiguous().permute(0, 2, 1, 3, 4).requires_grad_(True)
+    Q, K, V = mk(q), mk(k), mk(v)
+    assert not Q.is_contiguous() and Q.shape == (B, S, N, H, D)
+    PB = bias.to(dev, torch.float32).requires_grad_(True)
+    O = TKEvoAttention.apply(Q, K, V, mask.to(dev), PB)
+    assert O.stride() == Q.stride()
+    dO = d_o.to(dev, bf).permute(0, 2, 1, 3, 4).contiguous().permute(0, 2, 1, 3, 4)
+    O.backward(dO)
+    import _evoattn
+    _evoattn.device_status()
+    assert torch.equal(O.detach().float().cpu(), ref["o"])
+    assert torch.equal(K.grad.float().cpu(), ref["dk"]) and torch.equal(V.grad.float().cpu(), ref["dv"])
+    assert (Q.grad.float().cpu() - ref["dq"]).abs().max().item() <= 2.0 ** -6
+    assert (PB.grad.float().cpu() - ref["dbias"]).abs().max().item() <= 1e-3
+
+
+def test_strided_abi_rejects_bad_strides():
+    import _evoattn
+    dims = _evoattn.EvoDims(1, 4, 128, 2, 32)
+    t = torch.zeros(1, 4, 128, 2, 32, dtype=torch.bfloat16, device="cuda")
+    lse = torch.zeros(1, 4, 2, 128, device="cuda")
+    bias = torch.zeros(1, 2, 128, 128, dtype=torch.bfloat16, device="cuda")
+    mask = torch.zeros(1, 4, 128, dtype=torch.bfloat16, device="cuda")
+    bad = _evoattn.EvoStrides(0, 128 * 2 * 32, 2 * 32 + 4, 32)       # residue stride not a multiple of 8
+    with pytest.raises(_evoattn.EvoAttnError) as e:
+        _evoattn.fwd_strided(dims, bad, t, t, t, bias, mask, t, None, lse, 0.0,
+                             torch.cuda.current_stream().cuda_stream)
+    assert e.value.code == -1
+
+
 def test_c_abi_direct():
     """evo_fwd / evo_bwd called straight through ctypes with raw device pointers."""
     import _evoattn
