@@ -184,26 +184,31 @@ def test_host_streamed_matches_layer():
     assert (out["dbias"].float() - ref["dbias"].float()).abs().max().item() <= 1e-3
 
 
-def test_transposed_view_in_place():
-    """"Ending node" layout: Q/K/V stored [B][N_CTX][N_SEQ][H][D] and passed as permuted views.  The layer
-    reads and writes them in place (strided C-ABI entry points); results must equal the contiguous call
-    bit for bit (O, dK, dV) and the returned tensors must carry the view's strides."""
+@pytest.mark.parametrize("case", [
+    # (B, S, N, H, D, storage order as a permutation of (B, S, N, H, D) axes)
+    (1, 24, 200, 2, 32, (0, 2, 1, 3, 4)),     # "ending node": stored [B][N_CTX][N_SEQ][H][D]
+    (2, 5, 136, 3, 64, (0, 1, 3, 2, 4)),      # head-major, the reference kernel's own [B*S][H][N][D]
+])
+def test_permuted_view_in_place(case):
+    """Q/K/V stored in another axis order and passed as permuted (B, S, N, H, D) views.  The layer reads
+    and writes them in place (strided C-ABI entry points); results must equal the contiguous call bit
+    for bit (O, dK, dV) and the returned tensors must carry the view's strides."""
     from tk_evo_attention_layer import TKEvoAttention
-    B, S, N, H, D = 1, 24, 200, 2, 32
+    B, S, N, H, D, order = case
     q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "tail0to32", seed=21)
     ref = run_layer(q, k, v, mask, bias, d_o)
     bf, dev = torch.bfloat16, "cuda"
-    # storage order [B][N][S][H][D]; the operator sees the permuted (B, S, N, H, D) view
-    mk = lambda t: t.to(dev, bf).permute(0, 2, 1, 3, 4).contiguous().permute(0, 2, 1, 3, 4).requires_grad_(True)
-    Q, K, V = mk(q), mk(k), mk(v)
+    inv = [order.index(i) for i in range(5)]
+    view = lambda t: t.to(dev, bf).permute(*order).contiguous().permute(*inv)
+    Q, K, V = (view(t).requires_grad_(True) for t in (q, k, v))
     assert not Q.is_contiguous() and Q.shape == (B, S, N, H, D)
     PB = bias.to(dev, torch.float32).requires_grad_(True)
     O = TKEvoAttention.apply(Q, K, V, mask.to(dev), PB)
     assert O.stride() == Q.stride()
-    dO = d_o.to(dev, bf).permute(0, 2, 1, 3, 4).contiguous().permute(0, 2, 1, 3, 4)
-    O.backward(dO)
+    O.backward(view(d_o))
     import _evoattn
     _evoattn.device_status()
+    assert Q.grad.stride() == Q.stride()
     assert torch.equal(O.detach().float().cpu(), ref["o"])
     assert torch.equal(K.grad.float().cpu(), ref["dk"]) and torch.equal(V.grad.float().cpu(), ref["dv"])
     assert (Q.grad.float().cpu() - ref["dq"]).abs().max().item() <= 2.0 ** -6
