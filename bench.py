@@ -274,7 +274,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "frac": (achieved / peak) if achieved else None,
         "traffic": (NCU_DRAM_BYTES_PER_ROW[name] * rows) if name in NCU_DRAM_BYTES_PER_ROW else None,
         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 128 S rows "
-                          "(profiles/evo_bwd_kernel_cfg2_rows128.md), scaled by rows: every S row is touched once",
+                          "(summary under profiles/), scaled by rows: every S row is touched once",
         "peak_source": peak_src,
         "avg_launch_ms": bwd_avg_ms, "launches_timed": bwd_n,
         "fwd_kernel": {"avg_launch_ms": fwd_ms / max(fwd_n, 1), "launches_timed": fwd_n,

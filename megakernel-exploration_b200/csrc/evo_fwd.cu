@@ -322,6 +322,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (tid == 0) tma_wait_group_read<0>();
                 if (!g0_sync()) return false;
                 const int qrow = pqt * TILE + row;
+                __nv_bfloat16* resid_row = (p.o_resid != nullptr)
+                    ? p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h : nullptr;
 #pragma unroll
                 for (int c8 = 0; c8 < DH / 8; ++c8) {
                     uint4 v;
@@ -338,9 +340,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         for (int e = 0; e < 4; ++e)
                             rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]),
                                               outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
-                        __nv_bfloat16* dst =
-                            p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + c8 * 8;
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                        *reinterpret_cast<uint4*>(resid_row + c8 * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
                     }
                 }
                 if (qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = mt * LN2 + __logf(lt);
