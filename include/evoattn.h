@@ -90,6 +90,22 @@ int evo_bwd_strided(const EvoDims* dims, const EvoStrides* strides, const void* 
                     const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk, void* dv,
                     float* dbias, void* workspace, size_t workspace_bytes, float scale, void* stream);
 
+/* evo_bwd_strided in two separately launchable phases, for S-sharded multi-GPU
+ * callers (no counterpart in the reference, which is single-GPU):
+ *   EVO_BWD_PHASE_DBIAS  prep + the dBias kernel: dbias is complete when this phase is
+ *   EVO_BWD_PHASE_DQKV   the dQ/dK/dV kernel and the dQ conversion; needs the rows the
+ *                        first phase left in `workspace` (same workspace, same stream
+ *                        order), and leaves `reserved_sms` SMs unused
+ * so that the caller can start the all-reduce of dbias on another stream between the
+ * two calls and have it run on the reserved SMs next to the second phase.  Both bits
+ * and reserved_sms = 0 is evo_bwd_strided. */
+enum { EVO_BWD_PHASE_DBIAS = 1, EVO_BWD_PHASE_DQKV = 2 };
+int evo_bwd_phased(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                   const void* v, const void* pair_bias, const void* res_mask, const void* o,
+                   const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk, void* dv,
+                   float* dbias, void* workspace, size_t workspace_bytes, float scale, unsigned phases,
+                   int reserved_sms, void* stream);
+
 /* Bytes of scratch evo_bwd needs for these dims (delta rows + fp32 dQ accumulator). */
 size_t evo_bwd_workspace_bytes(const EvoDims* dims);
 

@@ -41,6 +41,8 @@ SYMBOLS = {
     "evo_fwd_strided": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 8 + [C.c_float, C.c_void_p]),
     "evo_bwd_strided": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 14
                         + [C.c_size_t, C.c_float, C.c_void_p]),
+    "evo_bwd_phased": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 14
+                       + [C.c_size_t, C.c_float, C.c_uint, C.c_int, C.c_void_p]),
     "evo_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
     "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 14 + [C.c_size_t, C.c_float, C.c_void_p]),
     "evo_bwd_static_scratch_capacity": (C.c_size_t, []),
@@ -114,6 +116,19 @@ def bwd_strided(dims: EvoDims, strides: EvoStrides, q, k, v, bias, mask, o, o_re
                                 _ptr(o), _ptr(o_resid), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv),
                                 _ptr(dbias), _ptr(workspace), workspace.numel() * workspace.element_size(),
                                 float(scale), stream), "evo_bwd_strided")
+
+
+BWD_PHASE_DBIAS, BWD_PHASE_DQKV = 1, 2
+
+
+def bwd_phased(dims: EvoDims, strides, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, workspace,
+               scale: float, phases: int, reserved_sms: int, stream: int) -> None:
+    """One or both phases of the backward (see evo_bwd_phased); strides may be None (contiguous)."""
+    check(lib().evo_bwd_phased(C.byref(dims), C.byref(strides) if strides is not None else None,
+                               _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask), _ptr(o), _ptr(o_resid),
+                               _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbias), _ptr(workspace),
+                               workspace.numel() * workspace.element_size(), float(scale), int(phases),
+                               int(reserved_sms), stream), "evo_bwd_phased")
 
 
 def bwd_workspace_bytes(dims: EvoDims) -> int:

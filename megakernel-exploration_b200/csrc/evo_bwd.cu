@@ -678,7 +678,8 @@ static BwdWorkspace bwd_workspace(const EvoDims* d) {
 template <int DH>
 static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
                       const void* mask, const void* o, const void* o_resid, const float* lse, const void* d_o,
-                      void* dq, void* dk, void* dv, float* dbias, uint8_t* ws, float scale, cudaStream_t st) {
+                      void* dq, void* dk, void* dv, float* dbias, uint8_t* ws, float scale, unsigned phases,
+                      int reserved_sms, cudaStream_t st) {
     using C = BwdCfg<DH>;
     const int BS = d->B * d->S;
     const int NT = (d->N + TILE - 1) / TILE;
@@ -717,21 +718,26 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
 
     const size_t dq_bytes = static_cast<size_t>(BS) * d->N * d->H * DH * 4;
     const size_t db_bytes = static_cast<size_t>(d->B) * d->H * d->N * d->N * 4;
+
+    if (phases & EVO_BWD_PHASE_DBIAS) {
+        if ((rc = cuda_err(cudaMemsetAsync(dbias, 0, db_bytes, st)))) return rc;
+        bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
+            static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), nlse2, delta,
+            maskl2, BS, d->N, d->H, p.NTP, lay);
+        if ((rc = cuda_err(cudaGetLastError()))) return rc;
+        if ((rc = launch_dbias(d, lay, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st))) return rc;
+    }
+    if (!(phases & EVO_BWD_PHASE_DQKV)) return EVO_OK;
+
     if ((rc = cuda_err(cudaMemsetAsync(dq_acc, 0, dq_bytes, st)))) return rc;
-    if ((rc = cuda_err(cudaMemsetAsync(dbias, 0, db_bytes, st)))) return rc;
-
-    bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
-        static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), nlse2, delta,
-        maskl2, BS, d->N, d->H, p.NTP, lay);
-    if ((rc = cuda_err(cudaGetLastError()))) return rc;
-
-    if ((rc = launch_dbias(d, lay, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st))) return rc;
-
     if ((rc = cuda_err(cudaFuncSetAttribute(evo_bwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(C::SMEM_BYTES)))))
         return rc;
-    const int grid = p.total_items < sms ? p.total_items : sms;
+    // SMs left to other work (a collective on another stream) while this kernel runs
+    int use_sms = sms - (reserved_sms > 0 ? reserved_sms : 0);
+    if (use_sms < 1) use_sms = 1;
+    const int grid = p.total_items < use_sms ? p.total_items : use_sms;
     prof_begin(1, st);
     evo_bwd_kernel<DH><<<grid, BWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tb, tdq, p);
     prof_end(1, st);
@@ -799,8 +805,8 @@ extern "C" int evo_bwd(const EvoDims* dims, const void* q, const void* k, const 
                        const void* pair_bias, const void* res_mask, const void* o, const void* o_resid,
                        const float* lse, const void* d_o, void* dq, void* dk, void* dv, float* dbias,
                        void* workspace, size_t workspace_bytes, float scale, void* stream) {
-    return evo_bwd_strided(dims, nullptr, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
-                           workspace, workspace_bytes, scale, stream);
+    return evo_bwd_phased(dims, nullptr, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+                          workspace, workspace_bytes, scale, EVO_BWD_PHASE_DBIAS | EVO_BWD_PHASE_DQKV, 0, stream);
 }
 
 extern "C" int evo_bwd_strided(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
@@ -808,8 +814,18 @@ extern "C" int evo_bwd_strided(const EvoDims* dims, const EvoStrides* strides, c
                                const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk,
                                void* dv, float* dbias, void* workspace, size_t workspace_bytes, float scale,
                                void* stream) {
+    return evo_bwd_phased(dims, strides, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+                          workspace, workspace_bytes, scale, EVO_BWD_PHASE_DBIAS | EVO_BWD_PHASE_DQKV, 0, stream);
+}
+
+extern "C" int evo_bwd_phased(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                              const void* v, const void* pair_bias, const void* res_mask, const void* o,
+                              const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk,
+                              void* dv, float* dbias, void* workspace, size_t workspace_bytes, float scale,
+                              unsigned phases, int reserved_sms, void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
+    if (!(phases & (EVO_BWD_PHASE_DBIAS | EVO_BWD_PHASE_DQKV))) return EVO_ERR_BAD_DIMS;
     evo::ActLayout lay;
     if ((rc = evo::layout_from_strides(dims, strides, &lay))) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse || !d_o || !dq || !dk || !dv || !dbias ||
@@ -829,7 +845,7 @@ extern "C" int evo_bwd_strided(const EvoDims* dims, const EvoStrides* strides, c
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     if (dims->D == 32)
         return evo::launch_bwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
-                                   ws, scale, st);
+                                   ws, scale, phases, reserved_sms, st);
     return evo::launch_bwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
-                               scale, st);
+                               scale, phases, reserved_sms, st);
 }

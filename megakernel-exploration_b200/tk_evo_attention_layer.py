@@ -46,6 +46,9 @@ if HERE not in sys.path:
 
 import _evoattn  # noqa: E402  (ctypes binding of libevoattn.so)
 
+# SMs the dQ/dK/dV kernel leaves to the d_pair_bias all-reduce that runs beside it (multi-GPU only).
+ALLREDUCE_RESERVED_SMS = int(os.environ.get("EVO_ALLREDUCE_RESERVED_SMS", "8"))
+
 # Head dims the kernels support natively; smaller ones are zero-padded up.
 TK_SUPPORTED_DIMS = (32, 64)
 
@@ -182,18 +185,21 @@ class TKEvoAttention(torch.autograd.Function):
         dbias = torch.empty((B, H, N_CTX, N_CTX), dtype=torch.float32, device=q.device)
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
         ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=q.device)
+        st_ = _evoattn.EvoStrides(*strides[:4]) if strides is not None else None
+        args = (dims, st_, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws, ctx.softmax_scale)
         with _device_ctx(q):
-            if strides is not None:
-                _evoattn.bwd_strided(dims, _evoattn.EvoStrides(*strides[:4]), q, k, v, bias, mask, o, o_resid, lse,
-                                     d_o, dq, dk, dv, dbias, ws, ctx.softmax_scale, _stream())
+            if ctx.process_group is None:
+                _evoattn.bwd_phased(*args, _evoattn.BWD_PHASE_DBIAS | _evoattn.BWD_PHASE_DQKV, 0, _stream())
             else:
-                _evoattn.bwd(dims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
-                             ctx.softmax_scale, _stream())
-
-        if ctx.process_group is not None:
-            # rows of N_SEQ are sharded over the group; pair_bias is replicated
-            import torch.distributed as dist
-            dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.process_group)
+                # Rows of N_SEQ are sharded over the group and pair_bias is replicated: d_pair_bias is
+                # summed over the ranks.  It is complete after the first phase, so its all-reduce runs
+                # (on the collective's own stream, on the SMs the second phase leaves free) while
+                # dQ/dK/dV are computed.
+                import torch.distributed as dist
+                _evoattn.bwd_phased(*args, _evoattn.BWD_PHASE_DBIAS, 0, _stream())
+                work = dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.process_group, async_op=True)
+                _evoattn.bwd_phased(*args, _evoattn.BWD_PHASE_DQKV, ALLREDUCE_RESERVED_SMS, _stream())
+                work.wait()
 
         if padded_D != D:
             dq, dk, dv = (t[..., :D].contiguous() for t in (dq, dk, dv))

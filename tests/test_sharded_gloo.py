@@ -39,14 +39,24 @@ def _install_cpu_doubles():
         o.copy_(evo_ref.evo_attention_ref(q.float(), k.float(), v.float(), m5, b5, scale))
         lse.copy_(evo_ref.evo_lse_ref(q.float(), k.float(), m5, b5, scale))
 
-    def fake_bwd(dims, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws, scale, stream):
+    calls = []
+
+    def fake_bwd_phased(dims, strides, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws, scale,
+                        phases, reserved_sms, stream):
+        # phase 1 (prep + dBias) and phase 2 (dQ/dK/dV) as the layer issues them around the all-reduce
+        assert strides is None
+        calls.append((phases, reserved_sms))
         B, S, N, H = dims.B, dims.S, dims.N, dims.H
         b5, m5 = bias.float().reshape(B, 1, H, N, N), mask.float().reshape(B, S, 1, 1, N)
         with torch.enable_grad():      # the oracle differentiates; autograd is off inside backward()
             r = evo_ref.evo_attention_fwd_bwd_ref(q.float(), k.float(), v.float(), m5, b5, d_o.float(), scale)
-        dq.copy_(r["dq"]); dk.copy_(r["dk"]); dv.copy_(r["dv"]); dbias.copy_(r["dbias"].reshape(B, H, N, N))
+        if phases & _evoattn.BWD_PHASE_DBIAS:
+            dbias.copy_(r["dbias"].reshape(B, H, N, N))
+        if phases & _evoattn.BWD_PHASE_DQKV:
+            dq.copy_(r["dq"]); dk.copy_(r["dk"]); dv.copy_(r["dv"])
 
-    _evoattn.fwd, _evoattn.bwd = fake_fwd, fake_bwd
+    _evoattn.fwd, _evoattn.bwd_phased = fake_fwd, fake_bwd_phased
+    L._bwd_calls = calls
     _evoattn.bwd_workspace_bytes = lambda dims: 256
     L._check_device = lambda t: None
     L._device_ctx = lambda t: contextlib.nullcontext()
@@ -67,6 +77,9 @@ def _worker(rank, world, port, out_dir):
     PB = bias.clone().requires_grad_(True)
     O = L.EvoAttention(process_group=dist.group.WORLD)(Q, K, V, mask, PB)
     O.backward(d_o.to(torch.bfloat16))
+    # with a process group the backward is issued in two phases around the all-reduce, and the second
+    # phase leaves SMs to the collective
+    assert [c[0] for c in L._bwd_calls] == [1, 2] and L._bwd_calls[1][1] == L.ALLREDUCE_RESERVED_SMS
     torch.save({"o": O.detach().float(), "dq": Q.grad.float(), "dk": K.grad.float(), "dv": V.grad.float(),
                 "dbias": PB.grad.float()}, os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
