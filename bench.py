@@ -179,7 +179,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     pg = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        pg = dist.group.WORLD
+        # the only collective of the path: the d_pair_bias all-reduce, on a group whose kernels are small
+        # enough to run beside the dQ/dK/dV kernel
+        from tk_evo_attention_layer import new_dbias_group
+        pg = new_dbias_group()
 
     name = args.workload
     B, S, N, H, D = wl.WORKLOADS[name][:5]

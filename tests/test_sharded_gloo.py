@@ -75,11 +75,11 @@ def _worker(rank, world, port, out_dir):
                                                    s_lo=lo, s_hi=lo + rows)
     Q, K, V = (t.to(torch.bfloat16).requires_grad_(True) for t in (q, k, v))
     PB = bias.clone().requires_grad_(True)
-    O = L.EvoAttention(process_group=dist.group.WORLD)(Q, K, V, mask, PB)
+    O = L.EvoAttention(process_group=L.new_dbias_group())(Q, K, V, mask, PB)
     O.backward(d_o.to(torch.bfloat16))
     # with a process group the backward is issued in two phases around the all-reduce, and the second
     # phase leaves SMs to the collective
-    assert [c[0] for c in L._bwd_calls] == [1, 2] and L._bwd_calls[1][1] == L.ALLREDUCE_RESERVED_SMS
+    assert [c[0] for c in L._bwd_calls] == [1, 2] and L._bwd_calls[1][1] == 0     # two ranks: nothing reserved
     torch.save({"o": O.detach().float(), "dq": Q.grad.float(), "dk": K.grad.float(), "dv": V.grad.float(),
                 "dbias": PB.grad.float()}, os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
