@@ -229,6 +229,44 @@ def test_strided_abi_rejects_bad_strides():
     assert e.value.code == -1
 
 
+def test_phased_backward_equals_single_call():
+    """evo_bwd_phased: the dBias phase followed by the dQ/dK/dV phase on fewer SMs (what the layer issues
+    around the all-reduce on several GPUs) gives the same dK and dV bits as evo_bwd, dBias to fp32
+    rounding and dQ to one bf16 step."""
+    import _evoattn
+    B, S, N, H, D = 1, 12, 384, 4, 32
+    q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 0.5, 1.0, "tail0to32", seed=17)
+    dev, bf = "cuda", torch.bfloat16
+    qd, kd, vd, dod = (t.to(dev, bf) for t in (q, k, v, d_o))
+    bd = bias.reshape(B, H, N, N).to(dev, bf)
+    md = mask.reshape(B, S, N).to(dev, bf)
+    dims = _evoattn.EvoDims(B, S, N, H, D)
+    st = torch.cuda.current_stream().cuda_stream
+    o, ores = torch.empty_like(qd), torch.empty_like(qd)
+    lse = torch.empty((B, S, H, N), dtype=torch.float32, device=dev)
+    _evoattn.fwd(dims, qd, kd, vd, bd, md, o, ores, lse, 0.0, st)
+    ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=dev)
+
+    def outs():
+        return [torch.full_like(qd, float("nan")) for _ in range(3)] + \
+               [torch.full((B, H, N, N), float("nan"), dtype=torch.float32, device=dev)]
+
+    a = outs()
+    _evoattn.bwd(dims, qd, kd, vd, bd, md, o, ores, lse, dod, *a, ws, 0.0, st)
+    b = outs()
+    args = (dims, None, qd, kd, vd, bd, md, o, ores, lse, dod, *b, ws, 0.0)
+    _evoattn.bwd_phased(*args, _evoattn.BWD_PHASE_DBIAS, 0, st)
+    torch.cuda.synchronize()
+    # dBias done (a sum over S slices by fp32 atomics: equal to rounding), dK untouched so far
+    assert (a[3] - b[3]).abs().max().item() <= 1e-4 and torch.isnan(b[1]).all()
+    _evoattn.bwd_phased(*args, _evoattn.BWD_PHASE_DQKV, 8, st)
+    torch.cuda.synchronize()
+    _evoattn.device_status()
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert (a[3] - b[3]).abs().max().item() <= 1e-4
+    assert (a[0].float() - b[0].float()).abs().max().item() <= 2.0 ** -6
+
+
 def test_c_abi_direct():
     """evo_fwd / evo_bwd called straight through ctypes with raw device pointers."""
     import _evoattn
