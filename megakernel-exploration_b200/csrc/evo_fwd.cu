@@ -82,7 +82,11 @@ struct FwdParams {
     unsigned int* status;
 };
 
-template <int DH>
+// STRIDED: the activation tensors are views with the strides of p.lay; otherwise they are
+// contiguous and the residual's address is formed from N and H alone.  (The generic address
+// arithmetic, in the finishing group's epilogue, cost 4-10 % of the kernel when it was the only
+// version: the contiguous case keeps its own instantiation.)
+template <int DH, bool STRIDED>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
@@ -322,8 +326,6 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (tid == 0) tma_wait_group_read<0>();
                 if (!g0_sync()) return false;
                 const int qrow = pqt * TILE + row;
-                __nv_bfloat16* resid_row = (p.o_resid != nullptr)
-                    ? p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h : nullptr;
 #pragma unroll
                 for (int c8 = 0; c8 < DH / 8; ++c8) {
                     uint4 v;
@@ -340,7 +342,12 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         for (int e = 0; e < 4; ++e)
                             rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]),
                                               outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
-                        *reinterpret_cast<uint4*>(resid_row + c8 * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                        __nv_bfloat16* dst;
+                        if constexpr (STRIDED)
+                            dst = p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + c8 * 8;
+                        else
+                            dst = p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + c8 * 8;
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
                     }
                 }
                 if (qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = mt * LN2 + __logf(lt);
@@ -539,12 +546,15 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     int dev = 0, sms = 0;
     if ((rc = cuda_err(cudaGetDevice(&dev)))) return rc;
     if ((rc = cuda_err(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))) return rc;
-    if ((rc = cuda_err(cudaFuncSetAttribute(evo_fwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    const ActLayout cl = contiguous_layout(d->N, d->H, DH);
+    const bool strided = (lay.row != cl.row || lay.n != cl.n || lay.h != cl.h);
+    auto kernel = strided ? evo_fwd_kernel<DH, true> : evo_fwd_kernel<DH, false>;
+    if ((rc = cuda_err(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(C::SMEM_BYTES)))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
     prof_begin(0, st);
-    evo_fwd_kernel<DH><<<grid, FWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tb, to, p);
+    kernel<<<grid, FWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tb, to, p);
     prof_end(0, st);
     return cuda_err(cudaGetLastError());
 }
