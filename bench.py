@@ -39,8 +39,8 @@ for _p in (ROOT, PKG):
 import evo_workloads as wl  # noqa: E402
 
 # DRAM bytes per S row of one evo_bwd_kernel launch, from the ncu capture summarised under profiles/
-# (156.88 MB read + 55.36 MB written at 128 rows of cfg2).
-NCU_DRAM_BYTES_PER_ROW = {"cfg2_msa_row": (156.88e6 + 55.36e6) / 128}
+# (156.85 MB read + 52.64 MB written at 128 rows of cfg2).
+NCU_DRAM_BYTES_PER_ROW = {"cfg2_msa_row": (156.85e6 + 52.64e6) / 128}
 
 METRIC = "EvoAttention fwd+bwd TFLOP/s"
 UNIT = "TFLOP/s"
