@@ -176,6 +176,15 @@ int evo_profile_read(int kernel, float* total_ms, int* launches);
 int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
                      float* out_xy, float* out_xty, float* out_ts, void* stream);
 
+/* Exercises the give-up path of the kernels' bounded waits without any fault (no
+ * counterpart in the reference, whose kernels wait without bound): one CTA waits on
+ * a barrier that nothing arrives at, with a limit of `limit_ns` nanoseconds
+ * (1 .. 100,000,000), records the time-out in the device status word, releases its
+ * other warp through the CTA's abort flag (*released, a device word, becomes 1) and
+ * returns normally.  evo_device_status afterwards reports EVO_ERR_DEVICE_WAIT with
+ * raw = (1 << 16) | 0xee, and clears the word. */
+int evo_selftest_wait_timeout(unsigned long long limit_ns, unsigned int* released, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -49,6 +49,7 @@ SYMBOLS = {
     "evo_bwd_static_scratch": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 13 + [C.c_float, C.c_void_p]),
     "evo_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
     "evo_selftest_mma": (C.c_int, [C.c_int] + [C.c_void_p] * 8),
+    "evo_selftest_wait_timeout": (C.c_int, [C.c_ulonglong, C.c_void_p, C.c_void_p]),
     "evo_profile_enable": (C.c_int, [C.c_int]),
     "evo_profile_read": (C.c_int, [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
 }
@@ -172,6 +173,11 @@ def profile_read(kernel: int):
     ms, n = C.c_float(0.0), C.c_int(0)
     check(lib().evo_profile_read(kernel, C.byref(ms), C.byref(n)), "evo_profile_read")
     return ms.value, n.value
+
+
+def selftest_wait_timeout(limit_ns: int, released, stream: int) -> None:
+    """Launches the one-CTA kernel whose wait runs out after `limit_ns` (see evo_selftest_wait_timeout)."""
+    check(lib().evo_selftest_wait_timeout(int(limit_ns), _ptr(released), stream), "evo_selftest_wait_timeout")
 
 
 def selftest_mma(D: int, x, y, z, out_yzt, out_xy, out_xty, out_ts, stream: int) -> None:

@@ -298,6 +298,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (KVR && c.n == 0 && !mbar_test(kv_full, c.it & 1)) return false;
                 if (c.gs > 0 && !mbar_test(sdp_free, (c.gs - 1) & 1)) return false;
                 tc_fence_after();
+                EVO_TS(t_i1);
                 const int r = c.n % c.x.nr;
                 const uint32_t sb = aSt + st * C::STAGE_STRIDE;
                 const uint32_t q_lo = RD::kmajor_lo(sb + C::ST_Q), do_lo = RD::kmajor_lo(sb + C::ST_DO);
@@ -311,6 +312,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     umma_ss(tmem + C::TMEM_DP, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC_SDP, kk > 0);
                 }
                 umma_commit(sdp_full);
+                EVO_TE(t_i1, p.status, 0xe2);
                 return true;
             };
             // dV, dK, dQ of the step under the cursor, if P/dS are out and the accumulators are free
@@ -324,6 +326,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // the first MMA into row r's dK/dV of an item overwrites them: the previous item's must be out
                 if (i == 0 && c.it > 0 && !mbar_test(&dkv_free[r], (c.it - 1) & 1)) return false;
                 tc_fence_after();
+                EVO_TS(t_i2);
                 const uint32_t sb = aSt + st * C::STAGE_STRIDE;
                 const uint32_t q_lo = RD::mnmajor_lo(sb + C::ST_Q), do_lo = RD::mnmajor_lo(sb + C::ST_DO);
                 const uint32_t k_lo = RD::mnmajor_lo(k_tile(c, r));
@@ -339,6 +342,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 umma_commit(&dq_full[c.gs % BWD_DQ_BUFS]);
                 umma_commit(&st_empty[st]);
                 if (KVR && c.n == c.nsteps - 1) umma_commit(kv_empty);
+                EVO_TE(t_i2, p.status, 0xe0);
                 return true;
             };
 
@@ -513,9 +517,11 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     uint32_t sv[16], dv[16];
+                    EVO_TS(t_ld);
                     tmem_ld16(lane_base + C::TMEM_S + 64 * wg + 16 * ch, sv);
                     tmem_ld16(lane_base + C::TMEM_DP + 64 * wg + 16 * ch, dv);
                     tmem_wait_ld();
+                    EVO_TE(t_ld, p.status, 0xb0);
                     if (ch == 3) {
                         tc_fence_before();
                         __syncwarp();
@@ -553,6 +559,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     ok = warp_all(mbar_wait(&dq_full[(gs - 1) % BWD_DQ_BUFS], ((gs - 1) / BWD_DQ_BUFS) & 1, wc, 0x61));
                     if (!ok) break;
                 }
+                EVO_TS(t_sts);
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
                     const uint32_t off = wg * SQ_SUB_BYTES + swz_off<128>(row, c8);
@@ -564,6 +571,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pds_ready);
+                EVO_TE(t_sts, p.status, 0xb3);
                 if (++r == x.nr) r = 0;
             }
         }
@@ -712,9 +720,8 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
-    int dev = 0, sms = 0;
-    if ((rc = cuda_err(cudaGetDevice(&dev)))) return rc;
-    if ((rc = cuda_err(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))) return rc;
+    int sms = 0;
+    if ((rc = sm_count(&sms))) return rc;
 
     const size_t dq_bytes = static_cast<size_t>(BS) * d->N * d->H * DH * 4;
     const size_t db_bytes = static_cast<size_t>(d->B) * d->H * d->N * d->N * 4;
@@ -731,8 +738,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     if (!(phases & EVO_BWD_PHASE_DQKV)) return EVO_OK;
 
     if ((rc = cuda_err(cudaMemsetAsync(dq_acc, 0, dq_bytes, st)))) return rc;
-    if ((rc = cuda_err(cudaFuncSetAttribute(evo_bwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(C::SMEM_BYTES)))))
+    if ((rc = set_max_smem_once(reinterpret_cast<const void*>(evo_bwd_kernel<DH>), static_cast<int>(C::SMEM_BYTES))))
         return rc;
     // SMs left to other work (a collective on another stream) while this kernel runs
     int use_sms = sms - (reserved_sms > 0 ? reserved_sms : 0);

@@ -24,6 +24,7 @@
 //                          Bias (bf16 pairs) and the running sum stay in
 //                          registers for the whole item.
 #include "evo_dbias.cuh"
+#include "evo_host.cuh"
 #include "evo_ptx.cuh"
 #include "evo_tiles.cuh"
 
@@ -368,8 +369,8 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
-    if ((rc = cuda_err(cudaFuncSetAttribute(evo_dbias_kernel<DH, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(C::SMEM_BYTES)))))
+    if ((rc = set_max_smem_once(reinterpret_cast<const void*>(evo_dbias_kernel<DH, NG>),
+                                static_cast<int>(C::SMEM_BYTES))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
     prof_begin(2, st);

@@ -379,6 +379,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ok) break;
                 EVO_TS(t_tile);
                 tc_fence_after();
+                EVO_TS(t_a);
                 uint32_t sr[64];
                 {
                     uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
@@ -390,9 +391,11 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_free[sbuf]);
+                EVO_TE(t_a, p.status, 0x70);
 
                 ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x32));
                 if (!ok) break;
+                EVO_TS(t_b);
                 {
                     // this warp's copy of the mask row slice: bf16 -> fp32 * log2e, -inf past N
                     const __nv_bfloat16* mraw = reinterpret_cast<const __nv_bfloat16*>(sb + C::ST_MASK) + 64 * wg;
@@ -403,6 +406,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                     __syncwarp();
                 }
+                EVO_TE(t_b, p.status, 0x71);
+                EVO_TS(t_c);
                 const uint8_t* sbias = sb + C::ST_BIAS + wg * SQ_SUB_BYTES;
                 // x = S*c1 + (bias*log2e + mask*log2e), two columns per instruction
                 const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
@@ -426,6 +431,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
                 mbar_release_after_reads(&kv_empty[st]);      // bias tile and mask row are read
+                EVO_TE(t_c, p.status, 0x72);
+                EVO_TS(t_d);
 
                 const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
                 const float m_new = fmaxf(m, tmax);
@@ -446,6 +453,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     l = l * alpha + ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y));
                 }
                 m = m_new;
+                EVO_TE(t_d, p.status, 0x73);
+                EVO_TS(t_e);
 
                 // The P columns in tensor memory are free once the previous tile's PV MMA is
                 // done; its result is folded in here.  On the first tile of an item that
@@ -469,6 +478,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             acc[c * 32 + i + 1] = a2.y;
                         }
                     }
+                    EVO_TE(t_e, p.status, 0x74);
                     if (j == 0) {
                         ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
                         if (!ok) break;
@@ -477,11 +487,13 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
                 // P (bf16 pairs) into this group's 32 columns of tensor memory
+                EVO_TS(t_f);
                 tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[wg]);
+                EVO_TE(t_f, p.status, 0x75);
                 EVO_TE(t_tile, p.status, 0x78);
             }
             have_prev = true;
@@ -543,14 +555,12 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
-    int dev = 0, sms = 0;
-    if ((rc = cuda_err(cudaGetDevice(&dev)))) return rc;
-    if ((rc = cuda_err(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))) return rc;
+    int sms = 0;
+    if ((rc = sm_count(&sms))) return rc;
     const ActLayout cl = contiguous_layout(d->N, d->H, DH);
     const bool strided = (lay.row != cl.row || lay.n != cl.n || lay.h != cl.h);
     auto kernel = strided ? evo_fwd_kernel<DH, true> : evo_fwd_kernel<DH, false>;
-    if ((rc = cuda_err(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(C::SMEM_BYTES)))))
+    if ((rc = set_max_smem_once(reinterpret_cast<const void*>(kernel), static_cast<int>(C::SMEM_BYTES))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
     prof_begin(0, st);

@@ -34,8 +34,34 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int rank,
-              const TmapDim* dims, CUtensorMapSwizzle swz) {
+namespace {
+// Encoded tensor maps keyed on everything the encoder sees.  A training loop calls with the same few
+// (pointer, shape, strides) combinations step after step; encoding costs microseconds per map on the
+// host, a dozen maps per step.  The cache is small and evicts round-robin.
+struct TmapKey {
+    const void* base;
+    int dt, rank, swz;
+    uint64_t extent[5], stride[5];
+    uint32_t box[5];
+    bool operator==(const TmapKey& o) const {
+        if (base != o.base || dt != o.dt || rank != o.rank || swz != o.swz) return false;
+        for (int i = 0; i < rank; ++i)
+            if (extent[i] != o.extent[i] || stride[i] != o.stride[i] || box[i] != o.box[i]) return false;
+        return true;
+    }
+};
+struct TmapEntry {
+    TmapKey key;
+    CUtensorMap map;
+};
+constexpr size_t TMAP_CACHE = 256;
+std::mutex g_tmap_mu;
+std::vector<TmapEntry> g_tmap_cache;
+size_t g_tmap_next = 0;
+}  // namespace
+
+static int encode_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int rank,
+                       const TmapDim* dims, CUtensorMapSwizzle swz) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return EVO_ERR_NO_DRIVER;
     cuuint64_t extent[5];
@@ -59,6 +85,35 @@ int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int ra
                       static_cast<unsigned long long>(dims[i].extent),
                       static_cast<unsigned long long>(i > 0 ? dims[i].stride_bytes : 0), dims[i].box);
     return EVO_ERR_TENSOR_MAP;
+}
+
+int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int rank,
+              const TmapDim* dims, CUtensorMapSwizzle swz) {
+    if (rank < 1 || rank > 5) return EVO_ERR_TENSOR_MAP;
+    TmapKey key{};
+    key.base = base; key.dt = static_cast<int>(dt); key.rank = rank; key.swz = static_cast<int>(swz);
+    for (int i = 0; i < rank; ++i) {
+        key.extent[i] = dims[i].extent;
+        key.stride[i] = i > 0 ? dims[i].stride_bytes : 0;
+        key.box[i] = dims[i].box;
+    }
+    {
+        std::lock_guard<std::mutex> lock(g_tmap_mu);
+        for (const TmapEntry& e : g_tmap_cache)
+            if (e.key == key) { *out = e.map; return EVO_OK; }
+    }
+    // A tensor map holds a virtual address and a shape, nothing device-specific: an entry encoded
+    // while one device was current is valid for the same pointer under any other.
+    const int rc = encode_tmap(out, base, dt, rank, dims, swz);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(g_tmap_mu);
+    if (g_tmap_cache.size() < TMAP_CACHE) {
+        g_tmap_cache.push_back(TmapEntry{key, *out});
+    } else {
+        g_tmap_cache[g_tmap_next] = TmapEntry{key, *out};
+        g_tmap_next = (g_tmap_next + 1) % TMAP_CACHE;
+    }
+    return EVO_OK;
 }
 
 int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows,
@@ -172,6 +227,7 @@ unsigned int* status_word() {
 namespace {
 struct ProfRec {
     std::vector<cudaEvent_t> start, stop;
+    bool armed = false;      // prof_begin pushed a pair that prof_end has not closed yet
 };
 std::mutex g_prof_mu;
 bool g_prof_on = false;
@@ -181,23 +237,67 @@ constexpr size_t PROF_MAX = 4096;
 
 void prof_begin(int kernel, cudaStream_t st) {
     std::lock_guard<std::mutex> lock(g_prof_mu);
-    if (!g_prof_on || g_prof[kernel].start.size() >= PROF_MAX) return;
+    ProfRec& r = g_prof[kernel];
+    r.armed = false;
+    if (!g_prof_on || r.start.size() >= PROF_MAX) return;
     cudaEvent_t a = nullptr, b = nullptr;
-    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
+    if (cudaEventCreate(&a) != cudaSuccess) {
         (void)cudaGetLastError();
         return;
     }
+    if (cudaEventCreate(&b) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cudaEventDestroy(a);
+        return;
+    }
     cudaEventRecord(a, st);
-    g_prof[kernel].start.push_back(a);
-    g_prof[kernel].stop.push_back(b);
+    r.start.push_back(a);
+    r.stop.push_back(b);
+    r.armed = true;
 }
 
 void prof_end(int kernel, cudaStream_t st) {
     std::lock_guard<std::mutex> lock(g_prof_mu);
     ProfRec& r = g_prof[kernel];
-    if (!g_prof_on || r.start.empty() || r.start.size() > PROF_MAX) return;
+    if (!r.armed) return;        // the matching prof_begin recorded nothing (off, full, or failed)
     cudaEventRecord(r.stop.back(), st);
+    r.armed = false;
 }
+
+// ---- per-device launch constants and the tensor-map cache ---------------------------
+int sm_count(int* out) {
+    static std::mutex mu;
+    static int cache[64] = {0};
+    int dev = 0;
+    int rc = cuda_err(cudaGetDevice(&dev));
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return EVO_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev]) {
+        int sms = 0;
+        if ((rc = cuda_err(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))) return rc;
+        cache[dev] = sms;
+    }
+    *out = cache[dev];
+    return EVO_OK;
+}
+
+int set_max_smem_once(const void* func, int bytes) {
+    // one attribute call per (device, kernel): the key is the pair, the value the size last set
+    struct Key { int dev; const void* fn; int bytes; };
+    static std::mutex mu;
+    static std::vector<Key> done;
+    int dev = 0;
+    int rc = cuda_err(cudaGetDevice(&dev));
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Key& k : done)
+        if (k.dev == dev && k.fn == func && k.bytes == bytes) return EVO_OK;
+    if ((rc = cuda_err(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes)))) return rc;
+    done.push_back(Key{dev, func, bytes});
+    return EVO_OK;
+}
+
 
 int check_dims(const EvoDims* d) {
     if (!d) return EVO_ERR_NULL_PTR;

@@ -63,6 +63,10 @@ int ensure_context();
 // Device address of this device's status word (nullptr on failure).
 unsigned int* status_word();
 int cuda_err(cudaError_t e);
+// SM count of the current device (read once per device).
+int sm_count(int* out);
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size).
+int set_max_smem_once(const void* func, int bytes);
 
 // Event pairs around the main kernels when profiling is enabled (no-ops otherwise).
 void prof_begin(int kernel, cudaStream_t st);

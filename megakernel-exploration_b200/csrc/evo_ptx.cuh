@@ -158,16 +158,16 @@ __device__ __forceinline__ uint64_t global_ns() {
     return t;
 }
 
-// Bounded wait on phase `parity` of `bar`.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
-                                          uint32_t site) {
+// Bounded wait on phase `parity` of `bar` with explicit limits (iterations, nanoseconds).
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, const WaitCtx& w,
+                                                  uint32_t site, uint32_t max_iters, uint64_t max_ns) {
     EVO_T0();
     if (mbar_try_wait(bar, parity)) {
         EVO_T1(w.status, site);
         return true;
     }
     uint64_t t0 = 0;
-    for (uint32_t it = 0; it < EVO_WAIT_LIMIT; ++it) {
+    for (uint32_t it = 0; it < max_iters; ++it) {
         if (mbar_try_wait(bar, parity)) {
             EVO_T1(w.status, site);
             return true;
@@ -179,13 +179,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
             if (*w.abort_flag) return false;
             const uint64_t now = global_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > EVO_WAIT_NS) break;
+            if (now - t0 > max_ns) break;
             if (it > 4096u) __nanosleep(64);
         }
     }
     report(w.status, ST_WAIT_TIMEOUT, site);
     *w.abort_flag = 1u;
     return false;
+}
+
+// Bounded wait on phase `parity` of `bar` (the limits every kernel of the library uses).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
+                                          uint32_t site) {
+    return mbar_wait_limited(bar, parity, w, site, EVO_WAIT_LIMIT, EVO_WAIT_NS);
 }
 
 // Makes a per-thread flag uniform across the warp (true only if true everywhere),
@@ -205,6 +211,46 @@ __device__ __forceinline__ void mbar_release_after_reads(uint64_t* bar) {
         __threadfence_block();
         mbar_arrive(bar);
     }
+}
+
+// The same hand-back without a fence.  `dep` must be computed FROM the values the last
+// loads of the buffer returned (any cheap combination of one register per load
+// instruction): the arrive takes it as an operand, so the hardware cannot issue the
+// arrive before those loads have written their registers, and a load instruction
+// completes for all lanes of the warp together.  Costs a few logic operations
+// instead of a membar (which also waits for every other outstanding access).
+__device__ __forceinline__ void mbar_release_after_loads(uint64_t* bar, uint32_t dep) {
+    __syncwarp();
+    if ((threadIdx.x & 31u) == 0u) {
+        // (dep & 0) keeps the address unchanged while carrying the dependency
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar) + (dep & 0u)) : "memory");
+    }
+}
+
+// ---- explicit shared-memory accesses ----------------------------------------------
+// Pointers into the dynamic shared-memory block are formed through integer arithmetic
+// (alignment), after which the compiler no longer knows their address space and emits
+// generic loads; these take the 32-bit shared address directly.
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t saddr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ float lds32f(uint32_t saddr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t saddr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts128f(uint32_t saddr, float4 v) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
 // ---- TMA --------------------------------------------------------------------

@@ -145,7 +145,47 @@ static int launch_selftest(const void* x, const void* y, const void* z, float* o
     return cuda_err(cudaGetLastError());
 }
 
+// A wait that nothing will ever satisfy, with a short limit: warp 0 waits on an mbarrier
+// nobody arrives at, gives up after `limit_ns`, records (ST_WAIT_TIMEOUT, site 0xee) in
+// the status word and raises the CTA's abort flag; warp 1 waits on a second such barrier
+// with the library's normal limits and must be released by the abort flag long before
+// those run out.  Then the kernel returns normally: no trap, no fault, no unbounded spin.
+__global__ void __launch_bounds__(64, 1) selftest_wait_kernel(unsigned long long limit_ns, unsigned int* status,
+                                                              unsigned int* released) {
+    __shared__ uint64_t bars[2];
+    __shared__ uint32_t abort_word;
+    volatile uint32_t* abort_flag = &abort_word;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    WaitCtx wc{abort_flag, status};
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    bool ok;
+    if (warp == 0) {
+        ok = warp_all(mbar_wait_limited(&bars[0], 0, wc, 0xee, EVO_WAIT_LIMIT, limit_ns));
+    } else {
+        ok = warp_all(mbar_wait(&bars[1], 0, wc, 0xef));
+        // released by the abort flag, not by its own limit: it never reports
+        if (!ok && tid == 32) *released = (*abort_flag != 0u) ? 1u : 0u;
+    }
+    __syncthreads();
+}
+
 }  // namespace evo
+
+extern "C" int evo_selftest_wait_timeout(unsigned long long limit_ns, unsigned int* released, void* stream) {
+    if (!released) return EVO_ERR_NULL_PTR;
+    if (limit_ns == 0 || limit_ns > 100000000ull) return EVO_ERR_BAD_DIMS;     // at most 0.1 s
+    if (int rc = evo::ensure_context()) return rc;
+    unsigned int* status = evo::status_word();
+    if (!status) return EVO_ERR_CUDA;
+    evo::selftest_wait_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, status, released);
+    return evo::cuda_err(cudaGetLastError());
+}
 
 extern "C" int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
                                 float* out_xy, float* out_xty, float* out_ts, void* stream) {

@@ -90,8 +90,11 @@ def _bf16c(x: torch.Tensor) -> torch.Tensor:
 
 def _shared_view_strides(Q, K, V):
     """Strides (elements) if Q, K, V are bf16 views that the kernels can read in place: identical
-    strides, contiguous head dim, 16-byte-aligned steps, (B, N_SEQ) flattenable.  None for
-    contiguous tensors (the plain path) and for anything else (which is copied)."""
+    strides, contiguous head dim, 16-byte-aligned steps, (B, N_SEQ) flattenable, and DENSE (a
+    permutation of a contiguous tensor: no holes, no overlap).  None for contiguous tensors (the
+    plain path) and for anything else (which is copied).  A view with holes -- q, k, v chunked out
+    of one fused projection, for instance -- is copied: outputs allocated with its strides would
+    carry the holes along and O would come back non-contiguous where the reference's never is."""
     if Q.is_contiguous() or any(t.dtype != torch.bfloat16 for t in (Q, K, V)):
         return None
     st = Q.stride()
@@ -103,6 +106,12 @@ def _shared_view_strides(Q, K, V):
             return None
     if B > 1 and S > 1 and st[0] != S * st[1]:
         return None
+    # dense: sorted by stride, every axis of extent > 1 steps by exactly the span of the inner ones
+    span = 1
+    for s_, ext in sorted((s_, ext) for s_, ext in zip(st, Q.shape) if ext > 1):
+        if s_ != span:
+            return None
+        span *= ext
     if any(t.data_ptr() % 16 for t in (Q, K, V)):
         return None
     return tuple(st)

@@ -44,3 +44,22 @@ def test_unsupported_head_dim():
     q, k, v, m, b = _inputs(D=128)
     with pytest.raises(ValueError):
         TKEvoAttention.apply(q, k, v, m, b)
+
+
+def test_strided_path_only_for_dense_views():
+    """Views the kernels read in place must be permutations of a contiguous tensor.  q, k, v chunked out
+    of one fused projection share strides but have holes: they are copied, so that O is contiguous."""
+    import tk_evo_attention_layer as L
+    bf = torch.bfloat16
+    B, S, N, H, D = 1, 4, 16, 2, 32
+    base = torch.zeros((B, N, S, H, D), dtype=bf)                 # "ending node" storage order
+    q = base.permute(0, 2, 1, 3, 4)
+    assert L._shared_view_strides(q, q, q) == tuple(q.stride())
+    qkv = torch.zeros((B, S, N, H, 3 * D), dtype=bf)
+    q, k, v = qkv.chunk(3, dim=-1)
+    assert q.stride() == k.stride() == v.stride() and not q.is_contiguous()
+    assert L._shared_view_strides(q, k, v) is None                # holes: copied, not read in place
+    t = torch.zeros((B, S, N, H, D), dtype=bf)
+    assert L._shared_view_strides(t, t, t) is None                # contiguous: the plain path
+    e = torch.zeros((B, 1, N, H, D), dtype=bf).expand(B, S, N, H, D)
+    assert L._shared_view_strides(e, e, e) is None                # overlapping (stride 0)

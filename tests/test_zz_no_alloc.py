@@ -9,8 +9,11 @@ compares every output with the regular evo_bwd on the same inputs.  dK and dV
 must agree bit for bit.  dQ and dBias are sums of fp32 reduce-adds whose order
 can differ from launch to launch, so they are compared within 2^-7 (dQ, bf16)
 and 1e-4 (dBias, fp32) -- the same slack the parity tests allow between two
-runs of the regular entry point.  It also checks that an oversized problem is
-refused.
+runs of the regular entry point.  The second call runs a smaller problem than
+the first, so the array still holds the larger problem's data beyond the new
+extents, and the amount of free device memory is read before and after that
+call: it must not move, which is the property the entry point exists for.  The
+test also checks that an oversized problem is refused.
 
 Collected last on purpose (file name), so that a failure here cannot hide the
 result of any other test in a run that stops at the first failure.
@@ -31,11 +34,11 @@ def _inputs(B, S, N, H, D, seed):
 
 def test_static_scratch_backward_matches_regular_backward():
     import _evoattn
-    B, S, N, H, D = 1, 7, 264, 3, 32        # ragged N, S not a multiple of the row chunk
-    dims = _evoattn.EvoDims(B, S, N, H, D)
-    assert _evoattn.bwd_workspace_bytes(dims) <= _evoattn.lib().evo_bwd_static_scratch_capacity()
     st = torch.cuda.current_stream().cuda_stream
-    for call in range(2):
+    # ragged N, S not a multiple of the row chunk; the second problem is smaller than the first
+    for call, (B, S, N, H, D) in enumerate([(1, 7, 264, 3, 32), (1, 4, 136, 2, 32)]):
+        dims = _evoattn.EvoDims(B, S, N, H, D)
+        assert _evoattn.bwd_workspace_bytes(dims) <= _evoattn.lib().evo_bwd_static_scratch_capacity()
         qd, kd, vd, dod, bd, md = _inputs(B, S, N, H, D, seed=100 + call)
         o, ores = torch.empty_like(qd), torch.empty_like(qd)
         lse = torch.empty((B, S, H, N), dtype=torch.float32, device="cuda")
@@ -47,8 +50,16 @@ def test_static_scratch_backward_matches_regular_backward():
 
         got = [torch.full_like(qd, float("nan")) for _ in range(3)] + \
               [torch.full((B, H, N, N), float("nan"), device="cuda")]
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         _evoattn.bwd_static_scratch(dims, qd, kd, vd, bd, md, o, ores, lse, dod, *got, 0.0, st)
+        torch.cuda.synchronize()
+        free_after = torch.cuda.mem_get_info()[0]
         _evoattn.device_status()
+        if call > 0:
+            # the first call on a device looks the array's address up (and may load the module's
+            # data); from then on a call must leave the device's free memory exactly as it was
+            assert free_after == free_before, f"device memory moved by {free_before - free_after} bytes"
 
         dq_r, dk_r, dv_r, db_r = ref
         dq_g, dk_g, dv_g, db_g = got
