@@ -176,6 +176,12 @@ int evo_profile_read(int kernel, float* total_ms, int* launches);
 int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
                      float* out_xy, float* out_xty, float* out_ts, void* stream);
 
+/* Unit check of the extra contraction block the backward kernels append to their
+ * logit products (no counterpart in the reference): y, z bf16 [128][D]; a, b bf16
+ * [128][8], 16-byte aligned; out fp32 [128][128] = y z^T + a b^T. */
+int evo_selftest_mma_extra(int D, const void* y, const void* z, const void* a, const void* b,
+                           float* out, void* stream);
+
 /* Exercises the give-up path of the kernels' bounded waits without any fault (no
  * counterpart in the reference, whose kernels wait without bound): one CTA waits on
  * a barrier that nothing arrives at, with a limit of `limit_ns` nanoseconds

@@ -49,6 +49,7 @@ SYMBOLS = {
     "evo_bwd_static_scratch": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 13 + [C.c_float, C.c_void_p]),
     "evo_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
     "evo_selftest_mma": (C.c_int, [C.c_int] + [C.c_void_p] * 8),
+    "evo_selftest_mma_extra": (C.c_int, [C.c_int] + [C.c_void_p] * 6),
     "evo_selftest_wait_timeout": (C.c_int, [C.c_ulonglong, C.c_void_p, C.c_void_p]),
     "evo_profile_enable": (C.c_int, [C.c_int]),
     "evo_profile_read": (C.c_int, [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
@@ -173,6 +174,11 @@ def profile_read(kernel: int):
     ms, n = C.c_float(0.0), C.c_int(0)
     check(lib().evo_profile_read(kernel, C.byref(ms), C.byref(n)), "evo_profile_read")
     return ms.value, n.value
+
+
+def selftest_mma_extra(D: int, y, z, a, b, out, stream: int) -> None:
+    check(lib().evo_selftest_mma_extra(int(D), _ptr(y), _ptr(z), _ptr(a), _ptr(b), _ptr(out), stream),
+          "evo_selftest_mma_extra")
 
 
 def selftest_wait_timeout(limit_ns: int, released, stream: int) -> None:

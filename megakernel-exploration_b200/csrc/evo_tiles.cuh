@@ -56,6 +56,19 @@ __device__ __forceinline__ uint64_t sq_mnmajor(uint32_t saddr, int kb) {
     return make_smem_desc(saddr + kb * 16 * 128, SQ_SUB_BYTES, 1024, SWZ_128B);
 }
 
+// EXTRA TILE [128 rows][8 bf16]: 16-byte rows, dense (2 KB): the canonical un-swizzled
+//   K-major layout with one 16-byte chunk per row (eight rows = one contiguous 128-byte
+//   core matrix).  A UMMA contraction block is 16 bf16 = two chunks; the second chunk
+//   (k = 8..15) is read from a zero-filled 2 KB tile at a HIGHER shared address, reached
+//   through the descriptor's leading-dimension offset.  An extra tile appended to a
+//   contraction adds rank-8 terms a[m, 0..7] . b[n, 0..7] to the product: per-row and
+//   per-column additive terms (mask, -LSE, -delta) then come out of the tensor core
+//   already summed into the logits instead of costing an add per element.
+constexpr uint32_t XT_BYTES = 2048;
+__device__ __forceinline__ uint64_t xt_desc(uint32_t saddr, uint32_t zero_saddr) {
+    return make_smem_desc(saddr, zero_saddr - saddr, 128, SWZ_NONE);
+}
+
 // ---- split descriptors -------------------------------------------------------------
 // The thread that issues MMAs is a single thread: every integer instruction it
 // spends on building a descriptor delays the next MMA.  A descriptor's upper

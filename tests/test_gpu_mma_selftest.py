@@ -29,3 +29,32 @@ def test_mma_operand_layouts(D):
         err = (ref - got.double().cpu()).abs().max().item()
         # bf16 products are exact in fp32; only the accumulation order differs
         assert err < 1e-3, f"D={D} {name}: max abs err {err}"
+
+
+@pytest.mark.parametrize("D", [32, 64])
+def test_extra_contraction_block(D):
+    """y z^T + a b^T with a, b as [128][8] extra tiles (un-swizzled 16-byte rows, second half of the
+    contraction block read from a zero tile): the form in which the backward kernels add the mask,
+    -LSE and -delta terms inside the tensor core.  Includes the large finite padding value."""
+    import _evoattn
+    g = torch.Generator().manual_seed(70 + D)
+    bf = torch.bfloat16
+    y = torch.randn((128, D), generator=g).to(bf)
+    z = torch.randn((128, D), generator=g).to(bf)
+    a = (torch.randn((128, 8), generator=g) * 10).to(bf)
+    b = (torch.randn((128, 8), generator=g) * 10).to(bf)
+    a[5, :] = 0
+    a[5, 2] = -1e30                     # a padded row: very negative, finite
+    b[:, 2] = 1
+    dev = "cuda"
+    out = torch.full((128, 128), float("nan"), device=dev)
+    _evoattn.selftest_mma_extra(D, y.to(dev), z.to(dev), a.to(dev), b.to(dev), out,
+                                torch.cuda.current_stream().cuda_stream)
+    _evoattn.device_status()
+    ref = y.double() @ z.double().T + a.double() @ b.double().T
+    got = out.double().cpu()
+    keep = torch.ones(128, dtype=torch.bool)
+    keep[5] = False
+    err = (ref[keep] - got[keep]).abs().max().item()
+    assert err < 2e-2, f"D={D}: max abs err {err}"          # fp32 accumulation of terms up to ~1e3
+    assert (got[5] < -1e29).all() and torch.isfinite(got[5]).all()
