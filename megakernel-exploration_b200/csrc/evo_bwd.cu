@@ -66,16 +66,16 @@ struct BwdCfg {
     static constexpr bool KV_RESIDENT = (DH == 64);
     static constexpr int HALF = DH / 2;               // head-dim columns drained per group
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;
-    // one stage: Q, dO [, K, V] tiles, then -LSE*log2e[128], delta[128] [, mask*log2e[128]]
+    // one stage: Q, dO [, K, V] tiles, then the extra tile of the q rows [and of the kv rows]
     static constexpr uint32_t ST_Q = 0, ST_DO = ROWT;
     static constexpr uint32_t ST_K = 2 * ROWT, ST_V = 3 * ROWT;            // streaming only
     static constexpr uint32_t ST_TILES = KV_RESIDENT ? 2 : 4;
-    static constexpr uint32_t ST_ROWV = ST_TILES * ROWT, ST_MASK = ST_ROWV + 1024;
-    static constexpr uint32_t STAGE_TX = ST_TILES * ROWT + (KV_RESIDENT ? 1024 : 1536);
-    static constexpr uint32_t STAGE_STRIDE = ST_TILES * ROWT + 2048;
-    // resident K/V buffer: K[RC], V[RC], mask rows [RC][128]
-    static constexpr uint32_t KV_BYTES = KV_RESIDENT ? (2 * RC * ROWT + 1024) : 0;
-    static constexpr uint32_t KV_TX = 2 * ROWT + 512;                       // per row of the chunk
+    static constexpr uint32_t ST_XQ = ST_TILES * ROWT, ST_XK = ST_XQ + XT_BYTES;
+    static constexpr uint32_t STAGE_TX = ST_TILES * ROWT + (KV_RESIDENT ? 1 : 2) * XT_BYTES;
+    static constexpr uint32_t STAGE_STRIDE = ST_TILES * ROWT + 2 * XT_BYTES;
+    // resident K/V buffer: K[RC], V[RC], extra tiles of the kv rows [RC]
+    static constexpr uint32_t KV_BYTES = KV_RESIDENT ? (2 * RC * ROWT + RC * XT_BYTES) : 0;
+    static constexpr uint32_t KV_TX = 2 * ROWT + XT_BYTES;                  // per row of the chunk
     static constexpr uint32_t OFF_STAGE = 0;
     static constexpr uint32_t OFF_KV = OFF_STAGE + QS * STAGE_STRIDE;
     static constexpr uint32_t OFF_BIAS = OFF_KV + KV_BYTES;
@@ -84,7 +84,10 @@ struct BwdCfg {
     // per drain warp: dQ slot [32 rows][32 fp32]
     static constexpr uint32_t WQ_BYTES = 32 * 32 * 4;
     static constexpr uint32_t OFF_WSTG = OFF_DS + SQ_BYTES;
-    static constexpr uint32_t OFF_BARS = OFF_WSTG + 4 * WQ_BYTES;
+    // constant extra tiles, above every tile that refers to the zero tile
+    static constexpr uint32_t OFF_XDP = OFF_WSTG + 4 * WQ_BYTES;            // column selector of -delta
+    static constexpr uint32_t OFF_ZERO = OFF_XDP + XT_BYTES;
+    static constexpr uint32_t OFF_BARS = OFF_ZERO + XT_BYTES;
     static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 7 + RC;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + alignment slack
@@ -105,9 +108,8 @@ struct BwdParams {
     int total_items; // B * CPB * H * NT
     float scale;     // softmax scale
     float c1;        // scale * log2(e)
-    const float* nlse2;   // [B*S][H][NTP]  -LSE*log2e, -inf in the padding
-    const float* delta;   // [B*S][H][NTP]  0 in the padding
-    const float* maskl2;  // [B*S][NTP]     mask*log2e, -inf in the padding
+    const __nv_bfloat16* xq;   // [B*S][H][NTP][8] extra tiles of the q rows  (bwd_prep_kernel)
+    const __nv_bfloat16* xk;   // [B*S][NTP][8]    extra tiles of the kv rows
     __nv_bfloat16* dk;    // activation layout `lay`
     __nv_bfloat16* dv;
     ActLayout lay;        // element strides of the activation tensors
@@ -156,9 +158,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 9); }
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1); }
         mbar_init(kv_full, 1);
-        mbar_init(kv_empty, 9);
+        mbar_init(kv_empty, 1);
         mbar_init(bias_full, 1);
         mbar_init(bias_empty, 8);
         mbar_init(sdp_full, 1);
@@ -177,6 +179,12 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
         prefetch_tmap(&tm_bias); prefetch_tmap(&tm_dq);
     }
+    // constant extra tiles: row n of the -delta selector is (0,0,0,0,1,1,0,0); the zero tile
+    if (tid < 128) {
+        *reinterpret_cast<uint4*>(smem + C::OFF_XDP + tid * 16) = make_uint4(0u, 0u, 0x3f803f80u, 0u);
+        *reinterpret_cast<uint4*>(smem + C::OFF_ZERO + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_async_smem();
     EVO_TRACE_INIT();
     tc_fence_before();
     __syncthreads();
@@ -221,8 +229,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     for (int r = 0; r < x.nr; ++r) {
                         tma_load_4d(kvb + r * C::ROWT, &tm_k, kv_full, 0, x.h, x.j * TILE, x.bs0 + r);
                         tma_load_4d(kvb + (RC + r) * C::ROWT, &tm_v, kv_full, 0, x.h, x.j * TILE, x.bs0 + r);
-                        bulk_load(kvb + 2 * RC * C::ROWT + r * 512,
-                                  p.maskl2 + static_cast<size_t>(x.bs0 + r) * p.NTP + x.j * TILE, 512, kv_full);
+                        bulk_load(kvb + 2 * RC * C::ROWT + r * XT_BYTES,
+                                  p.xk + (static_cast<size_t>(x.bs0 + r) * p.NTP + x.j * TILE) * 8, XT_BYTES, kv_full);
                     }
                 }
                 for (int n = 0; n < nsteps && ok; ++n, ++gs) {
@@ -247,12 +255,11 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (!KVR) {
                         tma_load_4d(sb + C::ST_K, &tm_k, &st_full[st], 0, x.h, x.j * TILE, bs);
                         tma_load_4d(sb + C::ST_V, &tm_v, &st_full[st], 0, x.h, x.j * TILE, bs);
-                        bulk_load(sb + C::ST_MASK, p.maskl2 + static_cast<size_t>(bs) * p.NTP + x.j * TILE, 512,
+                        bulk_load(sb + C::ST_XK, p.xk + (static_cast<size_t>(bs) * p.NTP + x.j * TILE) * 8, XT_BYTES,
                                   &st_full[st]);
                     }
                     const size_t ro = (static_cast<size_t>(bs) * p.H + x.h) * p.NTP + i * TILE;
-                    bulk_load(sb + C::ST_ROWV, p.nlse2 + ro, 512, &st_full[st]);
-                    bulk_load(sb + C::ST_ROWV + 512, p.delta + ro, 512, &st_full[st]);
+                    bulk_load(sb + C::ST_XQ, p.xq + ro * 8, XT_BYTES, &st_full[st]);
                 }
             }
             // Drain: the most recent loads have landed before the CTA exits.
@@ -269,6 +276,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const uint32_t p_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_P));
             const uint32_t ds_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_DS));
             const uint32_t ds_k_lo = SqDesc::kmajor_lo(smem_u32(smem + C::OFF_DS));
+            const uint32_t aZero = smem_u32(smem + C::OFF_ZERO);
+            const uint64_t d_xdp = xt_desc(smem_u32(smem + C::OFF_XDP), aZero);
 
             struct Cursor {
                 int it, n, gs, nsteps;
@@ -311,6 +320,11 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     umma_ss(tmem + C::TMEM_S, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC_SDP, kk > 0);
                     umma_ss(tmem + C::TMEM_DP, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC_SDP, kk > 0);
                 }
+                // + (mask - LSE) / scale on S, - delta on dP: the extra contraction block
+                const uint64_t d_xq = xt_desc(sb + C::ST_XQ, aZero);
+                const uint32_t xk_addr = KVR ? aKV + 2 * RC * C::ROWT + r * XT_BYTES : sb + C::ST_XK;
+                umma_ss(tmem + C::TMEM_S, d_xq, xt_desc(xk_addr, aZero), IDESC_SDP, 1u);
+                umma_ss(tmem + C::TMEM_DP, d_xq, d_xdp, IDESC_SDP, 1u);
                 umma_commit(sdp_full);
                 EVO_TE(t_i1, p.status, 0xe2);
                 return true;
@@ -468,89 +482,73 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int row = tid & 127;           // q row within the tile == TMEM lane
         const int wrow0 = (warp & 3) * 32;   // first tile row of this warp
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(wrow0) << 16);
-        uint8_t* sP = smem + C::OFF_P;
-        uint8_t* sDS = smem + C::OFF_DS;
+        const uint32_t aP = smem_u32(smem + C::OFF_P) + wg * SQ_SUB_BYTES;
+        const uint32_t aDS = smem_u32(smem + C::OFF_DS) + wg * SQ_SUB_BYTES;
+        const uint32_t aBias = smem_u32(smem + C::OFF_BIAS) + wg * SQ_SUB_BYTES;
+        const uint32_t scratch_w = smem_u32(tmem_slot + 2);       // a word nobody reads
         bool ok = true;
         int gs = 0, gb = 0;
+        const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
 
         uint32_t bias_pk[32];                // this thread's 64 bias values (bf16 pairs)
 
         for (int it = 0; it < n_items && ok; ++it) {
             const BwdItem x = decode(it);
             const int nsteps = NT * x.nr;
-            if (KVR) {
-                ok = warp_all(mbar_wait(kv_full, it & 1, wc, 0x62));     // mask rows of this item
-                if (!ok) break;
-            }
             int r = 0;                       // row of the chunk, innermost
             for (int n = 0; n < nsteps && ok; ++n, ++gs) {
-                const int st = gs % QS;
-                const uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
                 ok = warp_all(mbar_wait(sdp_full, gs & 1, wc, 0x63));
                 if (!ok) break;
                 EVO_TS(t_cmp);
                 if (r == 0) {
                     ok = warp_all(mbar_wait(bias_full, gb & 1, wc, 0x64));
                     if (!ok) break;
-                    const uint8_t* sbias = smem + C::OFF_BIAS + wg * SQ_SUB_BYTES;
+                    uint32_t dep = 0;
 #pragma unroll
                     for (int c8 = 0; c8 < 8; ++c8) {
-                        const uint4 bv = *reinterpret_cast<const uint4*>(sbias + swz_off<128>(row, c8));
+                        const uint4 bv = lds128(aBias + swz_off<128>(row, c8));
                         bias_pk[c8 * 4 + 0] = bv.x; bias_pk[c8 * 4 + 1] = bv.y;
                         bias_pk[c8 * 4 + 2] = bv.z; bias_pk[c8 * 4 + 3] = bv.w;
+                        dep ^= bv.x;
                     }
-                    mbar_release_after_reads(bias_empty);     // the tile now lives in registers
+                    mbar_release_after_loads(bias_empty, dep, scratch_w);     // the tile now lives in registers
                     ++gb;
                 }
-                ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x65));
-                if (!ok) break;
-                const float* rowv = reinterpret_cast<const float*>(sb + C::ST_ROWV);
-                const float nl = rowv[row];          // -LSE*log2e (-inf for padded rows)
-                const float dl = rowv[128 + row];    // delta (0 for padded rows)
-                const float* mrow = (KVR ? reinterpret_cast<const float*>(smem + C::OFF_KV + 2 * RC * C::ROWT) + r * 128
-                                         : reinterpret_cast<const float*>(sb + C::ST_MASK)) + 64 * wg;
 
+                // Per element: x = S' c1 + bias log2e (S' already carries mask and -LSE through the
+                // extra contraction block), P = exp2(x), dS = P dP' (dP' already carries -delta).
+                // Chunks of 16 columns; the tensor-memory loads of chunk ch+1 are in flight during
+                // the arithmetic of chunk ch.
                 uint32_t pkp[32], pkd[32];           // P and dS of this thread's 64 columns, bf16 pairs
-                const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
-                const float2 nl2 = make_float2(nl, nl), ndl2 = make_float2(-dl, -dl);
+                uint32_t sv[2][16], dv[2][16];
                 tc_fence_after();
+                tmem_ld16(lane_base + C::TMEM_S + 64 * wg, sv[0]);
+                tmem_ld16(lane_base + C::TMEM_DP + 64 * wg, dv[0]);
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t sv[16], dv[16];
-                    EVO_TS(t_ld);
-                    tmem_ld16(lane_base + C::TMEM_S + 64 * wg + 16 * ch, sv);
-                    tmem_ld16(lane_base + C::TMEM_DP + 64 * wg + 16 * ch, dv);
+                    const int cb = ch & 1;
                     tmem_wait_ld();
-                    EVO_TE(t_ld, p.status, 0xb0);
-                    if (ch == 3) {
+                    if (ch < 3) {
+                        tmem_ld16(lane_base + C::TMEM_S + 64 * wg + 16 * (ch + 1), sv[cb ^ 1]);
+                        tmem_ld16(lane_base + C::TMEM_DP + 64 * wg + 16 * (ch + 1), dv[cb ^ 1]);
+                    } else {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(sdp_free);
                     }
+                    float2 p2[8];
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        // two columns per instruction: x = S*c1 + (bias*log2e + mask*log2e) - LSE*log2e,
-                        // P = exp2(x), dS = P * (dP - delta)
-                        const float4 mv = *reinterpret_cast<const float4*>(mrow + 16 * ch + q4 * 4);
-                        const float2 mm[2] = {make_float2(mv.x, mv.y), make_float2(mv.z, mv.w)};
-#pragma unroll
-                        for (int w = 0; w < 2; ++w) {
-                            const int c = q4 * 4 + 2 * w;                 // 0..14 within this chunk
-                            const float2 t2 = ffma2(bf16x2_f2(bias_pk[ch * 8 + q4 * 2 + w]), l2e2, mm[w]);
-                            const float2 x2 = fadd2(ffma2(u2f2(sv[c], sv[c + 1]), c1x2, t2), nl2);
-                            const float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
-                            const float2 ds2 = fmul2(p2, fadd2(u2f2(dv[c], dv[c + 1]), ndl2));
-                            pkp[ch * 8 + q4 * 2 + w] = pack_bf16(p2.x, p2.y);
-                            pkd[ch * 8 + q4 * 2 + w] = pack_bf16(ds2.x, ds2.y);
-                        }
+                    for (int k = 0; k < 8; ++k) {
+                        const float2 b2 = fmul2(bf16x2_f2(bias_pk[ch * 8 + k]), l2e2);
+                        const float2 x2 = ffma2(u2f2(sv[cb][2 * k], sv[cb][2 * k + 1]), c1x2, b2);
+                        p2[k] = make_float2(ex2(x2.x), ex2(x2.y));
                     }
-                }
-                // the rows (and mask) of the stage and the resident mask rows are read
-                __syncwarp();
-                if (lane == 0) {
-                    __threadfence_block();     // see mbar_release_after_reads
-                    mbar_arrive(&st_empty[st]);
-                    if (KVR && n == nsteps - 1) mbar_arrive(kv_empty);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const float2 ds2 = fmul2(p2[k], u2f2(dv[cb][2 * k], dv[cb][2 * k + 1]));
+                        pkp[ch * 8 + k] = pack_bf16(p2[k].x, p2[k].y);
+                        pkd[ch * 8 + k] = pack_bf16(ds2.x, ds2.y);
+                    }
                 }
                 EVO_TE(t_cmp, p.status, 0x70);
 
@@ -562,11 +560,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 EVO_TS(t_sts);
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
-                    const uint32_t off = wg * SQ_SUB_BYTES + swz_off<128>(row, c8);
-                    *reinterpret_cast<uint4*>(sP + off) =
-                        make_uint4(pkp[c8 * 4 + 0], pkp[c8 * 4 + 1], pkp[c8 * 4 + 2], pkp[c8 * 4 + 3]);
-                    *reinterpret_cast<uint4*>(sDS + off) =
-                        make_uint4(pkd[c8 * 4 + 0], pkd[c8 * 4 + 1], pkd[c8 * 4 + 2], pkd[c8 * 4 + 3]);
+                    const uint32_t off = swz_off<128>(row, c8);
+                    sts128(aP + off, make_uint4(pkp[c8 * 4 + 0], pkp[c8 * 4 + 1], pkp[c8 * 4 + 2], pkp[c8 * 4 + 3]));
+                    sts128(aDS + off, make_uint4(pkd[c8 * 4 + 0], pkd[c8 * 4 + 1], pkd[c8 * 4 + 2], pkd[c8 * 4 + 3]));
                 }
                 fence_async_smem();
                 __syncwarp();
@@ -586,17 +582,36 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 // ---------------------------------------------------------------------------
 // prep: delta = rowsum(dO o O) (replaces evo_bwd_prep_ker, tk_evoattention.cu:352-416),
-// plus the pre-scaled, tile-padded LSE and mask rows the main kernel streams.
+// and the extra tiles through which the main kernels add every per-row and per-column
+// term of the logits inside the tensor core (evo_tiles.cuh, "EXTRA TILE"):
+//
+//   xq [B*S][H][NTP][8] bf16, row q:  ( 1, 1, a_hi, a_lo, -d_hi, -d_lo, 0, 0 )   a = -LSE / scale
+//   xk [B*S][NTP][8]    bf16, row kv: ( m_hi, m_lo, 1, 1, 0, 0, 0, 0 )           m = mask / scale
+//
+// so that  Q K^T + xq xk^T = Q K^T + (mask - LSE) / scale  (times scale*log2e: the base-2
+// logit minus the base-2 LSE) and  dO V^T + xq (0,0,0,0,1,1,0,0)^T = dP - delta.
+// Values are split into a bf16 head and a bf16 remainder (16 significant bits).  Rows
+// past N (padding up to whole tiles, NTP = tiles * 128) get a = m = -1e30: finite, so
+// that a product with a zero of the other tile stays zero, and far below any logit.
 // With o_resid (the bf16 rounding residual of O written by the forward), delta
 // uses O to about 16 bits instead of 8: the rounding of O otherwise puts an
 // error of order 2^-9 |dO||O| on every dS, which adds up over the S rows of dBias.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t split_bf16(float v) {
+    // (head, remainder) as a bf16 pair, head in the low half
+    v = fminf(fmaxf(v, -1e30f), 1e30f);
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+    return static_cast<uint32_t>(__bfloat16_as_ushort(hi)) | (static_cast<uint32_t>(__bfloat16_as_ushort(lo)) << 16);
+}
+
 template <int DH>
 __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ o_resid,
                                 const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
-                                const __nv_bfloat16* __restrict__ mask, float* __restrict__ nlse2,
-                                float* __restrict__ delta, float* __restrict__ maskl2, int BS, int N, int H,
+                                const __nv_bfloat16* __restrict__ mask, uint4* __restrict__ xq,
+                                uint4* __restrict__ xk, float inv_scale, int BS, int N, int H,
                                 int NTP, ActLayout lay) {
+    constexpr uint32_t ONES = 0x3f803f80u;     // bf16 (1, 1)
     const size_t rows = static_cast<size_t>(BS) * N * H;
     const size_t gstride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const size_t t0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -626,23 +641,22 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
             }
         }
         const size_t ro = (bs * H + h) * NTP + n;
-        delta[ro] = s;
-        nlse2[ro] = -lse[(bs * H + h) * N + n] * LOG2E;
+        xq[ro] = make_uint4(ONES, split_bf16(-lse[(bs * H + h) * N + n] * inv_scale), split_bf16(-s), 0u);
     }
-    // padding of the row vectors, and the mask rows
+    // padding of the per-row tiles, and the per-column tiles
     const int pad = NTP - N;
     const size_t npad = static_cast<size_t>(BS) * H * pad;
     for (size_t idx = t0; idx < npad; idx += gstride) {
         const size_t bh = idx / pad;
         const int n = N + static_cast<int>(idx % pad);
-        delta[bh * NTP + n] = 0.f;
-        nlse2[bh * NTP + n] = -INFINITY;
+        xq[bh * NTP + n] = make_uint4(ONES, split_bf16(-1e30f), 0u, 0u);
     }
     const size_t nmask = static_cast<size_t>(BS) * NTP;
     for (size_t idx = t0; idx < nmask; idx += gstride) {
         const size_t bs = idx / NTP;
         const int n = static_cast<int>(idx % NTP);
-        maskl2[idx] = (n < N) ? __bfloat162float(mask[bs * N + n]) * LOG2E : -INFINITY;
+        const float m = (n < N) ? __bfloat162float(mask[bs * N + n]) * inv_scale : -1e30f;
+        xk[idx] = make_uint4(split_bf16(m), ONES, 0u, 0u);
     }
 }
 
@@ -667,7 +681,7 @@ __global__ void cvt_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __re
 }
 
 struct BwdWorkspace {
-    size_t off_nlse2, off_delta, off_maskl2, off_dq, total;
+    size_t off_xq, off_xk, off_dq, total;
 };
 
 static BwdWorkspace bwd_workspace(const EvoDims* d) {
@@ -675,10 +689,9 @@ static BwdWorkspace bwd_workspace(const EvoDims* d) {
     const size_t NTP = static_cast<size_t>((d->N + TILE - 1) / TILE) * TILE;
     auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
     BwdWorkspace w;
-    w.off_nlse2 = 0;
-    w.off_delta = up(w.off_nlse2 + BS * d->H * NTP * 4);
-    w.off_maskl2 = up(w.off_delta + BS * d->H * NTP * 4);
-    w.off_dq = up(w.off_maskl2 + BS * NTP * 4);
+    w.off_xq = 0;
+    w.off_xk = up(w.off_xq + BS * d->H * NTP * 16);
+    w.off_dq = up(w.off_xk + BS * NTP * 16);
     w.total = up(w.off_dq + BS * d->N * d->H * d->D * 4);
     return w;
 }
@@ -692,9 +705,8 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     const int BS = d->B * d->S;
     const int NT = (d->N + TILE - 1) / TILE;
     const BwdWorkspace w = bwd_workspace(d);
-    float* nlse2 = reinterpret_cast<float*>(ws + w.off_nlse2);
-    float* delta = reinterpret_cast<float*>(ws + w.off_delta);
-    float* maskl2 = reinterpret_cast<float*>(ws + w.off_maskl2);
+    uint4* xq = reinterpret_cast<uint4*>(ws + w.off_xq);
+    uint4* xk = reinterpret_cast<uint4*>(ws + w.off_xk);
     float* dq_acc = reinterpret_cast<float*>(ws + w.off_dq);
 
     CUtensorMap tq, tk, tv, tdo, tb, tdq;
@@ -714,7 +726,8 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.total_items = d->B * p.CPB * d->H * NT;
     p.scale = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH));
     p.c1 = p.scale * LOG2E;
-    p.nlse2 = nlse2; p.delta = delta; p.maskl2 = maskl2;
+    p.xq = reinterpret_cast<const __nv_bfloat16*>(xq);
+    p.xk = reinterpret_cast<const __nv_bfloat16*>(xk);
     p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
     p.lay = lay;
     p.status = status_word();
@@ -730,10 +743,10 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
         if ((rc = cuda_err(cudaMemsetAsync(dbias, 0, db_bytes, st)))) return rc;
         bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
-            static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), nlse2, delta,
-            maskl2, BS, d->N, d->H, p.NTP, lay);
+            static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), xq, xk,
+            1.0f / p.scale, BS, d->N, d->H, p.NTP, lay);
         if ((rc = cuda_err(cudaGetLastError()))) return rc;
-        if ((rc = launch_dbias(d, lay, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st))) return rc;
+        if ((rc = launch_dbias(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st))) return rc;
     }
     if (!(phases & EVO_BWD_PHASE_DQKV)) return EVO_OK;
 

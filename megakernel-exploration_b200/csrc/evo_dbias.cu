@@ -14,11 +14,14 @@
 // for its operands.
 //
 //   warp NCW   (producer)  TMA per step (one S row): Q, dO tiles of q tile i,
-//                          K, V tiles of kv tile j, the -LSE / delta rows of i and
-//                          the mask row of j
-//   warp NCW+1 (mma)       S = Q K^T and dP = dO V^T into one of two tensor
-//                          memory buffers, so the MMAs of step n+1 overlap the
-//                          elementwise work of step n
+//                          K, V tiles of kv tile j, and the two extra tiles of the
+//                          step (per-row terms of i, per-column terms of j)
+//   warp NCW+1 (mma)       S' = Q K^T + (mask - LSE) / scale and dP' = dO V^T - delta
+//                          into one of two tensor memory buffers, so the MMAs of
+//                          step n+1 overlap the elementwise work of step n.  The
+//                          additive terms ride in an extra contraction block
+//                          (evo_tiles.cuh), so the elementwise work is one fused
+//                          multiply-add, one exp2 and one accumulate per element
 //   warps 0..NCW-1         NG compute groups of four warps; group g owns kv
 //                          columns g*CW .. g*CW+CW-1 of the tile, thread = q row.
 //                          Bias (bf16 pairs) and the running sum stay in
@@ -45,10 +48,13 @@ struct DbCfg {
     static constexpr int QS = (DH == 32) ? 6 : 3;         // load stages
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;
     static constexpr uint32_t ST_Q = 0, ST_DO = ROWT, ST_K = 2 * ROWT, ST_V = 3 * ROWT;
-    static constexpr uint32_t ST_ROWV = 4 * ROWT, ST_MASK = ST_ROWV + 1024;
-    static constexpr uint32_t STAGE_TX = 4 * ROWT + 1536;
-    static constexpr uint32_t STAGE_STRIDE = 4 * ROWT + 2048;
-    static constexpr uint32_t OFF_BARS = QS * STAGE_STRIDE;
+    static constexpr uint32_t ST_XQ = 4 * ROWT, ST_XK = ST_XQ + XT_BYTES;     // extra tiles of the step
+    static constexpr uint32_t STAGE_TX = 4 * ROWT + 2 * XT_BYTES;
+    static constexpr uint32_t STAGE_STRIDE = 4 * ROWT + 2 * XT_BYTES;
+    // constant extra tiles, above every stage (the zero tile must sit above the tiles that refer to it)
+    static constexpr uint32_t OFF_XDP = QS * STAGE_STRIDE;                    // column selector of -delta
+    static constexpr uint32_t OFF_ZERO = OFF_XDP + XT_BYTES;
+    static constexpr uint32_t OFF_BARS = OFF_ZERO + XT_BYTES;
     static constexpr uint32_t NUM_BARS = 2 * QS + 4;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;
@@ -63,9 +69,8 @@ struct DbParams {
     int Z, SL;            // S slices, rows per slice
     int total_items;      // Z * B * H * NT * NT
     float c1;             // scale * log2(e)
-    const float* nlse2;   // [B*S][H][NTP]
-    const float* delta;   // [B*S][H][NTP]
-    const float* maskl2;  // [B*S][NTP]
+    const __nv_bfloat16* xq;     // [B*S][H][NTP][8] extra tiles: per-row terms (see bwd_prep_kernel)
+    const __nv_bfloat16* xk;     // [B*S][NTP][8]    extra tiles: per-column terms
     const __nv_bfloat16* bias;   // [B][H][N][N]
     float* dbias;                // [B][H][N][N]
     unsigned int* status;
@@ -103,7 +108,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1 + NCW); }
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], NCW); }
         fence_mbar_init();
         fence_async_smem();
@@ -115,6 +120,12 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (warp == NCW && lane == 0) {
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
     }
+    // constant extra tiles: row n of the -delta selector is (0,0,0,0,1,1,0,0); the zero tile
+    for (int r = tid; r < 128; r += C::THREADS) {
+        *reinterpret_cast<uint4*>(smem + C::OFF_XDP + r * 16) = make_uint4(0u, 0u, 0x3f803f80u, 0u);
+        *reinterpret_cast<uint4*>(smem + C::OFF_ZERO + r * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_async_smem();
     EVO_TRACE_INIT();
     tc_fence_before();
     __syncthreads();
@@ -161,9 +172,8 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         tma_load_4d(sb + C::ST_DO, &tm_do, &st_full[st], 0, x.h, x.i * TILE, bs);
                         tma_load_4d(sb + C::ST_V, &tm_v, &st_full[st], 0, x.h, x.j * TILE, bs);
                         const size_t ro = (static_cast<size_t>(bs) * p.H + x.h) * p.NTP + x.i * TILE;
-                        bulk_load(sb + C::ST_ROWV, p.nlse2 + ro, 512, &st_full[st]);
-                        bulk_load(sb + C::ST_ROWV + 512, p.delta + ro, 512, &st_full[st]);
-                        bulk_load(sb + C::ST_MASK, p.maskl2 + static_cast<size_t>(bs) * p.NTP + x.j * TILE, 512,
+                        bulk_load(sb + C::ST_XQ, p.xq + ro * 8, XT_BYTES, &st_full[st]);
+                        bulk_load(sb + C::ST_XK, p.xk + (static_cast<size_t>(bs) * p.NTP + x.j * TILE) * 8, XT_BYTES,
                                   &st_full[st]);
                     }
                 }
@@ -176,6 +186,8 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 // ------------------------------ mma issuer ------------------------------
                 constexpr uint32_t IDESC = make_idesc_bf16(128, 128, 0, 0);
                 const uint32_t aSt = smem_u32(smem);
+                const uint32_t aZero = aSt + C::OFF_ZERO;
+                const uint64_t d_xdp = xt_desc(aSt + C::OFF_XDP, aZero);
                 bool ok = true;
                 int gs = 0;
                 for (int it = 0; it < n_items && ok; ++it) {
@@ -196,6 +208,10 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                             umma_ss(t0, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC, kk > 0);
                             umma_ss(t0 + 128, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC, kk > 0);
                         }
+                        // + (mask - LSE) / scale on S, - delta on dP: the extra contraction block
+                        const uint64_t d_xq = xt_desc(sb + C::ST_XQ, aZero);
+                        umma_ss(t0, d_xq, xt_desc(sb + C::ST_XK, aZero), IDESC, 1u);
+                        umma_ss(t0 + 128, d_xq, d_xdp, IDESC, 1u);
                         umma_commit(&sdp_full[buf]);
                         umma_commit(&st_empty[st]);
                     }
@@ -211,7 +227,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(wrow0) << 16) + g * CW;
         bool ok = true;
         int gs = 0;
-        const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
+        const float2 c1x2 = make_float2(p.c1, p.c1);
 
         for (int it = 0; it < n_items && ok; ++it) {
             const DbItem x = decode(it);
@@ -219,37 +235,33 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const int col0 = x.j * TILE + g * CW;
             const size_t tile_off = ((static_cast<size_t>(x.b) * p.H + x.h) * p.N + qrow) * p.N + col0;
 
-            uint32_t bias_pk[CW / 2];
-            float acc[CW];
+            // this thread's CW bias values, times log2(e), and the running sums: registers for the item
+            float2 bl2[CW / 2], acc[CW / 2];
 #pragma unroll
             for (int c8 = 0; c8 < CW / 8; ++c8) {
                 uint4 bv = make_uint4(0u, 0u, 0u, 0u);
                 if (qrow < p.N && col0 + c8 * 8 < p.N)
                     bv = __ldg(reinterpret_cast<const uint4*>(p.bias + tile_off + c8 * 8));
-                bias_pk[c8 * 4 + 0] = bv.x; bias_pk[c8 * 4 + 1] = bv.y;
-                bias_pk[c8 * 4 + 2] = bv.z; bias_pk[c8 * 4 + 3] = bv.w;
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = bf16x2_f2(bw[e]);
+                    bl2[c8 * 4 + e] = make_float2(f.x * LOG2E, f.y * LOG2E);
+                }
             }
 #pragma unroll
-            for (int c = 0; c < CW; ++c) acc[c] = 0.f;
+            for (int c = 0; c < CW / 2; ++c) acc[c] = make_float2(0.f, 0.f);
 
             for (int n = 0; n < x.ns && ok; ++n, ++gs) {
-                const int st = gs % QS, buf = gs & 1;
-                const uint8_t* sb = smem + st * C::STAGE_STRIDE;
+                const int buf = gs & 1;
                 ok = warp_all(mbar_wait(&sdp_full[buf], (gs >> 1) & 1, wc, 0xa0));
                 if (!ok) break;
-                ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0xa1));
-                if (!ok) break;
                 EVO_TS(t_math);
-                const float* rowv = reinterpret_cast<const float*>(sb + C::ST_ROWV);
-                const float nl = rowv[row];          // -LSE*log2e (-inf for padded rows)
-                const float dl = rowv[128 + row];    // delta
-                const float* mrow = reinterpret_cast<const float*>(sb + C::ST_MASK) + g * CW;
-                const float2 nl2 = make_float2(nl, nl), ndl2 = make_float2(-dl, -dl);
                 tc_fence_after();
                 // Chunks of 16 columns.  The tensor-memory loads of chunk ch+1 are in flight
-                // during the arithmetic of chunk ch, and the arithmetic goes stage by stage over
-                // the eight column pairs of the chunk so that neighbouring instructions are
-                // independent.
+                // during the arithmetic of chunk ch.  Per element: x = S' c1 + bias log2e (S'
+                // already carries mask and -LSE), P = exp2(x), sum += P dP' (dP' already
+                // carries -delta).
                 uint32_t sv[2][16], dv[2][16];
                 tmem_ld16(lane_base + buf * 256, sv[0]);
                 tmem_ld16(lane_base + buf * 256 + 128, dv[0]);
@@ -265,30 +277,16 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&sdp_free[buf]);
                     }
-                    // x = S*c1 + (bias + mask)*log2e - LSE*log2e, P = exp2(x), dS = P (dP - delta)
-                    float2 t2[8], p2[8];
+                    float2 p2[8];
 #pragma unroll
-                    for (int k = 0; k < 8; k += 2) {
-                        const float4 mv = *reinterpret_cast<const float4*>(mrow + 16 * ch + 2 * k);
-                        t2[k] = ffma2(bf16x2_f2(bias_pk[ch * 8 + k]), l2e2, make_float2(mv.x, mv.y));
-                        t2[k + 1] = ffma2(bf16x2_f2(bias_pk[ch * 8 + k + 1]), l2e2, make_float2(mv.z, mv.w));
+                    for (int k = 0; k < 8; ++k) {
+                        const float2 x2 = ffma2(u2f2(sv[cb][2 * k], sv[cb][2 * k + 1]), c1x2, bl2[ch * 8 + k]);
+                        p2[k] = make_float2(ex2(x2.x), ex2(x2.y));
                     }
 #pragma unroll
                     for (int k = 0; k < 8; ++k)
-                        t2[k] = fadd2(ffma2(u2f2(sv[cb][2 * k], sv[cb][2 * k + 1]), c1x2, t2[k]), nl2);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) p2[k] = make_float2(ex2(t2[k].x), ex2(t2[k].y));
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) t2[k] = fadd2(u2f2(dv[cb][2 * k], dv[cb][2 * k + 1]), ndl2);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const float2 a2 =
-                            ffma2(p2[k], t2[k], make_float2(acc[ch * 16 + 2 * k], acc[ch * 16 + 2 * k + 1]));
-                        acc[ch * 16 + 2 * k] = a2.x;
-                        acc[ch * 16 + 2 * k + 1] = a2.y;
-                    }
+                        acc[ch * 8 + k] = ffma2(p2[k], u2f2(dv[cb][2 * k], dv[cb][2 * k + 1]), acc[ch * 8 + k]);
                 }
-                mbar_release_after_reads(&st_empty[st]);      // row vectors and mask row are read
                 EVO_TE(t_math, p.status, 0xa8);
             }
             if (!ok) break;
@@ -301,11 +299,11 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     if (col0 + c4 * 4 < p.N) {
                         if (p.Z == 1) {
                             *reinterpret_cast<float4*>(out + c4 * 4) =
-                                make_float4(acc[c4 * 4], acc[c4 * 4 + 1], acc[c4 * 4 + 2], acc[c4 * 4 + 3]);
+                                make_float4(acc[c4 * 2].x, acc[c4 * 2].y, acc[c4 * 2 + 1].x, acc[c4 * 2 + 1].y);
                         } else {
                             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c4 * 4),
-                                         "f"(acc[c4 * 4]), "f"(acc[c4 * 4 + 1]), "f"(acc[c4 * 4 + 2]),
-                                         "f"(acc[c4 * 4 + 3])
+                                         "f"(acc[c4 * 2].x), "f"(acc[c4 * 2].y), "f"(acc[c4 * 2 + 1].x),
+                                         "f"(acc[c4 * 2 + 1].y)
                                          : "memory");
                         }
                     }
@@ -327,7 +325,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
 template <int DH>
 static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
-                          const void* d_o, const float* nlse2, const float* delta, const float* maskl2,
+                          const void* d_o, const void* xq, const void* xk,
                           float* dbias, float scale, int sms, cudaStream_t st) {
     constexpr int NG = EVO_DBIAS_GROUPS;
     using C = DbCfg<DH, NG>;
@@ -363,7 +361,8 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
     p.total_items = static_cast<int>(base * p.Z);
     const float sc = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH));
     p.c1 = sc * LOG2E;
-    p.nlse2 = nlse2; p.delta = delta; p.maskl2 = maskl2;
+    p.xq = static_cast<const __nv_bfloat16*>(xq);
+    p.xk = static_cast<const __nv_bfloat16*>(xk);
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.dbias = dbias;
     p.status = status_word();
@@ -380,11 +379,11 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
 }
 
 int launch_dbias(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
-                 const void* d_o, const float* nlse2, const float* delta, const float* maskl2, float* dbias,
+                 const void* d_o, const void* xq, const void* xk, float* dbias,
                  float scale, int sms, cudaStream_t st) {
     if (d->D == 32)
-        return launch_dbias_t<32>(d, lay, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st);
-    return launch_dbias_t<64>(d, lay, q, k, v, bias, d_o, nlse2, delta, maskl2, dbias, scale, sms, st);
+        return launch_dbias_t<32>(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
+    return launch_dbias_t<64>(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
 }
 
 }  // namespace evo

@@ -5,11 +5,11 @@
 
 namespace evo {
 
-// dbias [B][H][N][N] fp32 must be zeroed on `st` before the call.  nlse2, delta
-// and maskl2 are the tile-padded rows the prep kernel writes (see evo_bwd.cu).
+// dbias [B][H][N][N] fp32 must be zeroed on `st` before the call.  xq and xk are the
+// extra tiles the prep kernel writes (see evo_bwd.cu): bf16 [B*S][H][NTP][8] with the
+// per-row terms and bf16 [B*S][NTP][8] with the per-column terms.
 // D is 32 or 64; `lay` gives the strides of q, k, v, d_o.
 int launch_dbias(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
-                 const void* d_o, const float* nlse2, const float* delta, const float* maskl2, float* dbias,
-                 float scale, int sms, cudaStream_t st);
+                 const void* d_o, const void* xq, const void* xk, float* dbias, float scale, int sms, cudaStream_t st);
 
 }  // namespace evo

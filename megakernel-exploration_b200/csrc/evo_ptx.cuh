@@ -215,15 +215,17 @@ __device__ __forceinline__ void mbar_release_after_reads(uint64_t* bar) {
 
 // The same hand-back without a fence.  `dep` must be computed FROM the values the last
 // loads of the buffer returned (any cheap combination of one register per load
-// instruction): the arrive takes it as an operand, so the hardware cannot issue the
-// arrive before those loads have written their registers, and a load instruction
-// completes for all lanes of the warp together.  Costs a few logic operations
-// instead of a membar (which also waits for every other outstanding access).
-__device__ __forceinline__ void mbar_release_after_loads(uint64_t* bar, uint32_t dep) {
+// instruction).  Lane 0 stores it to a scratch word before the arrive: the store
+// cannot issue before those loads have written their registers (a load instruction
+// completes for all lanes of the warp together), instructions issue in order, and the
+// arrive's release semantics keep it behind the store.  Costs a few logic operations
+// and one store instead of a membar (which also waits for every other outstanding
+// access of the thread).  `scratch` is the shared address of any word nobody reads.
+__device__ __forceinline__ void mbar_release_after_loads(uint64_t* bar, uint32_t dep, uint32_t scratch) {
     __syncwarp();
     if ((threadIdx.x & 31u) == 0u) {
-        // (dep & 0) keeps the address unchanged while carrying the dependency
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar) + (dep & 0u)) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(scratch), "r"(dep) : "memory");
+        mbar_arrive(bar);
     }
 }
 
