@@ -49,7 +49,7 @@ namespace evo {
 
 // 4 warpgroups: 2 compute, drain, (producer, mma, 2 idle warps)
 constexpr int BWD_THREADS = 512;
-constexpr int BWD_WARP_DRAIN = 8, BWD_WARP_PRODUCER = 12, BWD_WARP_MMA = 13;
+constexpr int BWD_WARP_DRAIN = 8, BWD_WARP_PRODUCER = 12, BWD_WARP_MMA = 13;   // 13, 14, 15: mma issuers
 constexpr uint32_t BWD_TMEM_COLS = 512;
 constexpr int BWD_REGS_COMPUTE = 176;
 constexpr int BWD_REGS_OTHER = 80;
@@ -61,7 +61,10 @@ static_assert(BWD_REGS_COMPUTE * 256 + BWD_REGS_OTHER * 256 <= 128 * BWD_THREADS
 template <int DH>
 struct BwdCfg {
     static constexpr int RC = (DH == 32) ? 3 : 1;     // S rows per chunk
-    static constexpr int QS = (DH == 32) ? 3 : 2;     // load stages
+#ifndef EVO_BWD_QS32
+#define EVO_BWD_QS32 3
+#endif
+    static constexpr int QS = (DH == 32) ? EVO_BWD_QS32 : 2;     // load stages
     // D=32: K/V travel with every step's stage; D=64: one resident K/V buffer per item
     static constexpr bool KV_RESIDENT = (DH == 64);
     static constexpr int HALF = DH / 2;               // head-dim columns drained per group
@@ -88,7 +91,7 @@ struct BwdCfg {
     static constexpr uint32_t OFF_XDP = OFF_WSTG + 4 * WQ_BYTES;            // column selector of -delta
     static constexpr uint32_t OFF_ZERO = OFF_XDP + XT_BYTES;
     static constexpr uint32_t OFF_BARS = OFF_ZERO + XT_BYTES;
-    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 7 + RC;
+    static constexpr uint32_t NUM_BARS = 2 * QS + 2 + 2 + 7 + RC + 2;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
@@ -147,6 +150,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* dq_full = pds_ready + 1;         // [2]
     uint64_t* dq_free = dq_full + 2;           // [2]
     uint64_t* dkv_free = dq_free + 2;          // [RC]: accumulators of row r of the chunk are read out
+    uint64_t* tail_done = dkv_free + RC;       // [2] by step parity: both tail issuers' MMAs of a step are complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -158,9 +162,10 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1); }
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 2); }
         mbar_init(kv_full, 1);
-        mbar_init(kv_empty, 1);
+        mbar_init(kv_empty, 2);
+        for (int i = 0; i < 2; ++i) mbar_init(&tail_done[i], 2);
         mbar_init(bias_full, 1);
         mbar_init(bias_empty, 8);
         mbar_init(sdp_full, 1);
@@ -267,129 +272,95 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 (void)mbar_wait(&st_full[k % QS], (k / QS) & 1, wc, 0x43);
             if (gb > 0) (void)mbar_wait(bias_full, (gb - 1) & 1, wc, 0x44);
             if (KVR && n_items > 0) (void)mbar_wait(kv_full, (n_items - 1) & 1, wc, 0x45);
-        } else if (warp == BWD_WARP_MMA && lane == 0) {
-            // ------------------------------ mma issuer ------------------------------
+        } else if (warp >= BWD_WARP_MMA) {
+            // ------------------------------ mma issuers ------------------------------
+            // Three warps, one chain family each, so that no chain queues behind another one's
+            // issue: warp 13 issues S' and dP' of the next step as soon as the compute groups have
+            // read the previous pair, warp 14 issues dV += P^T dO and dK += dS^T Q, warp 15 issues
+            // dQ = dS K.  Each warp runs its loop with all lanes (uniform control flow: operand
+            // descriptors stay in uniform registers) and elects one lane to issue.
             constexpr uint32_t IDESC_SDP = make_idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t IDESC_DKV = make_idesc_bf16(128, DH, 1, 1);
             constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, DH, 0, 1);
             const uint32_t aSt = smem_u32(smem + C::OFF_STAGE), aKV = smem_u32(smem + C::OFF_KV);
-            const uint32_t p_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_P));
-            const uint32_t ds_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_DS));
-            const uint32_t ds_k_lo = SqDesc::kmajor_lo(smem_u32(smem + C::OFF_DS));
             const uint32_t aZero = smem_u32(smem + C::OFF_ZERO);
-            const uint64_t d_xdp = xt_desc(smem_u32(smem + C::OFF_XDP), aZero);
-
-            struct Cursor {
-                int it, n, gs, nsteps;
-                BwdItem x;
-            };
-            auto cur_start = [&](Cursor& c) {
-                c.it = 0; c.n = 0; c.gs = 0; c.nsteps = 1;
-                if (n_items > 0) { c.x = decode(0); c.nsteps = NT * c.x.nr; }
-            };
-            auto cur_next = [&](Cursor& c) {
-                ++c.gs;
-                if (++c.n == c.nsteps) {
-                    c.n = 0;
-                    if (++c.it < n_items) { c.x = decode(c.it); c.nsteps = NT * c.x.nr; }
-                }
-            };
-            auto k_tile = [&](const Cursor& c, int r) -> uint32_t {
-                return KVR ? aKV + r * C::ROWT : aSt + (c.gs % QS) * C::STAGE_STRIDE + C::ST_K;
-            };
-            auto v_tile = [&](const Cursor& c, int r) -> uint32_t {
-                return KVR ? aKV + (RC + r) * C::ROWT : aSt + (c.gs % QS) * C::STAGE_STRIDE + C::ST_V;
-            };
-            // S and dP of the step under the cursor, if everything they need is there
-            auto try_sdp = [&](const Cursor& c) -> bool {
-                const int st = c.gs % QS;
-                if (!mbar_test(&st_full[st], (c.gs / QS) & 1)) return false;
-                if (KVR && c.n == 0 && !mbar_test(kv_full, c.it & 1)) return false;
-                if (c.gs > 0 && !mbar_test(sdp_free, (c.gs - 1) & 1)) return false;
-                tc_fence_after();
-                EVO_TS(t_i1);
-                const int r = c.n % c.x.nr;
-                const uint32_t sb = aSt + st * C::STAGE_STRIDE;
-                const uint32_t q_lo = RD::kmajor_lo(sb + C::ST_Q), do_lo = RD::kmajor_lo(sb + C::ST_DO);
-                const uint32_t k_lo = RD::kmajor_lo(k_tile(c, r)), v_lo = RD::kmajor_lo(v_tile(c, r));
-                // The two chains are interleaved so that consecutive MMAs use different
-                // accumulators (an isolated chain into one accumulator measured ~100 cycles per
-                // MMA at N = 32 and ~180 at N = 128 whatever the operand layout; mixed chains less).
+            const int role = warp - BWD_WARP_MMA;          // 0: S/dP, 1: dV/dK, 2: dQ
+            bool ok = true;
+            int gs = 0;
+            for (int it = 0; it < n_items && ok; ++it) {
+                const BwdItem x = decode(it);
+                const int nsteps = NT * x.nr;
+                int i = 0, r = 0;
+                for (int n = 0; n < nsteps && ok; ++n, ++gs) {
+                    const int st = gs % QS;
+                    const uint32_t sb = aSt + st * C::STAGE_STRIDE;
+                    const uint32_t k_tile = KVR ? aKV + r * C::ROWT : sb + C::ST_K;
+                    if (role == 0) {
+                        ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x50));
+                        if (ok && KVR && n == 0) ok = warp_all(mbar_wait(kv_full, it & 1, wc, 0x51));
+                        if (ok && gs > 0) ok = warp_all(mbar_wait(sdp_free, (gs - 1) & 1, wc, 0x52));
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (elect_one()) {
+                            const uint32_t v_tile = KVR ? aKV + (RC + r) * C::ROWT : sb + C::ST_V;
+                            const uint32_t q_lo = RD::kmajor_lo(sb + C::ST_Q), do_lo = RD::kmajor_lo(sb + C::ST_DO);
+                            const uint32_t k_lo = RD::kmajor_lo(k_tile), v_lo = RD::kmajor_lo(v_tile);
 #pragma unroll
-                for (int kk = 0; kk < RT::KBLOCKS; ++kk) {
-                    umma_ss(tmem + C::TMEM_S, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC_SDP, kk > 0);
-                    umma_ss(tmem + C::TMEM_DP, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC_SDP, kk > 0);
-                }
-                // + (mask - LSE) / scale on S, - delta on dP: the extra contraction block
-                const uint64_t d_xq = xt_desc(sb + C::ST_XQ, aZero);
-                const uint32_t xk_addr = KVR ? aKV + 2 * RC * C::ROWT + r * XT_BYTES : sb + C::ST_XK;
-                umma_ss(tmem + C::TMEM_S, d_xq, xt_desc(xk_addr, aZero), IDESC_SDP, 1u);
-                umma_ss(tmem + C::TMEM_DP, d_xq, d_xdp, IDESC_SDP, 1u);
-                umma_commit(sdp_full);
-                EVO_TE(t_i1, p.status, 0xe2);
-                return true;
-            };
-            // dV, dK, dQ of the step under the cursor, if P/dS are out and the accumulators are free
-            auto try_tail = [&](const Cursor& c) -> bool {
-                const int st = c.gs % QS;
-                const int i = c.n / c.x.nr, r = c.n - i * c.x.nr;
-                if (!mbar_test(pds_ready, c.gs & 1)) return false;
-                if (c.gs >= BWD_DQ_BUFS &&
-                    !mbar_test(&dq_free[c.gs % BWD_DQ_BUFS], ((c.gs / BWD_DQ_BUFS) - 1) & 1))
-                    return false;
-                // the first MMA into row r's dK/dV of an item overwrites them: the previous item's must be out
-                if (i == 0 && c.it > 0 && !mbar_test(&dkv_free[r], (c.it - 1) & 1)) return false;
-                tc_fence_after();
-                EVO_TS(t_i2);
-                const uint32_t sb = aSt + st * C::STAGE_STRIDE;
-                const uint32_t q_lo = RD::mnmajor_lo(sb + C::ST_Q), do_lo = RD::mnmajor_lo(sb + C::ST_DO);
-                const uint32_t k_lo = RD::mnmajor_lo(k_tile(c, r));
-                const uint32_t t_dk = tmem + C::TMEM_DKV + r * 2 * DH, t_dv = t_dk + DH;
-                const uint32_t t_dq = tmem + C::TMEM_DQ + (c.gs % BWD_DQ_BUFS) * DH;
-                const uint32_t acc = (i > 0) ? 1u : 0u;
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {      // three interleaved chains (see try_sdp)
-                    umma_ss(t_dv, SqDesc::mnmajor(p_mn_lo, kk), RD::mnmajor(do_lo, kk), IDESC_DKV, kk > 0 ? 1u : acc);
-                    umma_ss(t_dk, SqDesc::mnmajor(ds_mn_lo, kk), RD::mnmajor(q_lo, kk), IDESC_DKV, kk > 0 ? 1u : acc);
-                    umma_ss(t_dq, SqDesc::kmajor(ds_k_lo, kk), RD::mnmajor(k_lo, kk), IDESC_DQ, kk > 0);
-                }
-                umma_commit(&dq_full[c.gs % BWD_DQ_BUFS]);
-                umma_commit(&st_empty[st]);
-                if (KVR && c.n == c.nsteps - 1) umma_commit(kv_empty);
-                EVO_TE(t_i2, p.status, 0xe0);
-                return true;
-            };
-
-            Cursor a, b;          // a: next S/dP to issue, b: next dV/dK/dQ to issue
-            cur_start(a);
-            cur_start(b);
-            uint32_t idle = 0;
-            uint64_t idle_t0 = 0;
-            while (b.it < n_items) {
-                bool progress = false;
-                // S/dP run at most one step ahead (they share one accumulator pair)
-                if (a.it < n_items && a.gs <= b.gs + 1 && try_sdp(a)) {
-                    cur_next(a);
-                    progress = true;
-                }
-                if (b.gs < a.gs && try_tail(b)) {
-                    cur_next(b);
-                    progress = true;
-                }
-                if (progress) {
-                    idle = 0;
-                } else {
-                    __nanosleep(20);
-                    if ((++idle & 255u) == 0u) {
-                        if (*abort_flag) break;
-                        const uint64_t now = global_ns();
-                        if (idle == 256u) idle_t0 = now;
-                        if (now - idle_t0 > EVO_WAIT_NS) {
-                            report(p.status, ST_WAIT_TIMEOUT, 0x5f);
-                            *abort_flag = 1u;
-                            break;
+                            for (int kk = 0; kk < RT::KBLOCKS; ++kk) {
+                                umma_ss(tmem + C::TMEM_S, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC_SDP, kk > 0);
+                                umma_ss(tmem + C::TMEM_DP, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC_SDP, kk > 0);
+                            }
+                            // + (mask - LSE) / scale on S, - delta on dP: the extra contraction block
+                            const uint64_t d_xq = xt_desc(sb + C::ST_XQ, aZero);
+                            const uint32_t xk_addr = KVR ? aKV + 2 * RC * C::ROWT + r * XT_BYTES : sb + C::ST_XK;
+                            umma_ss(tmem + C::TMEM_S, d_xq, xt_desc(xk_addr, aZero), IDESC_SDP, 1u);
+                            umma_ss(tmem + C::TMEM_DP, d_xq, xt_desc(smem_u32(smem + C::OFF_XDP), aZero), IDESC_SDP, 1u);
+                            umma_commit(sdp_full);
                         }
+                        __syncwarp();
+                    } else if (role == 1) {
+                        ok = warp_all(mbar_wait(pds_ready, gs & 1, wc, 0x53));
+                        // the first MMA into row r's dK/dV of an item overwrites them: the previous item's must be out
+                        if (ok && i == 0 && it > 0) ok = warp_all(mbar_wait(&dkv_free[r], (it - 1) & 1, wc, 0x55));
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (elect_one()) {
+                            const uint32_t p_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_P));
+                            const uint32_t ds_mn_lo = SqDesc::mnmajor_lo(smem_u32(smem + C::OFF_DS));
+                            const uint32_t q_lo = RD::mnmajor_lo(sb + C::ST_Q), do_lo = RD::mnmajor_lo(sb + C::ST_DO);
+                            const uint32_t t_dk = tmem + C::TMEM_DKV + r * 2 * DH, t_dv = t_dk + DH;
+                            const uint32_t acc = (i > 0) ? 1u : 0u;
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk) {      // two interleaved chains
+                                umma_ss(t_dv, SqDesc::mnmajor(p_mn_lo, kk), RD::mnmajor(do_lo, kk), IDESC_DKV, kk > 0 ? 1u : acc);
+                                umma_ss(t_dk, SqDesc::mnmajor(ds_mn_lo, kk), RD::mnmajor(q_lo, kk), IDESC_DKV, kk > 0 ? 1u : acc);
+                            }
+                            umma_commit(&tail_done[gs & 1]);
+                            umma_commit(&st_empty[st]);
+                            if (KVR && n == nsteps - 1) umma_commit(kv_empty);
+                        }
+                        __syncwarp();
+                    } else if (role == 2) {
+                        ok = warp_all(mbar_wait(pds_ready, gs & 1, wc, 0x53));
+                        if (ok && gs >= BWD_DQ_BUFS)
+                            ok = warp_all(mbar_wait(&dq_free[gs % BWD_DQ_BUFS], ((gs / BWD_DQ_BUFS) - 1) & 1, wc, 0x54));
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (elect_one()) {
+                            const uint32_t ds_k_lo = SqDesc::kmajor_lo(smem_u32(smem + C::OFF_DS));
+                            const uint32_t k_lo = RD::mnmajor_lo(k_tile);
+                            const uint32_t t_dq = tmem + C::TMEM_DQ + (gs % BWD_DQ_BUFS) * DH;
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk)
+                                umma_ss(t_dq, SqDesc::kmajor(ds_k_lo, kk), RD::mnmajor(k_lo, kk), IDESC_DQ, kk > 0);
+                            umma_commit(&dq_full[gs % BWD_DQ_BUFS]);
+                            umma_commit(&tail_done[gs & 1]);
+                            umma_commit(&st_empty[st]);
+                            if (KVR && n == nsteps - 1) umma_commit(kv_empty);
+                        }
+                        __syncwarp();
                     }
+                    if (++r == x.nr) { r = 0; ++i; }
                 }
             }
         } else if (warp < BWD_WARP_DRAIN + 4) {
@@ -436,6 +407,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         }
                     }
                     if (n == nsteps - 1) {
+                        ok = warp_all(mbar_wait(&tail_done[gs & 1], (gs >> 1) & 1, wc, 0x69));
+                        if (!ok) break;
+                        tc_fence_after();
                         // the item's last MMAs are done: dK/dV -> bf16 stores, row by row of the chunk;
                         // each row's accumulators are handed back as soon as they are read
                         const int kvrow = x.j * TILE + wrow0 + lane;
@@ -554,7 +528,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
                 // the P / dS tiles are free once the previous step's dV/dK/dQ MMAs are done
                 if (gs > 0) {
-                    ok = warp_all(mbar_wait(&dq_full[(gs - 1) % BWD_DQ_BUFS], ((gs - 1) / BWD_DQ_BUFS) & 1, wc, 0x61));
+                    ok = warp_all(mbar_wait(&tail_done[(gs - 1) & 1], ((gs - 1) >> 1) & 1, wc, 0x61));
                     if (!ok) break;
                 }
                 EVO_TS(t_sts);
