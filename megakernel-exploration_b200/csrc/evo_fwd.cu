@@ -37,6 +37,15 @@
 
 namespace evo {
 
+// How far the running row maximum may fall behind before the accumulator in tensor memory is
+// rescaled.  0 = the exact online softmax: the largest P of a row is exp2(0) = 1, which bf16
+// represents exactly, so a row dominated by one logit carries no rounding error from its main
+// term.  A lag of 8 (P up to 256, the rescale then almost never runs) measured 2 % faster but
+// put a 2^-9 relative error on exactly those main terms: 10x the dBias error at heavy-tailed
+// logits (0.033 against 0.0035 max-abs at B=1, S=48, N=768, H=8, D=32, bias std 2).
+#ifndef EVO_FWD_LAZY
+#define EVO_FWD_LAZY 0.0f
+#endif
 constexpr int FWD_THREADS = 384;           // 3 warpgroups: 2 softmax + (producer, mma, 2 idle warps)
 constexpr int FWD_REGS_SOFTMAX = 208;
 constexpr int FWD_REGS_OTHER = 88;
@@ -53,10 +62,9 @@ struct FwdCfg {
     static constexpr uint32_t OFF_Q = 0;                           // 2 buffers
     static constexpr uint32_t OFF_STAGE = OFF_Q + 2 * ROWT;
     static constexpr uint32_t OFF_O = OFF_STAGE + STAGES * STAGE_STRIDE;
-    // group 1 -> group 0 hand-over: per row m, l and DH accumulator values, padded pitch
-    static constexpr uint32_t XCH_PITCH = (DH + 4) * 4;
+    // exchange of the two groups' (m, l) per row
     static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
-    static constexpr uint32_t OFF_WMASK = OFF_XCH + 128 * XCH_PITCH;       // 8 warps x 64 floats
+    static constexpr uint32_t OFF_WMASK = OFF_XCH + 2 * 128 * 8;           // 8 warps x 64 floats
     static constexpr uint32_t OFF_BARS = OFF_WMASK + 8 * 256;
     static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 8 + 2 + 2 + 3;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
@@ -106,9 +114,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* s_free = s_full + 4;           // [4]
     uint64_t* p_ready = s_free + 4;          // [2] per softmax group
     uint64_t* pv_full = p_ready + 2;         // [2]
-    uint64_t* xch_full = pv_full + 2;        // group 1 has written its partial result
-    uint64_t* xch_empty = xch_full + 1;      // group 0 has read it
-    uint64_t* g0_bar = xch_empty + 1;        // rendezvous of group 0's four warps
+    uint64_t* e_bar = pv_full + 2;           // [2] rendezvous of the eight softmax warps in the epilogue
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -124,9 +130,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 9); }
         for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
         for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
-        mbar_init(xch_full, 4);
-        mbar_init(xch_empty, 4);
-        mbar_init(g0_bar, 4);
+        mbar_init(&e_bar[0], 8);
+        mbar_init(&e_bar[1], 8);
         fence_mbar_init();
         fence_async_smem();
     }
@@ -160,67 +165,63 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     if (warp >= 8) {
         reg_dec<FWD_REGS_OTHER>();
-        if (warp == 8 && lane == 0) {
-            // ------------------------------ producer ------------------------------
-            bool ok = true;
-            int g = 0;   // running kv-tile counter across items
-            for (int it = 0; it < n_items && ok; ++it) {
-                int bs, qt, h;
-                decode(it, bs, qt, h);
-                const int b = bs / p.S;
-                const int qb = it & 1;
-                if (it >= 2) ok = mbar_wait(&q_empty[qb], ((it >> 1) - 1) & 1, wc, 0x10);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&q_full[qb], C::ROWT);
-                tma_load_4d(smem + C::OFF_Q + qb * C::ROWT, &tm_q, &q_full[qb], 0, h, qt * TILE, bs);
-                for (int j = 0; j < NT; ++j, ++g) {
-                    const int st = g % ST;
-                    if (g >= ST) ok = mbar_wait(&kv_empty[st], ((g / ST) - 1) & 1, wc, 0x11);
+        if (warp == 8) {
+            if (lane == 0) {
+                // ------------------------------ producer ------------------------------
+                bool ok = true;
+                int g = 0;   // running kv-tile counter across items
+                for (int it = 0; it < n_items && ok; ++it) {
+                    int bs, qt, h;
+                    decode(it, bs, qt, h);
+                    const int b = bs / p.S;
+                    const int qb = it & 1;
+                    if (it >= 2) ok = mbar_wait(&q_empty[qb], ((it >> 1) - 1) & 1, wc, 0x10);
                     if (!ok) break;
-                    uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
-                    const int ncol = (p.N - j * TILE < TILE) ? (p.N - j * TILE) : TILE;   // multiple of 8
-                    mbar_arrive_expect_tx(&kv_full[st], 2 * C::ROWT + SQ_BYTES + ncol * 2);
-                    tma_load_4d(sb + C::ST_K, &tm_k, &kv_full[st], 0, h, j * TILE, bs);
-                    tma_load_4d(sb + C::ST_V, &tm_v, &kv_full[st], 0, h, j * TILE, bs);
-                    tma_load_4d(sb + C::ST_BIAS, &tm_bias, &kv_full[st], j * TILE, qt * TILE, h, b);
-                    tma_load_4d(sb + C::ST_BIAS + SQ_SUB_BYTES, &tm_bias, &kv_full[st], j * TILE + 64, qt * TILE, h, b);
-                    bulk_load(sb + C::ST_MASK, p.mask + static_cast<size_t>(bs) * p.N + j * TILE, ncol * 2, &kv_full[st]);
+                    mbar_arrive_expect_tx(&q_full[qb], C::ROWT);
+                    tma_load_4d(smem + C::OFF_Q + qb * C::ROWT, &tm_q, &q_full[qb], 0, h, qt * TILE, bs);
+                    for (int j = 0; j < NT; ++j, ++g) {
+                        const int st = g % ST;
+                        if (g >= ST) ok = mbar_wait(&kv_empty[st], ((g / ST) - 1) & 1, wc, 0x11);
+                        if (!ok) break;
+                        uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
+                        const int ncol = (p.N - j * TILE < TILE) ? (p.N - j * TILE) : TILE;   // multiple of 8
+                        mbar_arrive_expect_tx(&kv_full[st], 2 * C::ROWT + SQ_BYTES + ncol * 2);
+                        tma_load_4d(sb + C::ST_K, &tm_k, &kv_full[st], 0, h, j * TILE, bs);
+                        tma_load_4d(sb + C::ST_V, &tm_v, &kv_full[st], 0, h, j * TILE, bs);
+                        tma_load_4d(sb + C::ST_BIAS, &tm_bias, &kv_full[st], j * TILE, qt * TILE, h, b);
+                        tma_load_4d(sb + C::ST_BIAS + SQ_SUB_BYTES, &tm_bias, &kv_full[st], j * TILE + 64, qt * TILE, h, b);
+                        bulk_load(sb + C::ST_MASK, p.mask + static_cast<size_t>(bs) * p.N + j * TILE, ncol * 2, &kv_full[st]);
+                    }
                 }
+                // Drain: every load issued above has landed before the CTA exits.
+                const int issued = g;
+                for (int k = (issued > ST ? issued - ST : 0); k < issued; ++k)
+                    (void)mbar_wait(&kv_full[k % ST], (k / ST) & 1, wc, 0x12);
+                for (int it = (n_items > 2 ? n_items - 2 : 0); it < n_items; ++it)
+                    (void)mbar_wait(&q_full[it & 1], (it >> 1) & 1, wc, 0x13);
             }
-            // Drain: every load issued above has landed before the CTA exits.
-            const int issued = g;
-            for (int k = (issued > ST ? issued - ST : 0); k < issued; ++k)
-                (void)mbar_wait(&kv_full[k % ST], (k / ST) & 1, wc, 0x12);
-            for (int it = (n_items > 2 ? n_items - 2 : 0); it < n_items; ++it)
-                (void)mbar_wait(&q_full[it & 1], (it >> 1) & 1, wc, 0x13);
-        } else if (warp == 9 && lane == 0) {
-            // ------------------------------ mma issuer ------------------------------
-            // Issues whichever MMA has its operands ready: S of the next tile (needs
-            // its loads and the S accumulator read out) or PV_g of a tile whose P_g
-            // is in tensor memory.  Nothing here blocks on one barrier while
-            // another piece of work could go.
+        } else if (warp == 9) {
+            // ------------------------------ S issuer ------------------------------
+            // S_w = Q K[64w:64w+64, :]^T for both softmax groups w of every tile, one tile ahead of
+            // the softmax (two S buffers).  The warp runs its loop with all lanes (uniform control
+            // flow keeps the operand descriptors in uniform registers) and elects one lane to issue.
             constexpr uint32_t IDESC_S = make_idesc_bf16(128, 64, 0, 0);
-            constexpr uint32_t IDESC_PV = make_idesc_bf16(128, DH, 0, 1);
             const uint32_t aQ = smem_u32(smem + C::OFF_Q), aSt = smem_u32(smem + C::OFF_STAGE);
-            const int total_tiles = n_items * NT;
-            int s_next[2] = {0, 0};          // per group: next tile whose S_g is to be issued
-            int pv_next[2] = {0, 0};         // per group: next tile whose PV_g is to be issued
-            uint32_t idle = 0;
-            uint64_t idle_t0 = 0;
-            while (pv_next[0] < total_tiles || pv_next[1] < total_tiles) {
-                bool progress = false;
+            bool ok = true;
+            int g = 0;
+            for (int it = 0; it < n_items && ok; ++it) {
+                const int qb = it & 1;
+                for (int j = 0; j < NT && ok; ++j, ++g) {
+                    const int st = g % ST;
+                    if (j == 0) ok = warp_all(mbar_wait(&q_full[qb], (it >> 1) & 1, wc, 0x20));
+                    if (ok) ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x21));
 #pragma unroll
-                for (int w = 0; w < 2; ++w) {
-                    if (s_next[w] < total_tiles) {
-                        const int g = s_next[w];
-                        const int it = g / NT, j = g - it * NT;
-                        const int qb = it & 1, st = g % ST;
-                        const int sb = w + 2 * (g & 1);          // S buffer of this tile: S runs one tile ahead
-                        const bool rdy = (j != 0 || mbar_test(&q_full[qb], (it >> 1) & 1)) &&
-                                         mbar_test(&kv_full[st], (g / ST) & 1) &&
-                                         (g < 2 || mbar_test(&s_free[sb], ((g >> 1) - 1) & 1));
-                        if (rdy) {
-                            tc_fence_after();
+                    for (int w = 0; w < 2; ++w) {
+                        const int sb = w + 2 * (g & 1);
+                        if (ok && g >= 2) ok = warp_all(mbar_wait(&s_free[sb], ((g >> 1) - 1) & 1, wc, 0x22));
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (elect_one()) {
                             // K rows 64w..64w+63 of the tile: 64 rows further into the K-major tile
                             const uint32_t kt = aSt + st * C::STAGE_STRIDE + C::ST_K + w * 64 * RT::ROW_BYTES;
 #pragma unroll
@@ -228,39 +229,39 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                 umma_ss(tmem + C::TMEM_S + (g & 1) * 128 + 64 * w, RT::kmajor(aQ + qb * C::ROWT, kb),
                                         RT::kmajor(kt, kb), IDESC_S, kb > 0);
                             umma_commit(&s_full[sb]);
-                            ++s_next[w];
                             // Q is free once both groups' S of the item's last tile are issued
-                            if (j == NT - 1 && s_next[w ^ 1] > g) umma_commit(&q_empty[qb]);
-                            progress = true;
+                            if (w == 1 && j == NT - 1) umma_commit(&q_empty[qb]);
                         }
-                    }
-                    const int g = pv_next[w];
-                    if (g < s_next[w] && mbar_test(&p_ready[w], g & 1)) {
-                        const int st = g % ST;
-                        tc_fence_after();
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            umma_ts(tmem + C::TMEM_PV + w * DH, tmem + C::TMEM_P + w * 32 + kk * 8,
-                                    RT::mnmajor(aSt + st * C::STAGE_STRIDE + C::ST_V, 4 * w + kk), IDESC_PV, kk > 0);
-                        umma_commit(&pv_full[w]);
-                        ++pv_next[w];
-                        if (pv_next[w ^ 1] > g) umma_commit(&kv_empty[st]);   // both groups' PV of tile g issued
-                        progress = true;
+                        __syncwarp();
                     }
                 }
-                if (progress) {
-                    idle = 0;
-                } else {
-                    __nanosleep(20);
-                    if ((++idle & 255u) == 0u) {
-                        if (*abort_flag) break;
-                        const uint64_t now = global_ns();
-                        if (idle == 256u) idle_t0 = now;
-                        if (now - idle_t0 > EVO_WAIT_NS) {
-                            report(p.status, ST_WAIT_TIMEOUT, 0x2f);
-                            *abort_flag = 1u;
-                            break;
+            }
+        } else if (warp == 10) {
+            // ------------------------------ PV issuer ------------------------------
+            // PV_w (+)= P_w V[64w:64w+64, :] with P_w read from tensor memory; the accumulator of a
+            // group stays in tensor memory for the whole item (the first tile overwrites it).
+            constexpr uint32_t IDESC_PV = make_idesc_bf16(128, DH, 0, 1);
+            const uint32_t aSt = smem_u32(smem + C::OFF_STAGE);
+            bool ok = true;
+            int g = 0;
+            for (int it = 0; it < n_items && ok; ++it) {
+                for (int j = 0; j < NT && ok; ++j, ++g) {
+                    const int st = g % ST;
+#pragma unroll
+                    for (int w = 0; w < 2; ++w) {
+                        ok = warp_all(mbar_wait(&p_ready[w], g & 1, wc, 0x23));
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (elect_one()) {
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk)
+                                umma_ts(tmem + C::TMEM_PV + w * DH, tmem + C::TMEM_P + w * 32 + kk * 8,
+                                        RT::mnmajor(aSt + st * C::STAGE_STRIDE + C::ST_V, 4 * w + kk), IDESC_PV,
+                                        (kk > 0 || j > 0) ? 1u : 0u);
+                            umma_commit(&pv_full[w]);
+                            if (w == 1) umma_commit(&kv_empty[st]);   // both groups' PV of the tile issued
                         }
+                        __syncwarp();
                     }
                 }
             }
@@ -271,92 +272,88 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int wg = warp >> 2;            // 0 or 1: kv columns 64*wg .. 64*wg+63 of each tile
         const int row = tid & 127;           // q row within the tile == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-        uint8_t* sO = smem + C::OFF_O;
-        float* xrow = reinterpret_cast<float*>(smem + C::OFF_XCH + row * C::XCH_PITCH);
-        float* wmask = reinterpret_cast<float*>(smem + C::OFF_WMASK + warp * 256);
+        const uint32_t aStage = smem_u32(smem + C::OFF_STAGE);
+        const uint32_t aO = smem_u32(smem + C::OFF_O);
+        const uint32_t aXch = smem_u32(smem + C::OFF_XCH);            // [2 groups][128 rows] (m, l)
+        const uint32_t aWmask = smem_u32(smem + C::OFF_WMASK + warp * 256);
+        const uint32_t scratch_w = smem_u32(tmem_slot + 2);           // a word nobody reads
+        const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
         bool ok = true;
         int g = 0;
-        uint32_t g0_phase = 0;
-        auto g0_sync = [&]() -> bool {       // group 0 only (bounded)
+        uint32_t e_phase = 0;
+        // rendezvous of all eight softmax warps (bounded)
+        auto all_sync = [&](uint64_t* bar) -> bool {
             __syncwarp();
-            if (lane == 0) mbar_arrive(g0_bar);
-            const bool r = mbar_wait(g0_bar, g0_phase, wc, 0x30);
-            g0_phase ^= 1u;
-            return warp_all(r);
+            if (lane == 0) mbar_arrive(bar);
+            return warp_all(mbar_wait(bar, e_phase, wc, 0x30));
         };
 
-        float m = -INFINITY, l = 0.f;
-        float acc[DH];
-#pragma unroll
-        for (int i = 0; i < DH; ++i) acc[i] = 0.f;
+        float m_used = -INFINITY, l = 0.f;
 
-        // Finishes item `k` (coordinates pbs/pqt/ph) from its partial state (pm, pl, acc):
-        // group 1 hands its state over, group 0 merges, normalises and writes O / LSE.
-        auto epilogue = [&](int k, int pbs, int pqt, int ph, float pm, float pl) -> bool {
+        // Finishes item `k` (coordinates pbs/pqt/ph): the two groups exchange (m, l), and group wg
+        // merges, normalises and writes head-dim columns wg*DH/2 .. of O from BOTH groups'
+        // accumulators in tensor memory (any warp can read any column of its lanes).
+        auto epilogue = [&](int pbs, int pqt, int ph, float pm, float pl) -> bool {
             EVO_TS(t_epi);
-            if (wg == 1) {
-                if (k > 0 && !warp_all(mbar_wait(xch_empty, (k - 1) & 1, wc, 0x35))) return false;
-                xrow[0] = pm;
-                xrow[1] = pl;
-#pragma unroll
-                for (int c = 0; c < DH / 4; ++c)
-                    *reinterpret_cast<float4*>(xrow + 4 + c * 4) =
-                        make_float4(acc[c * 4 + 0], acc[c * 4 + 1], acc[c * 4 + 2], acc[c * 4 + 3]);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(xch_full);
+            constexpr int HD = DH / 2;
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aXch + (wg * 128 + row) * 8), "f"(pm), "f"(pl) : "memory");
+            // the previous O store must have finished reading sO before it is rewritten
+            if (tid == 0) tma_wait_group_read<0>();
+            if (!all_sync(e_bar)) return false;
+            tc_fence_after();          // the other group's last PV is complete too (it waited for it before arriving)
+            float om, ol;
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(om), "=f"(ol) : "r"(aXch + ((wg ^ 1) * 128 + row) * 8));
+            const float mt = fmaxf(pm, om);
+            const float ms = (mt == -INFINITY) ? 0.f : mt;
+            const float f = ex2(pm - ms), fo = ex2(om - ms);
+            const float lt = pl * f + ol * fo;
+            const float inv = 1.f / lt;
+            const float fa = f * inv, fb = fo * inv;
+            float mine[HD], other[HD];
+            if constexpr (HD == 16) {
+                tmem_ld_f32<16>(lane_base + C::TMEM_PV + wg * DH + wg * HD, mine);
+                tmem_ld_f32<16>(lane_base + C::TMEM_PV + (wg ^ 1) * DH + wg * HD, other);
             } else {
-                if (!warp_all(mbar_wait(xch_full, k & 1, wc, 0x36))) return false;
-                const float om = xrow[0], ol = xrow[1];
-                const float mt = fmaxf(pm, om);            // finite: column 0 of tile 0 is never -inf
-                const float f = ex2(pm - mt), fo = ex2(om - mt);
-                const float lt = pl * f + ol * fo;
-                const float inv = 1.f / lt;
-                float outv[DH];
+                tmem_ld_f32<32>(lane_base + C::TMEM_PV + wg * DH + wg * HD, mine);
+                tmem_ld_f32<32>(lane_base + C::TMEM_PV + (wg ^ 1) * DH + wg * HD, other);
+            }
+            tc_fence_before();
+            const int qrow = pqt * TILE + row;
 #pragma unroll
-                for (int c = 0; c < DH / 4; ++c) {
-                    const float4 v = *reinterpret_cast<const float4*>(xrow + 4 + c * 4);
-                    outv[c * 4 + 0] = (acc[c * 4 + 0] * f + v.x * fo) * inv;
-                    outv[c * 4 + 1] = (acc[c * 4 + 1] * f + v.y * fo) * inv;
-                    outv[c * 4 + 2] = (acc[c * 4 + 2] * f + v.z * fo) * inv;
-                    outv[c * 4 + 3] = (acc[c * 4 + 3] * f + v.w * fo) * inv;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(xch_empty);
-                // the previous O store must have finished reading sO before it is rewritten
-                if (tid == 0) tma_wait_group_read<0>();
-                if (!g0_sync()) return false;
-                const int qrow = pqt * TILE + row;
+            for (int c8 = 0; c8 < HD / 8; ++c8) {
+                float outv[8];
 #pragma unroll
-                for (int c8 = 0; c8 < DH / 8; ++c8) {
-                    uint4 v;
-                    v.x = pack_bf16(outv[c8 * 8 + 0], outv[c8 * 8 + 1]);
-                    v.y = pack_bf16(outv[c8 * 8 + 2], outv[c8 * 8 + 3]);
-                    v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
-                    v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
-                    *reinterpret_cast<uint4*>(sO + swz_off<RT::ROW_BYTES>(row, c8)) = v;
-                    if (p.o_resid != nullptr && qrow < p.N) {
-                        // rounding residual of O, straight to global memory
-                        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-                        uint32_t rw[4];
+                for (int e = 0; e < 8; ++e) outv[e] = mine[c8 * 8 + e] * fa + other[c8 * 8 + e] * fb;
+                uint4 v;
+                v.x = pack_bf16(outv[0], outv[1]);
+                v.y = pack_bf16(outv[2], outv[3]);
+                v.z = pack_bf16(outv[4], outv[5]);
+                v.w = pack_bf16(outv[6], outv[7]);
+                const int chunk = wg * (HD / 8) + c8;             // 16-byte chunk of the row
+                sts128(aO + swz_off<RT::ROW_BYTES>(row, chunk), v);
+                if (p.o_resid != nullptr && qrow < p.N) {
+                    // rounding residual of O, straight to global memory
+                    const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                    uint32_t rw[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]),
-                                              outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
-                        __nv_bfloat16* dst;
-                        if constexpr (STRIDED)
-                            dst = p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + c8 * 8;
-                        else
-                            dst = p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + c8 * 8;
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
-                    }
+                    for (int e = 0; e < 4; ++e)
+                        rw[e] = pack_bf16(outv[2 * e] - bf16_lo(vw[e]), outv[2 * e + 1] - bf16_hi(vw[e]));
+                    __nv_bfloat16* dst;
+                    if constexpr (STRIDED)
+                        dst = p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + chunk * 8;
+                    else
+                        dst = p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + chunk * 8;
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
                 }
-                if (qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = mt * LN2 + __logf(lt);
-                fence_async_smem();
-                if (!g0_sync()) return false;
-                if (tid == 0) {
-                    tma_store_4d(&tm_o, sO, 0, ph, pqt * TILE, pbs);
-                    tma_commit_group();
-                }
+            }
+            if (wg == 0 && qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = ms * LN2 + __logf(lt);
+            fence_async_smem();
+            // both halves of sO are written, and both groups have read the accumulators
+            if (!all_sync(e_bar + 1)) return false;
+            e_phase ^= 1u;
+            if (tid == 0) {
+                tma_store_4d(&tm_o, smem + C::OFF_O, 0, ph, pqt * TILE, pbs);
+                tma_commit_group();
             }
             EVO_TE(t_epi, p.status, 0x79);
             return true;
@@ -369,102 +366,112 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; it < n_items && ok; ++it) {
             int bs, qt, h;
             decode(it, bs, qt, h);
-            m = -INFINITY;
+            m_used = -INFINITY;
             l = 0.f;
             for (int j = 0; j < NT && ok; ++j, ++g) {
                 const int st = g % ST;
-                const uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
+                const uint32_t sb = aStage + st * C::STAGE_STRIDE;
                 const int sbuf = wg + 2 * (g & 1);
+                const uint32_t tS = lane_base + C::TMEM_S + (g & 1) * 128 + 64 * wg;
                 ok = warp_all(mbar_wait(&s_full[sbuf], (g >> 1) & 1, wc, 0x31));
                 if (!ok) break;
                 EVO_TS(t_tile);
                 tc_fence_after();
-                EVO_TS(t_a);
-                uint32_t sr[64];
-                {
-                    uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
-                    uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
-                    tmem_ld32(lane_base + C::TMEM_S + (g & 1) * 128 + 64 * wg, lo);
-                    tmem_ld32(lane_base + C::TMEM_S + (g & 1) * 128 + 64 * wg + 32, hi);
-                    tmem_wait_ld();
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s_free[sbuf]);
-                EVO_TE(t_a, p.status, 0x70);
+                uint32_t sv[2][16];
+                tmem_ld16(tS, sv[0]);
 
                 ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x32));
                 if (!ok) break;
-                EVO_TS(t_b);
                 {
                     // this warp's copy of the mask row slice: bf16 -> fp32 * log2e, -inf past N
-                    const __nv_bfloat16* mraw = reinterpret_cast<const __nv_bfloat16*>(sb + C::ST_MASK) + 64 * wg;
-#pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        const int c = lane + 32 * t;
-                        wmask[c] = (j * TILE + 64 * wg + c < p.N) ? __bfloat162float(mraw[c]) * LOG2E : -INFINITY;
-                    }
+                    const uint32_t mraw = sb + C::ST_MASK + 128 * wg + 4 * lane;      // two bf16 per lane
+                    uint32_t mw;
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(mw) : "r"(mraw));
+                    const int c = j * TILE + 64 * wg + 2 * lane;
+                    const float m0 = (c < p.N) ? bf16_lo(mw) * LOG2E : -INFINITY;
+                    const float m1 = (c + 1 < p.N) ? bf16_hi(mw) * LOG2E : -INFINITY;
+                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aWmask + 8 * lane), "f"(m0), "f"(m1) : "memory");
                     __syncwarp();
                 }
-                EVO_TE(t_b, p.status, 0x71);
-                EVO_TS(t_c);
-                const uint8_t* sbias = sb + C::ST_BIAS + wg * SQ_SUB_BYTES;
-                // x = S*c1 + (bias*log2e + mask*log2e), two columns per instruction
-                const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
+                // x = S*c1 + (bias*log2e + mask*log2e), in chunks of 16 columns; the tensor-memory
+                // load of chunk ch+1 is in flight during the arithmetic of chunk ch
+                float2 x2[32];
                 float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: ILP
+                uint32_t dep = 0;
+                const uint32_t sbias = sb + C::ST_BIAS + wg * SQ_SUB_BYTES;
 #pragma unroll
-                for (int c8 = 0; c8 < 8; ++c8) {
-                    const uint4 bv = *reinterpret_cast<const uint4*>(sbias + swz_off<128>(row, c8));
-                    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-                    const float4 ma = *reinterpret_cast<const float4*>(wmask + c8 * 8);
-                    const float4 mb = *reinterpret_cast<const float4*>(wmask + c8 * 8 + 4);
-                    const float2 mm[4] = {make_float2(ma.x, ma.y), make_float2(ma.z, ma.w),
-                                          make_float2(mb.x, mb.y), make_float2(mb.z, mb.w)};
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int cb = ch & 1;
+                    tmem_wait_ld();
+                    if (ch < 3) {
+                        tmem_ld16(tS + 16 * (ch + 1), sv[cb ^ 1]);
+                    } else {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&s_free[sbuf]);
+                    }
+                    const uint4 b0 = lds128(sbias + swz_off<128>(row, 2 * ch));
+                    const uint4 b1 = lds128(sbias + swz_off<128>(row, 2 * ch + 1));
+                    dep ^= b0.x ^ b1.x;
+                    const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                    float2 mm[8];
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        const int c = c8 * 8 + 2 * w;
-                        const float2 t2 = ffma2(bf16x2_f2(bw[w]), l2e2, mm[w]);
-                        const float2 x2 = ffma2(u2f2(sr[c], sr[c + 1]), c1x2, t2);
-                        sr[c] = __float_as_uint(x2.x);
-                        sr[c + 1] = __float_as_uint(x2.y);
-                        tmx[w] = fmax3(tmx[w], x2.x, x2.y);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 mv = lds128f(aWmask + 64 * ch + 16 * q4);
+                        mm[2 * q4] = make_float2(mv.x, mv.y);
+                        mm[2 * q4 + 1] = make_float2(mv.z, mv.w);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const float2 t2 = ffma2(bf16x2_f2(bw[k]), l2e2, mm[k]);
+                        const float2 xx = ffma2(u2f2(sv[cb][2 * k], sv[cb][2 * k + 1]), c1x2, t2);
+                        x2[ch * 8 + k] = xx;
+                        tmx[k & 3] = fmax3(tmx[k & 3], xx.x, xx.y);
                     }
                 }
-                mbar_release_after_reads(&kv_empty[st]);      // bias tile and mask row are read
-                EVO_TE(t_c, p.status, 0x72);
-                EVO_TS(t_d);
+                mbar_release_after_loads(&kv_empty[st], dep, scratch_w);      // bias tile and mask row are read
 
                 const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
-                const float m_new = fmaxf(m, tmax);
-                const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = ex2(m - m_safe);
+                const float m_new = fmaxf(m_used, tmax);
+                // When the running maximum rises (by more than EVO_FWD_LAZY), the accumulator in
+                // tensor memory and the row sum are rescaled; otherwise the tensor core simply keeps
+                // accumulating into the same tile.
+                const bool need = (j > 0) && (m_new - m_used > EVO_FWD_LAZY);
+                const float m_old = m_used;
+                if (j == 0 || need) m_used = m_new;
+                const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
                 // P = exp2(x - m), packed to bf16 pairs; row sum in two packed chains
                 uint32_t pk[32];
+                float rsum;
                 {
                     const float2 nm2 = make_float2(-m_safe, -m_safe);
                     float2 rs[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
-                        const float2 d2 = fadd2(u2f2(sr[2 * c], sr[2 * c + 1]), nm2);
+                        const float2 d2 = fadd2(x2[c], nm2);
                         const float2 p2 = make_float2(ex2(d2.x), ex2(d2.y));
                         rs[c & 1] = fadd2(rs[c & 1], p2);
                         pk[c] = pack_bf16(p2.x, p2.y);
                     }
-                    l = l * alpha + ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y));
+                    rsum = (rs[0].x + rs[0].y) + (rs[1].x + rs[1].y);
                 }
-                m = m_new;
-                EVO_TE(t_d, p.status, 0x73);
-                EVO_TS(t_e);
 
-                // The P columns in tensor memory are free once the previous tile's PV MMA is
-                // done; its result is folded in here.  On the first tile of an item that
-                // previous tile belongs to the previous item, whose epilogue runs now.
+                // The P columns in tensor memory are free once the previous tile's PV MMA is done.
+                // On the first tile of an item that previous tile belongs to the previous item, whose
+                // epilogue runs now (its last PV has had the whole softmax above to finish).
                 if (j > 0 || have_prev) {
                     ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x33));
                     if (!ok) break;
                     tc_fence_after();
-                    const float sc = (j > 0) ? alpha : 1.0f;
-                    const float2 sc2 = make_float2(sc, sc);
+                }
+                if (j == 0 && have_prev) {
+                    ok = epilogue(pbs, pqt, ph, pm, pl);
+                    if (!ok) break;
+                }
+                if (__any_sync(0xffffffffu, need)) {
+                    // rare: rescale this group's accumulator (lanes that need nothing scale by 1)
+                    const float alpha = need ? ex2(m_old - m_safe) : 1.0f;
+                    const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
                     for (int c = 0; c < DH / 32; ++c) {
                         uint32_t r[32];
@@ -472,49 +479,33 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
-                            const float2 a2 = fmul2(fadd2(make_float2(acc[c * 32 + i], acc[c * 32 + i + 1]),
-                                                          u2f2(r[i], r[i + 1])), sc2);
-                            acc[c * 32 + i] = a2.x;
-                            acc[c * 32 + i + 1] = a2.y;
+                            const float2 v2 = fmul2(u2f2(r[i], r[i + 1]), a2);
+                            r[i] = __float_as_uint(v2.x);
+                            r[i + 1] = __float_as_uint(v2.y);
                         }
+                        tmem_st32(lane_base + C::TMEM_PV + wg * DH + c * 32, r);
                     }
-                    EVO_TE(t_e, p.status, 0x74);
-                    if (j == 0) {
-                        ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
-                        if (!ok) break;
-#pragma unroll
-                        for (int i = 0; i < DH; ++i) acc[i] = 0.f;
-                    }
+                    l *= alpha;
                 }
+                l += rsum;
                 // P (bf16 pairs) into this group's 32 columns of tensor memory
-                EVO_TS(t_f);
                 tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[wg]);
-                EVO_TE(t_f, p.status, 0x75);
                 EVO_TE(t_tile, p.status, 0x78);
             }
             have_prev = true;
             pbs = bs; pqt = qt; ph = h;
-            pm = m; pl = l;
+            pm = m_used; pl = l;
         }
         if (ok && have_prev) {
             // last item: its final PV and epilogue
             ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x34));
             if (ok) {
                 tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < DH / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_base + C::TMEM_PV + wg * DH + c * 32, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
-                }
-                tc_fence_before();
-                ok = epilogue(n_items - 1, pbs, pqt, ph, pm, pl);
+                ok = epilogue(pbs, pqt, ph, pm, pl);
             }
         }
         if (tid == 0) tma_wait_group<0>();
