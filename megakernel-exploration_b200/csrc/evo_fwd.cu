@@ -61,12 +61,14 @@ struct FwdCfg {
     static constexpr uint32_t STAGE_STRIDE = 2 * ROWT + SQ_BYTES + 1024;
     static constexpr uint32_t OFF_Q = 0;                           // 2 buffers
     static constexpr uint32_t OFF_STAGE = OFF_Q + 2 * ROWT;
+    // O staging: one [128][DH/2] half tile per softmax group (each group stores its own columns)
     static constexpr uint32_t OFF_O = OFF_STAGE + STAGES * STAGE_STRIDE;
-    // exchange of the two groups' (m, l) per row
+    static constexpr uint32_t O_HALF = ROWT / 2;
+    // exchange of the two groups' (m, l) per row: [item parity][group][128 rows]
     static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
-    static constexpr uint32_t OFF_WMASK = OFF_XCH + 2 * 128 * 8;           // 8 warps x 64 floats
+    static constexpr uint32_t OFF_WMASK = OFF_XCH + 2 * 2 * 128 * 8;       // 8 warps x 64 floats
     static constexpr uint32_t OFF_BARS = OFF_WMASK + 8 * 256;
-    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 8 + 2 + 2 + 3;
+    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 8 + 2 + 2 + 8;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
     static constexpr uint32_t TMEM_S = 0;                          // two buffers: + (tile & 1) * 128 + g * 64
@@ -114,7 +116,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* s_free = s_full + 4;           // [4]
     uint64_t* p_ready = s_free + 4;          // [2] per softmax group
     uint64_t* pv_full = p_ready + 2;         // [2]
-    uint64_t* e_bar = pv_full + 2;           // [2] rendezvous of the eight softmax warps in the epilogue
+    uint64_t* xch_ready = pv_full + 2;       // [item parity][group]: the group's final (m, l) of an item are written
+    uint64_t* o_read = xch_ready + 4;        // [group]: the group has read both accumulators of the finished item
+    uint64_t* g_bar = o_read + 2;            // [group]: rendezvous of the group's four warps
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -130,8 +134,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 9); }
         for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
         for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
-        mbar_init(&e_bar[0], 8);
-        mbar_init(&e_bar[1], 8);
+        for (int i = 0; i < 4; ++i) mbar_init(&xch_ready[i], 4);
+        for (int i = 0; i < 2; ++i) { mbar_init(&o_read[i], 4); mbar_init(&g_bar[i], 4); }
         fence_mbar_init();
         fence_async_smem();
     }
@@ -280,29 +284,34 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
         bool ok = true;
         int g = 0;
-        uint32_t e_phase = 0;
-        // rendezvous of all eight softmax warps (bounded)
-        auto all_sync = [&](uint64_t* bar) -> bool {
+        uint32_t g_phase = 0;
+        // rendezvous of this group's four warps (bounded)
+        auto group_sync = [&]() -> bool {
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar);
-            return warp_all(mbar_wait(bar, e_phase, wc, 0x30));
+            if (lane == 0) mbar_arrive(&g_bar[wg]);
+            const bool r = warp_all(mbar_wait(&g_bar[wg], g_phase, wc, 0x30));
+            g_phase ^= 1u;
+            return r;
         };
 
         float m_used = -INFINITY, l = 0.f;
 
-        // Finishes item `k` (coordinates pbs/pqt/ph): the two groups exchange (m, l), and group wg
-        // merges, normalises and writes head-dim columns wg*DH/2 .. of O from BOTH groups'
-        // accumulators in tensor memory (any warp can read any column of its lanes).
-        auto epilogue = [&](int pbs, int pqt, int ph, float pm, float pl) -> bool {
+        // Finishes item `k` (coordinates pbs/pqt/ph).  Each group merges, normalises and stores
+        // head-dim columns wg*DH/2 .. of O, reading BOTH groups' accumulators from tensor memory
+        // (any warp can read any column of its lanes); the other group's (m, l) come through
+        // shared memory, written when that group finished the item.  Nothing here makes the two
+        // groups meet: every wait is for something the other group did a whole tile earlier.
+        auto epilogue = [&](int k, int pbs, int pqt, int ph, float pm, float pl) -> bool {
             EVO_TS(t_epi);
             constexpr int HD = DH / 2;
-            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aXch + (wg * 128 + row) * 8), "f"(pm), "f"(pl) : "memory");
-            // the previous O store must have finished reading sO before it is rewritten
-            if (tid == 0) tma_wait_group_read<0>();
-            if (!all_sync(e_bar)) return false;
-            tc_fence_after();          // the other group's last PV is complete too (it waited for it before arriving)
+            if (!warp_all(mbar_wait(&xch_ready[(k & 1) * 2 + (wg ^ 1)], (k >> 1) & 1, wc, 0x35))) return false;
+            // the other group's last PV of the item (its accumulator is read below); that barrier cannot
+            // run a phase ahead: the other group's next PV waits for this group's o_read arrival
+            if (!warp_all(mbar_wait(&pv_full[wg ^ 1], ((k + 1) * NT - 1) & 1, wc, 0x37))) return false;
+            tc_fence_after();
             float om, ol;
-            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(om), "=f"(ol) : "r"(aXch + ((wg ^ 1) * 128 + row) * 8));
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(om), "=f"(ol)
+                         : "r"(aXch + (((k & 1) * 2 + (wg ^ 1)) * 128 + row) * 8));
             const float mt = fmaxf(pm, om);
             const float ms = (mt == -INFINITY) ? 0.f : mt;
             const float f = ex2(pm - ms), fo = ex2(om - ms);
@@ -318,7 +327,13 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tmem_ld_f32<32>(lane_base + C::TMEM_PV + (wg ^ 1) * DH + wg * HD, other);
             }
             tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_read[wg]);       // this warp is done with both accumulators
+            // the previous store of this group's half tile must have finished reading it
+            if (row == 0) tma_wait_group_read<0>();
+            if (!group_sync()) return false;
             const int qrow = pqt * TILE + row;
+            const uint32_t sO = aO + wg * C::O_HALF;
 #pragma unroll
             for (int c8 = 0; c8 < HD / 8; ++c8) {
                 float outv[8];
@@ -329,8 +344,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 v.y = pack_bf16(outv[2], outv[3]);
                 v.z = pack_bf16(outv[4], outv[5]);
                 v.w = pack_bf16(outv[6], outv[7]);
-                const int chunk = wg * (HD / 8) + c8;             // 16-byte chunk of the row
-                sts128(aO + swz_off<RT::ROW_BYTES>(row, chunk), v);
+                sts128(sO + swz_off<RT::ROW_BYTES / 2>(row, c8), v);
                 if (p.o_resid != nullptr && qrow < p.N) {
                     // rounding residual of O, straight to global memory
                     const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
@@ -340,21 +354,21 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         rw[e] = pack_bf16(outv[2 * e] - bf16_lo(vw[e]), outv[2 * e + 1] - bf16_hi(vw[e]));
                     __nv_bfloat16* dst;
                     if constexpr (STRIDED)
-                        dst = p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + chunk * 8;
+                        dst = p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + wg * HD + c8 * 8;
                     else
-                        dst = p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + chunk * 8;
+                        dst = p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + wg * HD + c8 * 8;
                     *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
                 }
             }
             if (wg == 0 && qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = ms * LN2 + __logf(lt);
             fence_async_smem();
-            // both halves of sO are written, and both groups have read the accumulators
-            if (!all_sync(e_bar + 1)) return false;
-            e_phase ^= 1u;
-            if (tid == 0) {
-                tma_store_4d(&tm_o, smem + C::OFF_O, 0, ph, pqt * TILE, pbs);
+            if (!group_sync()) return false;
+            if (row == 0) {
+                tma_store_4d(&tm_o, smem + C::OFF_O + wg * C::O_HALF, wg * HD, ph, pqt * TILE, pbs);
                 tma_commit_group();
             }
+            // the other group has read this group's accumulator: the next item's first PV may overwrite it
+            if (!warp_all(mbar_wait(&o_read[wg ^ 1], k & 1, wc, 0x36))) return false;
             EVO_TE(t_epi, p.status, 0x79);
             return true;
         };
@@ -465,7 +479,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tc_fence_after();
                 }
                 if (j == 0 && have_prev) {
-                    ok = epilogue(pbs, pqt, ph, pm, pl);
+                    ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
                     if (!ok) break;
                 }
                 if (__any_sync(0xffffffffu, need)) {
@@ -496,6 +510,12 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (lane == 0) mbar_arrive(&p_ready[wg]);
                 EVO_TE(t_tile, p.status, 0x78);
             }
+            if (!ok) break;
+            // publish this group's (m, l) of the item for the other group's epilogue
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aXch + (((it & 1) * 2 + wg) * 128 + row) * 8),
+                         "f"(m_used), "f"(l) : "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xch_ready[(it & 1) * 2 + wg]);
             have_prev = true;
             pbs = bs; pqt = qt; ph = h;
             pm = m_used; pl = l;
@@ -505,10 +525,10 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x34));
             if (ok) {
                 tc_fence_after();
-                ok = epilogue(pbs, pqt, ph, pm, pl);
+                ok = epilogue(n_items - 1, pbs, pqt, ph, pm, pl);
             }
         }
-        if (tid == 0) tma_wait_group<0>();
+        if (row == 0) tma_wait_group<0>();
     }
 
     if (tid == 0) EVO_TE(t_kernel, p.status, 0x7e);
@@ -532,7 +552,7 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE, lay))) return rc;
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE, lay))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
-    if ((rc = make_tmap_qkv(&to, o, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    if ((rc = make_tmap_qkv_cols(&to, o, BS, d->N, d->H, DH, TILE, DH / 2, lay))) return rc;   // half-tile stores
 
     FwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;

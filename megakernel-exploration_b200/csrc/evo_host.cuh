@@ -48,6 +48,9 @@ int layout_from_strides(const EvoDims* d, const EvoStrides* s, ActLayout* out);
 // head's [rows x D] tile, swizzled by row.
 int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows,
                   const ActLayout& lay);
+// The same view with a box of [rows x cols] head-dim columns (cols * 2 bytes = 32, 64 or 128), swizzled by box row.
+int make_tmap_qkv_cols(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows, int cols,
+                       const ActLayout& lay);
 // [BS][N][H][D] of `elem_bytes`-wide elements (2: bf16, 4: fp32) with a box of
 // [rows x box_cols]; the swizzle matches the box row (32, 64 or 128 bytes).
 int make_tmap_rows_box(CUtensorMap* out, const void* base, int elem_bytes, int BS, int N, int H, int D,
