@@ -108,8 +108,8 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], NCW); }
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 2); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 2); mbar_init(&sdp_free[i], NCW); }
         fence_mbar_init();
         fence_async_smem();
     }
@@ -181,40 +181,41 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 for (int k = (gs > QS ? gs - QS : 0); k < gs; ++k)
                     (void)mbar_wait(&st_full[k % QS], (k / QS) & 1, wc, 0x83);
             }
-        } else if (warp == NCW + 1) {
-            if (lane == 0) {
-                // ------------------------------ mma issuer ------------------------------
-                constexpr uint32_t IDESC = make_idesc_bf16(128, 128, 0, 0);
-                const uint32_t aSt = smem_u32(smem);
-                const uint32_t aZero = aSt + C::OFF_ZERO;
-                const uint64_t d_xdp = xt_desc(aSt + C::OFF_XDP, aZero);
-                bool ok = true;
-                int gs = 0;
-                for (int it = 0; it < n_items && ok; ++it) {
-                    const DbItem x = decode(it);
-                    for (int n = 0; n < x.ns && ok; ++n, ++gs) {
-                        const int st = gs % QS, buf = gs & 1;
-                        ok = mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x90);
-                        if (ok && gs >= 2) ok = mbar_wait(&sdp_free[buf], ((gs >> 1) - 1) & 1, wc, 0x91);
-                        if (!ok) break;
-                        tc_fence_after();
+        } else if (warp == NCW + 1 || warp == NCW + 2) {
+            // ------------------------------ mma issuers ------------------------------
+            // warp NCW+1 issues S' = Q K^T + extra block, warp NCW+2 issues dP' = dO V^T + extra
+            // block, so that neither chain queues behind the other's issue.  Each warp runs its
+            // loop with all lanes (uniform control flow keeps the operand descriptors in uniform
+            // registers) and elects one lane to issue.
+            constexpr uint32_t IDESC = make_idesc_bf16(128, 128, 0, 0);
+            const bool is_dp = (warp == NCW + 2);
+            const uint32_t aSt = smem_u32(smem);
+            const uint32_t aZero = aSt + C::OFF_ZERO;
+            bool ok = true;
+            int gs = 0;
+            for (int it = 0; it < n_items && ok; ++it) {
+                const DbItem x = decode(it);
+                for (int n = 0; n < x.ns && ok; ++n, ++gs) {
+                    const int st = gs % QS, buf = gs & 1;
+                    ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x90));
+                    if (ok && gs >= 2) ok = warp_all(mbar_wait(&sdp_free[buf], ((gs >> 1) - 1) & 1, wc, 0x91));
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (elect_one()) {
                         const uint32_t sb = aSt + st * C::STAGE_STRIDE;
-                        const uint32_t t0 = tmem + buf * 256;
-                        const uint32_t q_lo = RD::kmajor_lo(sb + C::ST_Q), k_lo = RD::kmajor_lo(sb + C::ST_K);
-                        const uint32_t do_lo = RD::kmajor_lo(sb + C::ST_DO), v_lo = RD::kmajor_lo(sb + C::ST_V);
-                        // two interleaved chains: consecutive MMAs use different accumulators
+                        const uint32_t t0 = tmem + buf * 256 + (is_dp ? 128u : 0u);
+                        const uint32_t a_lo = RD::kmajor_lo(sb + (is_dp ? C::ST_DO : C::ST_Q));
+                        const uint32_t b_lo = RD::kmajor_lo(sb + (is_dp ? C::ST_V : C::ST_K));
 #pragma unroll
-                        for (int kk = 0; kk < RT::KBLOCKS; ++kk) {
-                            umma_ss(t0, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC, kk > 0);
-                            umma_ss(t0 + 128, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC, kk > 0);
-                        }
+                        for (int kk = 0; kk < RT::KBLOCKS; ++kk)
+                            umma_ss(t0, RD::kmajor(a_lo, kk), RD::kmajor(b_lo, kk), IDESC, kk > 0);
                         // + (mask - LSE) / scale on S, - delta on dP: the extra contraction block
-                        const uint64_t d_xq = xt_desc(sb + C::ST_XQ, aZero);
-                        umma_ss(t0, d_xq, xt_desc(sb + C::ST_XK, aZero), IDESC, 1u);
-                        umma_ss(t0 + 128, d_xq, d_xdp, IDESC, 1u);
+                        umma_ss(t0, xt_desc(sb + C::ST_XQ, aZero),
+                                xt_desc(is_dp ? aSt + C::OFF_XDP : sb + C::ST_XK, aZero), IDESC, 1u);
                         umma_commit(&sdp_full[buf]);
                         umma_commit(&st_empty[st]);
                     }
+                    __syncwarp();
                 }
             }
         }
