@@ -68,7 +68,7 @@ struct FwdCfg {
     static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
     static constexpr uint32_t OFF_WMASK = OFF_XCH + 2 * 2 * 128 * 8;       // 8 warps x 64 floats
     static constexpr uint32_t OFF_BARS = OFF_WMASK + 8 * 256;
-    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 8 + 2 + 2 + 8;
+    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 8 + 2 + 2 + 8 + 2;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
     static constexpr uint32_t TMEM_S = 0;                          // two buffers: + (tile & 1) * 128 + g * 64
@@ -119,6 +119,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* xch_ready = pv_full + 2;       // [item parity][group]: the group's final (m, l) of an item are written
     uint64_t* o_read = xch_ready + 4;        // [group]: the group has read both accumulators of the finished item
     uint64_t* g_bar = o_read + 2;            // [group]: rendezvous of the group's four warps
+    uint64_t* xu_done = g_bar + 2;           // [group]: the group has finished the exp2 pass of a tile
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -135,7 +136,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
         for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
         for (int i = 0; i < 4; ++i) mbar_init(&xch_ready[i], 4);
-        for (int i = 0; i < 2; ++i) { mbar_init(&o_read[i], 4); mbar_init(&g_bar[i], 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&o_read[i], 4); mbar_init(&g_bar[i], 4); mbar_init(&xu_done[i], 4); }
         fence_mbar_init();
         fence_async_smem();
     }
@@ -217,8 +218,10 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int qb = it & 1;
                 for (int j = 0; j < NT && ok; ++j, ++g) {
                     const int st = g % ST;
+                    EVO_TL(p.status, 1, g, 0);
                     if (j == 0) ok = warp_all(mbar_wait(&q_full[qb], (it >> 1) & 1, wc, 0x20));
                     if (ok) ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x21));
+                    EVO_TL(p.status, 1, g, 1);
 #pragma unroll
                     for (int w = 0; w < 2; ++w) {
                         const int sb = w + 2 * (g & 1);
@@ -237,6 +240,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             if (w == 1 && j == NT - 1) umma_commit(&q_empty[qb]);
                         }
                         __syncwarp();
+                        EVO_TL(p.status, 1, g, 2 + w);
                     }
                 }
             }
@@ -255,6 +259,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     for (int w = 0; w < 2; ++w) {
                         ok = warp_all(mbar_wait(&p_ready[w], g & 1, wc, 0x23));
                         if (!ok) break;
+                        EVO_TL(p.status, 2, g, 2 * w);
                         tc_fence_after();
                         if (elect_one()) {
 #pragma unroll
@@ -266,6 +271,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             if (w == 1) umma_commit(&kv_empty[st]);   // both groups' PV of the tile issued
                         }
                         __syncwarp();
+                        EVO_TL(p.status, 2, g, 2 * w + 1);
                     }
                 }
             }
@@ -387,8 +393,10 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const uint32_t sb = aStage + st * C::STAGE_STRIDE;
                 const int sbuf = wg + 2 * (g & 1);
                 const uint32_t tS = lane_base + C::TMEM_S + (g & 1) * 128 + 64 * wg;
+                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 0);
                 ok = warp_all(mbar_wait(&s_full[sbuf], (g >> 1) & 1, wc, 0x31));
                 if (!ok) break;
+                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 1);
                 EVO_TS(t_tile);
                 tc_fence_after();
                 uint32_t sv[2][16];
@@ -444,6 +452,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
                 mbar_release_after_loads(&kv_empty[st], dep, scratch_w);      // bias tile and mask row are read
+                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 2);
 
                 const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
                 const float m_new = fmaxf(m_used, tmax);
@@ -454,6 +463,19 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const float m_old = m_used;
                 if (j == 0 || need) m_used = m_new;
                 const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+                // The exp2 pass loads the special-function unit, the passes around it the other pipes.
+                // Left alone the two groups run in lockstep, both in the same pass at the same time.
+                // At D = 32 they take turns instead: group 0 runs the exp2 pass of tile g, then group 1
+                // runs its own, while the other group is in the fused-multiply-add pass of its next tile
+                // or in its epilogue (measured 0.468 -> 0.440 ms at B=1, S=512, N=384, H=8; one warp per
+                // scheduler cannot saturate the unit alone, so the gain is small, and at D = 64, with
+                // its longer epilogue, taking turns measured 2 % slower).  Group 0 waits for group 1's
+                // pass of the previous tile, group 1 for group 0's pass of this tile.
+                constexpr bool PINGPONG = (DH == 32);
+                if (PINGPONG && (wg == 1 || g > 0)) {
+                    ok = warp_all(mbar_wait(&xu_done[wg ^ 1], (wg == 1 ? g : g - 1) & 1, wc, 0x38));
+                    if (!ok) break;
+                }
                 // P = exp2(x - m), packed to bf16 pairs; row sum in two packed chains
                 uint32_t pk[32];
                 float rsum;
@@ -469,10 +491,19 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                     rsum = (rs[0].x + rs[0].y) + (rs[1].x + rs[1].y);
                 }
+                if (PINGPONG) {
+                    // hand the unit over; the store orders the arrive behind the last exp2 of the pass
+                    __syncwarp();
+                    if (lane == 0) {
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(scratch_w), "r"(pk[31]) : "memory");
+                        mbar_arrive(&xu_done[wg]);
+                    }
+                }
 
                 // The P columns in tensor memory are free once the previous tile's PV MMA is done.
                 // On the first tile of an item that previous tile belongs to the previous item, whose
                 // epilogue runs now (its last PV has had the whole softmax above to finish).
+                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 3);
                 if (j > 0 || have_prev) {
                     ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x33));
                     if (!ok) break;
@@ -482,6 +513,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
                     if (!ok) break;
                 }
+                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 4);
                 if (__any_sync(0xffffffffu, need)) {
                     // rare: rescale this group's accumulator (lanes that need nothing scale by 1)
                     const float alpha = need ? ex2(m_old - m_safe) : 1.0f;
@@ -508,6 +540,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[wg]);
+                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 5);
                 EVO_TE(t_tile, p.status, 0x78);
             }
             if (!ok) break;

@@ -216,7 +216,7 @@ int ensure_context() {
 
 // One status word per device; kernels receive its address as an argument.
 #ifdef EVO_TRACE
-__device__ unsigned long long g_status_word[1 + 512] = {0};   // status word + cycle accounting
+__device__ unsigned long long g_status_word[1 + 512 + 8 * 64 * 8] = {0};   // status word + cycle accounting + timeline
 #else
 __device__ unsigned int g_status_word = 0;
 #endif
@@ -361,6 +361,16 @@ int evo_trace_read(unsigned long long* out) {
     rc = evo::cuda_err(cudaMemcpy(out, p + 2, 512 * 8, cudaMemcpyDeviceToHost));
     if (rc) return rc;
     return evo::cuda_err(cudaMemset(p + 2, 0, 512 * 8));
+}
+// Trace builds only: copies (and clears) the timeline of CTA 0: [8 roles][64 steps][8 events] clock values.
+int evo_timeline_read(unsigned long long* out) {
+    unsigned int* p = evo::status_word();
+    if (!p) return EVO_ERR_CUDA;
+    int rc = evo::cuda_err(cudaDeviceSynchronize());
+    if (rc) return rc;
+    rc = evo::cuda_err(cudaMemcpy(out, p + 2 + 1024, 8 * 64 * 8 * 8, cudaMemcpyDeviceToHost));
+    if (rc) return rc;
+    return evo::cuda_err(cudaMemset(p + 2 + 1024, 0, 8 * 64 * 8 * 8));
 }
 #endif
 

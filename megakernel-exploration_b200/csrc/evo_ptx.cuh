@@ -103,7 +103,11 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 
 // Optional cycle accounting (builds with -DEVO_TRACE only): per wait site / code
 // region, summed over warps and CTAs, in the words that follow the status word.
-#ifdef EVO_TRACE
+#if defined(EVO_TRACE) && defined(EVO_TL_ONLY)
+__device__ __forceinline__ void trace_add(unsigned int*, uint32_t, long long) {}
+__device__ __forceinline__ void trace_init() {}
+__device__ __forceinline__ void trace_flush(unsigned int*) {}
+#elif defined(EVO_TRACE)
 // accumulators live in shared memory during the kernel and are added to the global
 // words once at the end, so that tracing perturbs the timing as little as possible
 __device__ __forceinline__ unsigned long long* trace_smem() {
@@ -128,6 +132,16 @@ __device__ __forceinline__ void trace_flush(unsigned int* status) {
     for (int i = threadIdx.x; i < 512; i += blockDim.x)
         if (t[i]) atomicAdd(&g[i], t[i]);
 }
+#endif
+#ifdef EVO_TRACE
+// timeline of CTA 0 (trace builds): clock at (role, step, event), plain stores to global memory
+__device__ __forceinline__ void timeline(unsigned int* status, int role, int step, int evt) {
+    if (blockIdx.x == 0 && (threadIdx.x & 31u) == 0u && step < 64) {
+        unsigned long long* g = reinterpret_cast<unsigned long long*>(status + 2) + 512;
+        g[(role * 64 + step) * 8 + evt] = static_cast<unsigned long long>(clock64());
+    }
+}
+#define EVO_TL(status, role, step, evt) timeline((status), (role), (step), (evt))
 #define EVO_TRACE_INIT() trace_init()
 #define EVO_TRACE_FLUSH(status) trace_flush(status)
 #define EVO_T0() const long long evo_t0_ = clock64()
@@ -135,6 +149,7 @@ __device__ __forceinline__ void trace_flush(unsigned int* status) {
 #define EVO_TS(var) const long long var = clock64()
 #define EVO_TE(var, status, site) trace_add((status), (site), clock64() - var)
 #else
+#define EVO_TL(status, role, step, evt) do {} while (0)
 #define EVO_TRACE_INIT() do {} while (0)
 #define EVO_TRACE_FLUSH(status) do {} while (0)
 #define EVO_T0() do {} while (0)
