@@ -47,12 +47,73 @@ UNIT = "TFLOP/s"
 
 
 def _peaks():
+    """Measured dense bf16 peaks of this pool's B200s: `burst` for a kernel timed by itself,
+    `sustained` for one inside a seconds-long loop under the power cap."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return float(p["bf16_tflops_sustained"]), "measured sustained cuBLAS bf16 (MEASURED_PEAKS.json)"
-    return 1400.0, "fallback sustained bf16 estimate"
+        return {"burst": float(p["bf16_tflops"]), "sustained": float(p["bf16_tflops_sustained"]),
+                "source": "measured cuBLAS bf16, burst (MEASURED_PEAKS.json): the timed loop is a fraction of a "
+                          "second at full clock"}
+    return {"burst": 1590.0, "sustained": 1400.0, "source": "fallback figures of an earlier measurement on this pool"}
+
+
+def _strong_cfg4(world, rank, dev, pg, TKEvoAttention, barrier, steps):
+    """Config 4 (B=1, S=1024, N=768, H=8, D=32) on one GPU (rank 0 alone, the others wait) and split over
+    all ranks along S, in the same process: {"ms_1gpu", "ms_Ngpu", "speedup"}."""
+    import torch.distributed as dist
+    name = "cfg4_large_msa"
+    B, S, N, H, D = wl.WORKLOADS[name][:5]
+    if S % world:
+        return None
+    bf = torch.bfloat16
+
+    def make(lo, hi):
+        q, k, v, mask, bias, d_o = wl.make_workload(name, lo, hi)
+        t = [x.to(dev, bf) for x in (q, k, v, d_o)] + [mask.to(dev, bf), bias.to(dev, bf)]
+        for x in (t[0], t[1], t[2], t[5]):
+            x.requires_grad_(True)
+        return t
+
+    def run(t, group, n):
+        Q, K, V, DO, M, PB = t
+
+        def one():
+            for x in (Q, K, V, PB):
+                x.grad = None
+            o = TKEvoAttention.apply(Q, K, V, M, PB) if group is None else TKEvoAttention.apply(Q, K, V, M, PB, group)
+            o.backward(DO)
+
+        for _ in range(3):
+            one()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    ms1 = torch.zeros(1, device=dev)
+    if rank == 0:
+        t = make(0, S)
+        ms1[0] = run(t, None, steps)
+        del t
+        torch.cuda.empty_cache()
+    barrier()
+    dist.broadcast(ms1, 0)
+    rows = S // world
+    t = make(rank * rows, (rank + 1) * rows)
+    barrier()
+    msn = torch.tensor([run(t, pg, steps)], device=dev)
+    dist.all_reduce(msn, op=dist.ReduceOp.MAX)
+    del t
+    torch.cuda.empty_cache()
+    return {"workload": name, "S_total": S, "S_per_gpu": rows, "steps": steps, "ms_1gpu": ms1.item(),
+            "ms_Ngpu": msn.item(), "speedup": ms1.item() / msn.item(),
+            "note": "device-resident fwd+bwd per step; N-GPU time is the max over ranks"}
 
 
 class ClockSampler:
@@ -128,44 +189,61 @@ def _cpu_fwd_bwd(name: str, rows: int, repeats: int):
     return wl.flops_fwd_bwd(B, rows, N, H, D) / sec / 1e12, sec, torch.get_num_threads()
 
 
-def run_reference(args, rank: int):
+def run_reference(args, rank: int, world: int):
     """The reference's path on the host CPU: its documented math restated in eager
-    PyTorch (the reference kernel itself needs ThunderKittens and an sm_90a GPU)."""
+    PyTorch (the reference kernel itself needs ThunderKittens and an sm_90a GPU).
+    Each step is one forward + backward over a bounded sample of the workload's S rows
+    (rows are independent problems, so TFLOP/s on a row subset is the workload's rate)."""
     if rank != 0:
         return
     name = args.workload
     B, S, N, H, D = wl.WORKLOADS[name][:5]
-    vals = []
+    if args.rows:
+        S = args.rows
+    S_total = S * world if args.scaling == "weak" else S
+    S_per_gpu = S if args.scaling == "weak" else S // world
     torch.set_num_threads(os.cpu_count() or 1)
     from oracle import evo_ref
-    # size the per-step sample so that the whole run takes about a minute
-    probe = wl.make_workload(name, 0, min(S, 4))
-    t0 = time.perf_counter()
-    evo_ref.evo_attention_fwd_bwd_ref(*probe[:3], probe[3], probe[4], probe[5])
-    per_row = (time.perf_counter() - t0) / min(S, 4)
-    rows = int(60.0 / max(args.steps + args.warmup, 1) / max(per_row, 1e-6))
-    rows = max(2, min(S, args.cpu_rows, rows))
+    rows = max(1, min(S, args.cpu_rows))
     q, k, v, mask, bias, d_o = wl.make_workload(name, 0, rows)
+    # one untimed pass (thread pool, allocator), then size the sample: the whole run stays within a few
+    # minutes, and never drops below 16 rows (smaller samples time the framework, not the math)
+    evo_ref.evo_attention_fwd_bwd_ref(q, k, v, mask, bias, d_o, s_chunk=32)
+    t0 = time.perf_counter()
+    evo_ref.evo_attention_fwd_bwd_ref(q, k, v, mask, bias, d_o, s_chunk=32)
+    per_pass = time.perf_counter() - t0
+    budget = 150.0 / max(args.steps + args.warmup, 1)
+    if per_pass > budget and rows > 16:
+        rows = max(16, int(rows * budget / per_pass))
+        q, k, v, mask, bias, d_o = wl.make_workload(name, 0, rows)
+    vals = []
     for i in range(args.warmup + args.steps):
         t0 = time.perf_counter()
         evo_ref.evo_attention_fwd_bwd_ref(q, k, v, mask, bias, d_o, s_chunk=32)
         dt = time.perf_counter() - t0
         if i >= args.warmup:
             vals.append(dt)
-    sec = sum(vals) / len(vals)
+    sec = statistics.median(vals)
     tf = wl.flops_fwd_bwd(B, rows, N, H, D) / sec / 1e12
-    sample = f"{rows} of {S} S rows of {name} per step (rows are independent), fp32 eager, S-chunked by 32"
+    sample = f"{rows} of {S_total} S rows of {name} per step (rows are independent), fp32 eager, S-chunked by 32"
     out = {
         "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": name, "B": B, "S": S, "N": N, "H": H, "D": D, "sample": sample},
+        "config": _config(name, B, S_total, S_per_gpu, N, H, D, world),
         "cpu_baseline": {"value": tf, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(out), flush=True)
+
+
+def _config(name, B, S_total, S_per_gpu, N, H, D, world):
+    """The `config` object both arms print (same keys, same values)."""
+    return {"workload": name, "B": B, "S_total": S_total, "S_per_gpu": S_per_gpu, "N": N, "H": H, "D": D,
+            "parallelism": f"S-sharded x{world}, pair bias replicated, NCCL all-reduce of dBias",
+            "l2": "each step streams > 126 MB (inputs larger than L2)"}
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
@@ -233,24 +311,32 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         torch.cuda.synchronize()
 
     def timed(fn, steps):
+        """Total milliseconds of `steps` calls (one event pair around the whole loop, max over ranks) and the
+        per-step milliseconds (an event at every step boundary, this rank)."""
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record()
+        for i in range(steps):
             fn()
-        e1.record()
+            ev[i + 1].record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        ms = torch.tensor([ev[0].elapsed_time(ev[steps])], device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return ms.item()
+        per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+        return ms.item(), per
 
     for _ in range(max(args.warmup, 3)):
         step()
     _evoattn.device_status()
-    _evoattn.profile_enable(True)
+    # headline: nothing but the steps inside the timed region
     with ClockSampler(local_rank) as cs:
-        ms_total = timed(step, args.steps)
+        ms_total, per_step = timed(step, args.steps)
+    _evoattn.device_status()
+    # a second, short loop with the library's per-kernel events, for the roofline figures only
+    prof_steps = max(3, min(args.steps, 20))
+    _evoattn.profile_enable(True)
+    timed(step, prof_steps)
     _evoattn.profile_enable(False)
     fwd_ms, fwd_n = _evoattn.profile_read(0)
     bwd_ms, bwd_n = _evoattn.profile_read(1)
@@ -260,25 +346,60 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
         step_e2e()
-    ms_e2e = timed(step_e2e, e2e_steps)
+    ms_e2e, _ = timed(step_e2e, e2e_steps)
     _evoattn.device_status()
+
+    # ---- N > 1: the overlapped, phased backward against a plain all-reduce of the partial dBias ----
+    multi_gpu_check = None
+    if world > 1:
+        PB32 = PB.detach().float().requires_grad_(True)            # fp32 leaf: d_pair_bias comes back in fp32
+
+        def grads(group):
+            for t in (Q, K, V, PB32):
+                t.grad = None
+            o = TKEvoAttention.apply(Q, K, V, M, PB32) if group is None else TKEvoAttention.apply(Q, K, V, M, PB32, group)
+            o.backward(DO)
+            return [t.grad.detach().clone() for t in (Q, K, V, PB32)]
+
+        got = grads(pg)                                             # phased backward, overlapped all-reduce
+        part = grads(None)                                          # this rank's rows alone, no group
+        dist.all_reduce(part[3], op=dist.ReduceOp.SUM)              # default group, blocking
+        db_err = (got[3].float() - part[3].float()).abs().max()
+        dq_err = (got[0].float() - part[0].float()).abs().max()
+        same = torch.tensor([float(torch.equal(got[1], part[1]) and torch.equal(got[2], part[2]))], device=dev)
+        stats = torch.stack([db_err, dq_err, 1.0 - same[0]])
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        db_e, dq_e, diff = (float(x) for x in stats.tolist())
+        multi_gpu_check = {"dbias_max_abs": db_e, "dq_max_abs": dq_e, "dk_dv_bit_identical": diff == 0.0,
+                           "ok": bool(db_e <= 1e-3 and dq_e <= 2.0 ** -6 and diff == 0.0),
+                           "what": "d_pair_bias of the phased backward with the overlapped all-reduce against "
+                                   "the same rows without a group followed by a blocking all-reduce (fp32, "
+                                   "<= 1e-3); dK/dV bit-identical, dQ within one bf16 step; max over ranks"}
+        for t in (Q, K, V, PB):
+            t.grad = None
+
+    # ---- N > 1: strong scaling of config 4 (S = 1024 split over the ranks) in the same run ----
+    strong = None
+    if world > 1 and not args.no_strong_cfg4 and name == "cfg2_msa_row" and args.scaling == "weak" and not args.rows:
+        strong = _strong_cfg4(world, rank, dev, pg, TKEvoAttention, barrier, max(3, min(args.steps, 20)))
 
     flops_step = wl.flops_fwd_bwd(B, S_total, N, H, D)          # whole job, all ranks
     ms_step = ms_total / args.steps
     value = flops_step / (ms_step * 1e-3) / 1e12
     e2e_value = flops_step / (ms_e2e / e2e_steps * 1e-3) / 1e12
 
-    peak, peak_src = _peaks()
+    peaks = _peaks()
     bwd_flops_launch = 10.0 * B * rows * H * N * N * D           # this rank's launch
     bwd_avg_ms = bwd_ms / max(bwd_n, 1)
     achieved = bwd_flops_launch / (bwd_avg_ms * 1e-3) / 1e12 if bwd_n else None
     roofline = {
-        "kernel": "evo_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": (achieved / peak) if achieved else None,
+        "kernel": "evo_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peaks["burst"], "unit": "TFLOP/s",
+        "frac": (achieved / peaks["burst"]) if achieved else None,
+        "frac_of_sustained_peak": (achieved / peaks["sustained"]) if achieved else None,
         "traffic": (NCU_DRAM_BYTES_PER_ROW[name] * rows) if name in NCU_DRAM_BYTES_PER_ROW else None,
         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 128 S rows "
                           "(summary under profiles/), scaled by rows: every S row is touched once",
-        "peak_source": peak_src,
+        "peak_source": peaks["source"],
         "avg_launch_ms": bwd_avg_ms, "launches_timed": bwd_n,
         "fwd_kernel": {"avg_launch_ms": fwd_ms / max(fwd_n, 1), "launches_timed": fwd_n,
                        "achieved": (4.0 * B * rows * H * N * N * D) / (fwd_ms / max(fwd_n, 1) * 1e-3) / 1e12 if fwd_n else None},
@@ -299,16 +420,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": name, "B": B, "S_total": S_total, "S_per_gpu": rows, "N": N, "H": H, "D": D,
-                       "parallelism": f"S-sharded x{world}, pair bias replicated, NCCL all-reduce of dBias",
-                       "l2": "each step streams > 126 MB (inputs larger than L2)",
-                       "pct_of_2250_dense_bf16": 100.0 * value / (2250.0 * world)},
+            "config": _config(name, B, S_total, rows, N, H, D, world),
+            "pct_of_2250_dense_bf16": 100.0 * value / (2250.0 * world),
+            "ms_per_step_median": statistics.median(per_step), "ms_per_step_min": min(per_step),
             "clocks": cs.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "bytes_are": "per rank (the value is the whole job)",
                     "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps},
             "gpu_launches": 5 * args.steps,   # forward; backward: prep, dBias, dQ/dK/dV, dQ conversion
             "roofline": roofline,
         }
+        if multi_gpu_check is not None:
+            out["multi_gpu_check"] = multi_gpu_check
+        if strong is not None:
+            out["strong_cfg4"] = strong
         if cpu is not None:
             out["cpu_baseline"] = cpu
         print(json.dumps(out), flush=True)
@@ -393,6 +518,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--cpu-rows", type=int, default=64, help="S rows per CPU pass (bounded sample)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-strong-cfg4", action="store_true",
+                    help="N > 1: skip the strong-scaling record of config 4 that the default line carries")
     ap.add_argument("--rows", type=int, default=0,
                     help="override the workload's S (small captures under a profiler)")
     args = ap.parse_args()
@@ -400,7 +527,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world)
         return
     if args.sweep_reference_shapes:
         run_reference_sweep(args)
