@@ -33,6 +33,9 @@
 
 namespace evo {
 
+// every fourth column pair takes its exp2 on the fused-multiply-add pipe (see ex2_poly2)
+constexpr int DBIAS_POLY_EVERY = 4;
+
 template <int DH, int NG>
 struct DbCfg {
     static constexpr int CW = TILE / NG;                  // kv columns per thread
@@ -282,7 +285,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
                         const float2 x2 = ffma2(u2f2(sv[cb][2 * k], sv[cb][2 * k + 1]), c1x2, bl2[ch * 8 + k]);
-                        p2[k] = make_float2(ex2(x2.x), ex2(x2.y));
+                        p2[k] = use_poly<DBIAS_POLY_EVERY>(k) ? ex2_poly2(x2) : make_float2(ex2(x2.x), ex2(x2.y));
                     }
 #pragma unroll
                     for (int k = 0; k < 8; ++k)

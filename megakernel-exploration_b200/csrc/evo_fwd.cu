@@ -46,14 +46,24 @@ namespace evo {
 #ifndef EVO_FWD_LAZY
 #define EVO_FWD_LAZY 0.0f
 #endif
-constexpr int FWD_THREADS = 384;           // 3 warpgroups: 2 softmax + (producer, mma, 2 idle warps)
-constexpr int FWD_REGS_SOFTMAX = 208;
-constexpr int FWD_REGS_OTHER = 88;
-// the CTA's register pool is the launch count (cap for 384 threads: 168) times the threads
-static_assert(FWD_REGS_SOFTMAX * 256 + FWD_REGS_OTHER * 128 <= 168 * FWD_THREADS, "register pool");
-
-template <int DH>
+// Softmax groups per CTA.  A group is four warps (thread = one q row) that own kv columns
+// g*CW .. g*CW+CW-1 (CW = 128 / NG) of every tile and run their own online softmax over them; the
+// groups' partial results are merged in the epilogue.  NG = 2 is the general form.  NG = 4 (D = 32
+// only: tensor memory holds four accumulators of 32 columns, not of 64) puts four softmax warps on
+// every scheduler, so that two of them can keep the exp2 unit saturated while the other two are in
+// the fused-multiply-add pass of their tile.
+template <int DH, int NG>
 struct FwdCfg {
+    static_assert(NG == 2 || NG == 4, "two or four softmax groups");
+    static constexpr int CW = TILE / NG;                       // kv columns per group
+    static constexpr int NSW = NG * 4;                         // softmax warps
+    static constexpr int THREADS = (NSW + 4) * 32;             // + producer, S issuer, PV issuer, one idle warp
+    // setmaxnreg budgets: the CTA's register pool is the launch count (the cap ptxas derives from
+    // the launch bound) times the threads; an increase that the pool cannot satisfy blocks for ever
+    static constexpr int REGS_LAUNCH = (65536 / THREADS) & ~7;
+    static constexpr int REGS_SOFTMAX = (NG == 2) ? 208 : 112;
+    static constexpr int REGS_OTHER = (NG == 2) ? 88 : 32;
+    static_assert(REGS_SOFTMAX * NSW * 32 + REGS_OTHER * 128 <= REGS_LAUNCH * THREADS, "register pool");
     static constexpr int STAGES = (DH == 32) ? 3 : 2;
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;          // one [128][DH] bf16 tile
     // one stage: K tile, V tile, bias tile (two [128][64] halves), raw bf16 mask row
@@ -61,19 +71,20 @@ struct FwdCfg {
     static constexpr uint32_t STAGE_STRIDE = 2 * ROWT + SQ_BYTES + 1024;
     static constexpr uint32_t OFF_Q = 0;                           // 2 buffers
     static constexpr uint32_t OFF_STAGE = OFF_Q + 2 * ROWT;
-    // O staging: one [128][DH/2] half tile per softmax group (each group stores its own columns)
+    // O staging: one [128][DH/NG] slice per softmax group (each group stores its own head-dim columns)
     static constexpr uint32_t OFF_O = OFF_STAGE + STAGES * STAGE_STRIDE;
-    static constexpr uint32_t O_HALF = ROWT / 2;
-    // exchange of the two groups' (m, l) per row: [item parity][group][128 rows]
+    static constexpr int HD = DH / NG;                             // head-dim columns a group finalises
+    static constexpr uint32_t O_SLICE = ROWT / NG;
+    // exchange of the groups' (m, l) per row: [item parity][group][128 rows]
     static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
-    static constexpr uint32_t OFF_WMASK = OFF_XCH + 2 * 2 * 128 * 8;       // 8 warps x 64 floats
-    static constexpr uint32_t OFF_BARS = OFF_WMASK + 8 * 256;
-    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 8 + 2 + 2 + 8 + 2;
+    static constexpr uint32_t OFF_WMASK = OFF_XCH + 2 * NG * 128 * 8;      // NSW warps x CW floats
+    static constexpr uint32_t OFF_BARS = OFF_WMASK + NSW * CW * 4;
+    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 4 * NG + 2 * NG + 2 * NG + 2 * NG + 2;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
-    static constexpr uint32_t TMEM_S = 0;                          // two buffers: + (tile & 1) * 128 + g * 64
+    static constexpr uint32_t TMEM_S = 0;                          // two buffers: + (tile & 1) * 128 + g * CW
     static constexpr uint32_t TMEM_PV = 256;                       // + g * DH
-    static constexpr uint32_t TMEM_P = 256 + 2 * DH;               // + g * 32: 64 bf16 per lane
+    static constexpr uint32_t TMEM_P = 256 + NG * DH;              // + g * CW/2: CW bf16 per lane
     static constexpr uint32_t TMEM_COLS = 512;
     static_assert(TMEM_P + 64 <= TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -94,16 +105,17 @@ struct FwdParams {
 
 // STRIDED: the activation tensors are views with the strides of p.lay; otherwise they are
 // contiguous and the residual's address is formed from N and H alone.  (The generic address
-// arithmetic, in the finishing group's epilogue, cost 4-10 % of the kernel when it was the only
-// version: the contiguous case keeps its own instantiation.)
-template <int DH, bool STRIDED>
-__global__ void __launch_bounds__(FWD_THREADS, 1)
+// arithmetic, in the epilogue, cost 4-10 % of the kernel when it was the only version: the
+// contiguous case keeps its own instantiation.)
+template <int DH, bool STRIDED, int NG>
+__global__ void __launch_bounds__((FwdCfg<DH, NG>::THREADS), 1)
 evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
                const __grid_constant__ CUtensorMap tm_o, const FwdParams p) {
-    using C = FwdCfg<DH>;
+    using C = FwdCfg<DH, NG>;
     using RT = RowTile<DH>;
-    constexpr int ST = C::STAGES;
+    constexpr int ST = C::STAGES, CW = C::CW, NSW = C::NSW, HD = C::HD;
+    constexpr int W_PROD = NSW, W_S = NSW + 1, W_PV = NSW + 2;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -112,14 +124,14 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* q_empty = bars + 2;            // [2]
     uint64_t* kv_full = bars + 4;            // [ST]
     uint64_t* kv_empty = kv_full + ST;       // [ST]
-    uint64_t* s_full = kv_empty + ST;        // [4]: softmax group + 2 * S buffer
-    uint64_t* s_free = s_full + 4;           // [4]
-    uint64_t* p_ready = s_free + 4;          // [2] per softmax group
-    uint64_t* pv_full = p_ready + 2;         // [2]
-    uint64_t* xch_ready = pv_full + 2;       // [item parity][group]: the group's final (m, l) of an item are written
-    uint64_t* o_read = xch_ready + 4;        // [group]: the group has read both accumulators of the finished item
-    uint64_t* g_bar = o_read + 2;            // [group]: rendezvous of the group's four warps
-    uint64_t* xu_done = g_bar + 2;           // [group]: the group has finished the exp2 pass of a tile
+    uint64_t* s_full = kv_empty + ST;        // [2 * NG]: softmax group + NG * S buffer
+    uint64_t* s_free = s_full + 2 * NG;      // [2 * NG]
+    uint64_t* p_ready = s_free + 2 * NG;     // [NG] per softmax group
+    uint64_t* pv_full = p_ready + NG;        // [NG]
+    uint64_t* xch_ready = pv_full + NG;      // [item parity][group]: the group's final (m, l) of an item are written
+    uint64_t* o_read = xch_ready + 2 * NG;   // [group]: the group has read every accumulator of the finished item
+    uint64_t* g_bar = o_read + NG;           // [group]: rendezvous of the group's four warps
+    uint64_t* xu_done = g_bar + NG;          // [2]: a half of the groups has finished the exp2 pass of a tile
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -132,19 +144,21 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tid == 0) {
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
-        for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 9); }
-        for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
-        for (int i = 0; i < 4; ++i) mbar_init(&xch_ready[i], 4);
-        for (int i = 0; i < 2; ++i) { mbar_init(&o_read[i], 4); mbar_init(&g_bar[i], 4); mbar_init(&xu_done[i], 4); }
+        for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], NSW + 1); }
+        for (int i = 0; i < 2 * NG; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); mbar_init(&xch_ready[i], 4); }
+        for (int i = 0; i < NG; ++i) {
+            mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1);
+            mbar_init(&o_read[i], 4); mbar_init(&g_bar[i], 4);
+        }
+        for (int i = 0; i < 2; ++i) mbar_init(&xu_done[i], NSW / 2);
         fence_mbar_init();
         fence_async_smem();
     }
-    if (warp == 9) {
+    if (warp == W_S) {
         tmem_alloc(tmem_slot, C::TMEM_COLS);
         tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == W_PROD && lane == 0) {
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
         prefetch_tmap(&tm_bias); prefetch_tmap(&tm_o);
     }
@@ -168,9 +182,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bs = r / p.QT;
     };
 
-    if (warp >= 8) {
-        reg_dec<FWD_REGS_OTHER>();
-        if (warp == 8) {
+    if (warp >= NSW) {
+        reg_dec<C::REGS_OTHER>();
+        if (warp == W_PROD) {
             if (lane == 0) {
                 // ------------------------------ producer ------------------------------
                 bool ok = true;
@@ -205,12 +219,12 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 for (int it = (n_items > 2 ? n_items - 2 : 0); it < n_items; ++it)
                     (void)mbar_wait(&q_full[it & 1], (it >> 1) & 1, wc, 0x13);
             }
-        } else if (warp == 9) {
+        } else if (warp == W_S) {
             // ------------------------------ S issuer ------------------------------
-            // S_w = Q K[64w:64w+64, :]^T for both softmax groups w of every tile, one tile ahead of
-            // the softmax (two S buffers).  The warp runs its loop with all lanes (uniform control
+            // S_w = Q K[CW w : CW w + CW, :]^T for every softmax group w of every tile, one tile ahead
+            // of the softmax (two S buffers).  The warp runs its loop with all lanes (uniform control
             // flow keeps the operand descriptors in uniform registers) and elects one lane to issue.
-            constexpr uint32_t IDESC_S = make_idesc_bf16(128, 64, 0, 0);
+            constexpr uint32_t IDESC_S = make_idesc_bf16(128, CW, 0, 0);
             const uint32_t aQ = smem_u32(smem + C::OFF_Q), aSt = smem_u32(smem + C::OFF_STAGE);
             bool ok = true;
             int g = 0;
@@ -218,35 +232,32 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int qb = it & 1;
                 for (int j = 0; j < NT && ok; ++j, ++g) {
                     const int st = g % ST;
-                    EVO_TL(p.status, 1, g, 0);
                     if (j == 0) ok = warp_all(mbar_wait(&q_full[qb], (it >> 1) & 1, wc, 0x20));
                     if (ok) ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x21));
-                    EVO_TL(p.status, 1, g, 1);
 #pragma unroll
-                    for (int w = 0; w < 2; ++w) {
-                        const int sb = w + 2 * (g & 1);
+                    for (int w = 0; w < NG; ++w) {
+                        const int sb = w + NG * (g & 1);
                         if (ok && g >= 2) ok = warp_all(mbar_wait(&s_free[sb], ((g >> 1) - 1) & 1, wc, 0x22));
                         if (!ok) break;
                         tc_fence_after();
                         if (elect_one()) {
-                            // K rows 64w..64w+63 of the tile: 64 rows further into the K-major tile
-                            const uint32_t kt = aSt + st * C::STAGE_STRIDE + C::ST_K + w * 64 * RT::ROW_BYTES;
+                            // K rows CW w .. of the tile: that many rows further into the K-major tile
+                            const uint32_t kt = aSt + st * C::STAGE_STRIDE + C::ST_K + w * CW * RT::ROW_BYTES;
 #pragma unroll
                             for (int kb = 0; kb < RT::KBLOCKS; ++kb)
-                                umma_ss(tmem + C::TMEM_S + (g & 1) * 128 + 64 * w, RT::kmajor(aQ + qb * C::ROWT, kb),
+                                umma_ss(tmem + C::TMEM_S + (g & 1) * 128 + CW * w, RT::kmajor(aQ + qb * C::ROWT, kb),
                                         RT::kmajor(kt, kb), IDESC_S, kb > 0);
                             umma_commit(&s_full[sb]);
-                            // Q is free once both groups' S of the item's last tile are issued
-                            if (w == 1 && j == NT - 1) umma_commit(&q_empty[qb]);
+                            // Q is free once every group's S of the item's last tile is issued
+                            if (w == NG - 1 && j == NT - 1) umma_commit(&q_empty[qb]);
                         }
                         __syncwarp();
-                        EVO_TL(p.status, 1, g, 2 + w);
                     }
                 }
             }
-        } else if (warp == 10) {
+        } else if (warp == W_PV) {
             // ------------------------------ PV issuer ------------------------------
-            // PV_w (+)= P_w V[64w:64w+64, :] with P_w read from tensor memory; the accumulator of a
+            // PV_w (+)= P_w V[CW w : CW w + CW, :] with P_w read from tensor memory; the accumulator of a
             // group stays in tensor memory for the whole item (the first tile overwrites it).
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, DH, 0, 1);
             const uint32_t aSt = smem_u32(smem + C::OFF_STAGE);
@@ -256,38 +267,41 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 for (int j = 0; j < NT && ok; ++j, ++g) {
                     const int st = g % ST;
 #pragma unroll
-                    for (int w = 0; w < 2; ++w) {
+                    for (int w = 0; w < NG; ++w) {
                         ok = warp_all(mbar_wait(&p_ready[w], g & 1, wc, 0x23));
                         if (!ok) break;
-                        EVO_TL(p.status, 2, g, 2 * w);
                         tc_fence_after();
                         if (elect_one()) {
 #pragma unroll
-                            for (int kk = 0; kk < 4; ++kk)
-                                umma_ts(tmem + C::TMEM_PV + w * DH, tmem + C::TMEM_P + w * 32 + kk * 8,
-                                        RT::mnmajor(aSt + st * C::STAGE_STRIDE + C::ST_V, 4 * w + kk), IDESC_PV,
+                            for (int kk = 0; kk < CW / 16; ++kk)
+                                umma_ts(tmem + C::TMEM_PV + w * DH, tmem + C::TMEM_P + w * (CW / 2) + kk * 8,
+                                        RT::mnmajor(aSt + st * C::STAGE_STRIDE + C::ST_V, (CW / 16) * w + kk), IDESC_PV,
                                         (kk > 0 || j > 0) ? 1u : 0u);
                             umma_commit(&pv_full[w]);
-                            if (w == 1) umma_commit(&kv_empty[st]);   // both groups' PV of the tile issued
+                            if (w == NG - 1) umma_commit(&kv_empty[st]);   // every group's PV of the tile issued
                         }
                         __syncwarp();
-                        EVO_TL(p.status, 2, g, 2 * w + 1);
                     }
                 }
             }
         }
     } else {
-        reg_inc<FWD_REGS_SOFTMAX>();
+        reg_inc<C::REGS_SOFTMAX>();
         // ------------------------------ softmax groups ------------------------------
-        const int wg = warp >> 2;            // 0 or 1: kv columns 64*wg .. 64*wg+63 of each tile
+        const int wg = warp >> 2;            // kv columns CW*wg .. CW*wg+CW-1 of each tile
         const int row = tid & 127;           // q row within the tile == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         const uint32_t aStage = smem_u32(smem + C::OFF_STAGE);
-        const uint32_t aO = smem_u32(smem + C::OFF_O);
-        const uint32_t aXch = smem_u32(smem + C::OFF_XCH);            // [2 groups][128 rows] (m, l)
-        const uint32_t aWmask = smem_u32(smem + C::OFF_WMASK + warp * 256);
+        const uint32_t aO = smem_u32(smem + C::OFF_O) + wg * C::O_SLICE;
+        const uint32_t aXch = smem_u32(smem + C::OFF_XCH);            // [parity][group][128 rows] (m, l)
+        const uint32_t aWmask = smem_u32(smem + C::OFF_WMASK) + warp * CW * 4;
         const uint32_t scratch_w = smem_u32(tmem_slot + 2);           // a word nobody reads
         const float2 c1x2 = make_float2(p.c1, p.c1), l2e2 = make_float2(LOG2E, LOG2E);
+        // where this group's columns sit in the bias tile (two [128][64] sub-tiles, 16-byte chunks)
+        constexpr int CH0_MASK = 7;
+        const uint32_t bias_sub = ((CW * wg) >> 6) * SQ_SUB_BYTES;
+        const int bias_c0 = ((CW * wg) & 63) >> 3;
+        (void)CH0_MASK;
         bool ok = true;
         int g = 0;
         uint32_t g_phase = 0;
@@ -303,61 +317,65 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         float m_used = -INFINITY, l = 0.f;
 
         // Finishes item `k` (coordinates pbs/pqt/ph).  Each group merges, normalises and stores
-        // head-dim columns wg*DH/2 .. of O, reading BOTH groups' accumulators from tensor memory
-        // (any warp can read any column of its lanes); the other group's (m, l) come through
-        // shared memory, written when that group finished the item.  Nothing here makes the two
-        // groups meet: every wait is for something the other group did a whole tile earlier.
+        // head-dim columns wg*HD .. of O, reading EVERY group's accumulator from tensor memory
+        // (any warp can read any column of its lanes); the other groups' (m, l) come through
+        // shared memory, written when those groups finished the item.  Nothing here makes the
+        // groups meet: every wait is for something another group did a whole tile earlier.
         auto epilogue = [&](int k, int pbs, int pqt, int ph, float pm, float pl) -> bool {
             EVO_TS(t_epi);
-            constexpr int HD = DH / 2;
-            if (!warp_all(mbar_wait(&xch_ready[(k & 1) * 2 + (wg ^ 1)], (k >> 1) & 1, wc, 0x35))) return false;
-            // the other group's last PV of the item (its accumulator is read below); that barrier cannot
-            // run a phase ahead: the other group's next PV waits for this group's o_read arrival
-            if (!warp_all(mbar_wait(&pv_full[wg ^ 1], ((k + 1) * NT - 1) & 1, wc, 0x37))) return false;
+            float gm[NG], gl[NG];
+#pragma unroll
+            for (int og = 0; og < NG; ++og) {
+                if (og == wg) { gm[og] = pm; gl[og] = pl; continue; }
+                if (!warp_all(mbar_wait(&xch_ready[(k & 1) * NG + og], (k >> 1) & 1, wc, 0x35))) return false;
+                // that group's last PV of the item (its accumulator is read below); the barrier cannot
+                // run a phase ahead: that group's next PV waits for this group's o_read arrival
+                if (!warp_all(mbar_wait(&pv_full[og], ((k + 1) * NT - 1) & 1, wc, 0x37))) return false;
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(gm[og]), "=f"(gl[og])
+                             : "r"(aXch + (((k & 1) * NG + og) * 128 + row) * 8));
+            }
             tc_fence_after();
-            float om, ol;
-            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(om), "=f"(ol)
-                         : "r"(aXch + (((k & 1) * 2 + (wg ^ 1)) * 128 + row) * 8));
-            const float mt = fmaxf(pm, om);
+            float mt = gm[0];
+#pragma unroll
+            for (int og = 1; og < NG; ++og) mt = fmaxf(mt, gm[og]);
             const float ms = (mt == -INFINITY) ? 0.f : mt;
-            const float f = ex2(pm - ms), fo = ex2(om - ms);
-            const float lt = pl * f + ol * fo;
+            float gf[NG], lt = 0.f;
+#pragma unroll
+            for (int og = 0; og < NG; ++og) { gf[og] = ex2(gm[og] - ms); lt += gl[og] * gf[og]; }
             const float inv = 1.f / lt;
-            const float fa = f * inv, fb = fo * inv;
-            float mine[HD], other[HD];
-            if constexpr (HD == 16) {
-                tmem_ld_f32<16>(lane_base + C::TMEM_PV + wg * DH + wg * HD, mine);
-                tmem_ld_f32<16>(lane_base + C::TMEM_PV + (wg ^ 1) * DH + wg * HD, other);
-            } else {
-                tmem_ld_f32<32>(lane_base + C::TMEM_PV + wg * DH + wg * HD, mine);
-                tmem_ld_f32<32>(lane_base + C::TMEM_PV + (wg ^ 1) * DH + wg * HD, other);
+            float outv[HD];
+#pragma unroll
+            for (int e = 0; e < HD; ++e) outv[e] = 0.f;
+#pragma unroll
+            for (int og = 0; og < NG; ++og) {
+                float part[HD];
+                tmem_ld_f32<HD>(lane_base + C::TMEM_PV + og * DH + wg * HD, part);
+                const float fs = gf[og] * inv;
+#pragma unroll
+                for (int e = 0; e < HD; ++e) outv[e] = fmaf(part[e], fs, outv[e]);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&o_read[wg]);       // this warp is done with both accumulators
-            // the previous store of this group's half tile must have finished reading it
+            if (lane == 0) mbar_arrive(&o_read[wg]);       // this warp is done with every accumulator
+            // the previous store of this group's slice must have finished reading it
             if (row == 0) tma_wait_group_read<0>();
             if (!group_sync()) return false;
             const int qrow = pqt * TILE + row;
-            const uint32_t sO = aO + wg * C::O_HALF;
 #pragma unroll
             for (int c8 = 0; c8 < HD / 8; ++c8) {
-                float outv[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) outv[e] = mine[c8 * 8 + e] * fa + other[c8 * 8 + e] * fb;
                 uint4 v;
-                v.x = pack_bf16(outv[0], outv[1]);
-                v.y = pack_bf16(outv[2], outv[3]);
-                v.z = pack_bf16(outv[4], outv[5]);
-                v.w = pack_bf16(outv[6], outv[7]);
-                sts128(sO + swz_off<RT::ROW_BYTES / 2>(row, c8), v);
+                v.x = pack_bf16(outv[c8 * 8 + 0], outv[c8 * 8 + 1]);
+                v.y = pack_bf16(outv[c8 * 8 + 2], outv[c8 * 8 + 3]);
+                v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
+                v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
+                sts128(aO + swz_off<HD * 2>(row, c8), v);
                 if (p.o_resid != nullptr && qrow < p.N) {
                     // rounding residual of O, straight to global memory
                     const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
                     uint32_t rw[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
-                        rw[e] = pack_bf16(outv[2 * e] - bf16_lo(vw[e]), outv[2 * e + 1] - bf16_hi(vw[e]));
+                        rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]), outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
                     __nv_bfloat16* dst;
                     if constexpr (STRIDED)
                         dst = p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + wg * HD + c8 * 8;
@@ -370,11 +388,13 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             fence_async_smem();
             if (!group_sync()) return false;
             if (row == 0) {
-                tma_store_4d(&tm_o, smem + C::OFF_O + wg * C::O_HALF, wg * HD, ph, pqt * TILE, pbs);
+                tma_store_4d(&tm_o, smem + C::OFF_O + wg * C::O_SLICE, wg * HD, ph, pqt * TILE, pbs);
                 tma_commit_group();
             }
-            // the other group has read this group's accumulator: the next item's first PV may overwrite it
-            if (!warp_all(mbar_wait(&o_read[wg ^ 1], k & 1, wc, 0x36))) return false;
+            // the other groups have read this group's accumulator: the next item's first PV may overwrite it
+#pragma unroll
+            for (int og = 0; og < NG; ++og)
+                if (og != wg && !warp_all(mbar_wait(&o_read[og], k & 1, wc, 0x36))) return false;
             EVO_TE(t_epi, p.status, 0x79);
             return true;
         };
@@ -391,12 +411,12 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int j = 0; j < NT && ok; ++j, ++g) {
                 const int st = g % ST;
                 const uint32_t sb = aStage + st * C::STAGE_STRIDE;
-                const int sbuf = wg + 2 * (g & 1);
-                const uint32_t tS = lane_base + C::TMEM_S + (g & 1) * 128 + 64 * wg;
-                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 0);
+                const int sbuf = wg + NG * (g & 1);
+                const uint32_t tS = lane_base + C::TMEM_S + (g & 1) * 128 + CW * wg;
+                if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 0);
                 ok = warp_all(mbar_wait(&s_full[sbuf], (g >> 1) & 1, wc, 0x31));
                 if (!ok) break;
-                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 1);
+                if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 1);
                 EVO_TS(t_tile);
                 tc_fence_after();
                 uint32_t sv[2][16];
@@ -406,34 +426,43 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ok) break;
                 {
                     // this warp's copy of the mask row slice: bf16 -> fp32 * log2e, -inf past N
-                    const uint32_t mraw = sb + C::ST_MASK + 128 * wg + 4 * lane;      // two bf16 per lane
-                    uint32_t mw;
-                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(mw) : "r"(mraw));
-                    const int c = j * TILE + 64 * wg + 2 * lane;
-                    const float m0 = (c < p.N) ? bf16_lo(mw) * LOG2E : -INFINITY;
-                    const float m1 = (c + 1 < p.N) ? bf16_hi(mw) * LOG2E : -INFINITY;
-                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aWmask + 8 * lane), "f"(m0), "f"(m1) : "memory");
+                    if constexpr (CW == 64) {
+                        const uint32_t mraw = sb + C::ST_MASK + 2 * CW * wg + 4 * lane;      // two bf16 per lane
+                        uint32_t mw;
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(mw) : "r"(mraw));
+                        const int c = j * TILE + CW * wg + 2 * lane;
+                        const float m0 = (c < p.N) ? bf16_lo(mw) * LOG2E : -INFINITY;
+                        const float m1 = (c + 1 < p.N) ? bf16_hi(mw) * LOG2E : -INFINITY;
+                        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aWmask + 8 * lane), "f"(m0), "f"(m1) : "memory");
+                    } else {
+                        const uint32_t mraw = sb + C::ST_MASK + 2 * CW * wg + 2 * lane;      // one bf16 per lane
+                        uint16_t mw;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(mw) : "r"(mraw));
+                        const int c = j * TILE + CW * wg + lane;
+                        const float m0 = (c < p.N) ? __uint_as_float(static_cast<uint32_t>(mw) << 16) * LOG2E : -INFINITY;
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(aWmask + 4 * lane), "f"(m0) : "memory");
+                    }
                     __syncwarp();
                 }
                 // x = S*c1 + (bias*log2e + mask*log2e), in chunks of 16 columns; the tensor-memory
                 // load of chunk ch+1 is in flight during the arithmetic of chunk ch
-                float2 x2[32];
+                float2 x2[CW / 2];
                 float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: ILP
                 uint32_t dep = 0;
-                const uint32_t sbias = sb + C::ST_BIAS + wg * SQ_SUB_BYTES;
+                const uint32_t sbias = sb + C::ST_BIAS + bias_sub;
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < CW / 16; ++ch) {
                     const int cb = ch & 1;
                     tmem_wait_ld();
-                    if (ch < 3) {
+                    if (ch + 1 < CW / 16) {
                         tmem_ld16(tS + 16 * (ch + 1), sv[cb ^ 1]);
                     } else {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&s_free[sbuf]);
                     }
-                    const uint4 b0 = lds128(sbias + swz_off<128>(row, 2 * ch));
-                    const uint4 b1 = lds128(sbias + swz_off<128>(row, 2 * ch + 1));
+                    const uint4 b0 = lds128(sbias + swz_off<128>(row, bias_c0 + 2 * ch));
+                    const uint4 b1 = lds128(sbias + swz_off<128>(row, bias_c0 + 2 * ch + 1));
                     dep ^= b0.x ^ b1.x;
                     const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
                     float2 mm[8];
@@ -452,7 +481,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
                 mbar_release_after_loads(&kv_empty[st], dep, scratch_w);      // bias tile and mask row are read
-                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 2);
+                if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 2);
 
                 const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
                 const float m_new = fmaxf(m_used, tmax);
@@ -464,26 +493,30 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (j == 0 || need) m_used = m_new;
                 const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
                 // The exp2 pass loads the special-function unit, the passes around it the other pipes.
-                // Left alone the two groups run in lockstep, both in the same pass at the same time.
-                // At D = 32 they take turns instead: group 0 runs the exp2 pass of tile g, then group 1
-                // runs its own, while the other group is in the fused-multiply-add pass of its next tile
-                // or in its epilogue (measured 0.468 -> 0.440 ms at B=1, S=512, N=384, H=8; one warp per
-                // scheduler cannot saturate the unit alone, so the gain is small, and at D = 64, with
-                // its longer epilogue, taking turns measured 2 % slower).  Group 0 waits for group 1's
-                // pass of the previous tile, group 1 for group 0's pass of this tile.
+                // Left alone the groups run in lockstep, all in the same pass at the same time.  At
+                // D = 32 the two halves of the groups take turns instead: the first half runs the exp2
+                // pass of tile g, then the second half runs its own, while the other half is in the
+                // fused-multiply-add pass of its next tile or in its epilogue.  The first half waits
+                // for the second half's pass of the previous tile, the second for the first's pass of
+                // this tile.  (At D = 64, with its longer epilogue, taking turns measured 2 % slower.)
+#ifdef EVO_FWD_NO_PINGPONG
+                constexpr bool PINGPONG = false;
+#else
                 constexpr bool PINGPONG = (DH == 32);
-                if (PINGPONG && (wg == 1 || g > 0)) {
-                    ok = warp_all(mbar_wait(&xu_done[wg ^ 1], (wg == 1 ? g : g - 1) & 1, wc, 0x38));
+#endif
+                const int half = wg / (NG / 2);
+                if (PINGPONG && (half == 1 || g > 0)) {
+                    ok = warp_all(mbar_wait(&xu_done[half ^ 1], (half == 1 ? g : g - 1) & 1, wc, 0x38));
                     if (!ok) break;
                 }
                 // P = exp2(x - m), packed to bf16 pairs; row sum in two packed chains
-                uint32_t pk[32];
+                uint32_t pk[CW / 2];
                 float rsum;
                 {
                     const float2 nm2 = make_float2(-m_safe, -m_safe);
                     float2 rs[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
+                    for (int c = 0; c < CW / 2; ++c) {
                         const float2 d2 = fadd2(x2[c], nm2);
                         const float2 p2 = make_float2(ex2(d2.x), ex2(d2.y));
                         rs[c & 1] = fadd2(rs[c & 1], p2);
@@ -495,15 +528,15 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // hand the unit over; the store orders the arrive behind the last exp2 of the pass
                     __syncwarp();
                     if (lane == 0) {
-                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(scratch_w), "r"(pk[31]) : "memory");
-                        mbar_arrive(&xu_done[wg]);
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(scratch_w), "r"(pk[CW / 2 - 1]) : "memory");
+                        mbar_arrive(&xu_done[half]);
                     }
                 }
 
                 // The P columns in tensor memory are free once the previous tile's PV MMA is done.
                 // On the first tile of an item that previous tile belongs to the previous item, whose
                 // epilogue runs now (its last PV has had the whole softmax above to finish).
-                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 3);
+                if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 3);
                 if (j > 0 || have_prev) {
                     ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x33));
                     if (!ok) break;
@@ -513,9 +546,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
                     if (!ok) break;
                 }
-                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 4);
+                if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 4);
                 if (__any_sync(0xffffffffu, need)) {
-                    // rare: rescale this group's accumulator (lanes that need nothing scale by 1)
+                    // rescale this group's accumulator (lanes that need nothing scale by 1)
                     const float alpha = need ? ex2(m_old - m_safe) : 1.0f;
                     const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
@@ -534,21 +567,22 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     l *= alpha;
                 }
                 l += rsum;
-                // P (bf16 pairs) into this group's 32 columns of tensor memory
-                tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
+                // P (bf16 pairs) into this group's columns of tensor memory
+                if constexpr (CW == 64) tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
+                else tmem_st16(lane_base + C::TMEM_P + wg * 16, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[wg]);
-                if ((warp & 3) == 0) EVO_TL(p.status, 5 + wg, g, 5);
+                if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 5);
                 EVO_TE(t_tile, p.status, 0x78);
             }
             if (!ok) break;
-            // publish this group's (m, l) of the item for the other group's epilogue
-            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aXch + (((it & 1) * 2 + wg) * 128 + row) * 8),
+            // publish this group's (m, l) of the item for the other groups' epilogues
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(aXch + (((it & 1) * NG + wg) * 128 + row) * 8),
                          "f"(m_used), "f"(l) : "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&xch_ready[(it & 1) * 2 + wg]);
+            if (lane == 0) mbar_arrive(&xch_ready[(it & 1) * NG + wg]);
             have_prev = true;
             pbs = bs; pqt = qt; ph = h;
             pm = m_used; pl = l;
@@ -568,14 +602,18 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     EVO_TRACE_FLUSH(p.status);
-    if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
+    if (warp == W_S) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-template <int DH>
+#ifndef EVO_FWD_NG32
+#define EVO_FWD_NG32 2
+#endif
+
+template <int DH, int NG>
 static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v,
                       const void* bias, const void* mask, void* o, void* o_resid, float* lse, float scale,
                       cudaStream_t st) {
-    using C = FwdCfg<DH>;
+    using C = FwdCfg<DH, NG>;
     const int BS = d->B * d->S;
     const int QT = (d->N + TILE - 1) / TILE;
 
@@ -585,7 +623,7 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE, lay))) return rc;
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE, lay))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
-    if ((rc = make_tmap_qkv_cols(&to, o, BS, d->N, d->H, DH, TILE, DH / 2, lay))) return rc;   // half-tile stores
+    if ((rc = make_tmap_qkv_cols(&to, o, BS, d->N, d->H, DH, TILE, C::HD, lay))) return rc;   // one slice per group
 
     FwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
@@ -603,12 +641,12 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     if ((rc = sm_count(&sms))) return rc;
     const ActLayout cl = contiguous_layout(d->N, d->H, DH);
     const bool strided = (lay.row != cl.row || lay.n != cl.n || lay.h != cl.h);
-    auto kernel = strided ? evo_fwd_kernel<DH, true> : evo_fwd_kernel<DH, false>;
+    auto kernel = strided ? evo_fwd_kernel<DH, true, NG> : evo_fwd_kernel<DH, false, NG>;
     if ((rc = set_max_smem_once(reinterpret_cast<const void*>(kernel), static_cast<int>(C::SMEM_BYTES))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
     prof_begin(0, st);
-    kernel<<<grid, FWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tb, to, p);
+    kernel<<<grid, C::THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tb, to, p);
     prof_end(0, st);
     return cuda_err(cudaGetLastError());
 }
@@ -637,6 +675,6 @@ extern "C" int evo_fwd_strided(const EvoDims* dims, const EvoStrides* strides, c
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dims->D == 32)
-        return evo::launch_fwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
-    return evo::launch_fwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
+        return evo::launch_fwd<32, EVO_FWD_NG32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
+    return evo::launch_fwd<64, 2>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
 }

@@ -132,15 +132,17 @@ int make_tmap_qkv_cols(CUtensorMap* out, const void* base, int BS, int N, int H,
                        const ActLayout& lay) {
     const uint64_t e = 2;
     const int rb = cols * 2;
-    if (rb != 32 && rb != 64 && rb != 128) return EVO_ERR_TENSOR_MAP;
+    if (rb != 16 && rb != 32 && rb != 64 && rb != 128) return EVO_ERR_TENSOR_MAP;
     TmapDim d[4] = {
         {static_cast<uint64_t>(D), 0, static_cast<uint32_t>(cols)},
         {static_cast<uint64_t>(H), static_cast<uint64_t>(lay.h) * e, 1},
         {static_cast<uint64_t>(N), static_cast<uint64_t>(lay.n) * e, static_cast<uint32_t>(rows)},
         {static_cast<uint64_t>(BS), static_cast<uint64_t>(lay.row) * e, 1},
     };
-    return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, d,
-                     rb == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : (rb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B));
+    const CUtensorMapSwizzle sw = rb == 16 ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                : (rb == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                : (rb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B));
+    return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, d, sw);
 }
 
 int layout_from_strides(const EvoDims* d, const EvoStrides* s, ActLayout* out) {

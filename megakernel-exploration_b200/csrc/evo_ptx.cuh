@@ -390,6 +390,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(addr)
+        : "memory");
+}
+// Store 16 consecutive 32-bit columns of this thread's lane.
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
 // Store 32 consecutive 32-bit columns of this thread's lane (counterpart of tmem_ld32).
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -406,11 +423,17 @@ __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// N consecutive fp32 columns (N = 16 or 32) of this thread's lane into dst[].
+// N consecutive fp32 columns (N = 8, 16 or 32) of this thread's lane into dst[].
 template <int N>
 __device__ __forceinline__ void tmem_ld_f32(uint32_t addr, float* dst) {
-    static_assert(N == 16 || N == 32, "16 or 32 columns");
-    if constexpr (N == 32) {
+    static_assert(N == 8 || N == 16 || N == 32, "8, 16 or 32 columns");
+    if constexpr (N == 8) {
+        uint32_t r[8];
+        tmem_ld8(addr, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dst[i] = __uint_as_float(r[i]);
+    } else if constexpr (N == 32) {
         uint32_t r[32];
         tmem_ld32(addr, r);
         tmem_wait_ld();
@@ -494,6 +517,36 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// 2^x for x <= 0 (any magnitude, -inf included) on the fused-multiply-add pipe instead of
+// the special-function unit, two values at a time: x = n + f with n = round(x), f in
+// [-0.5, 0.5]; 2^f by a cubic (minimax, relative error 7.5e-5, far below the bf16 rounding
+// the result goes through); 2^n by adding n to the exponent field.  Adding 1.5 * 2^23
+// rounds to the nearest integer and leaves it in the low mantissa bits.  A loop that is
+// bound by the special-function unit can hand every k-th column pair to this routine so that
+// both pipes work at the same time.  Measured at B=1, S=512, N=384, H=8, D=32: the dBias kernel,
+// whose arithmetic is little more than the exp2, gains 8 % with every fourth pair (0.218 ->
+// 0.200 ms); the forward and the dQ/dK/dV kernel, which are not bound by that unit, gain nothing
+// (every third pair) or lose (every second: 0.441 -> 0.478 ms and 0.480 -> 0.533 ms).
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 xf = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
+    const float2 n = __fadd2_rn(xf, make_float2(-12582912.0f, -12582912.0f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.0551714588f, 0.0551714588f), make_float2(0.242610862f, 0.242610862f));
+    p = __ffma2_rn(p, f, make_float2(0.693260992f, 0.693260992f));
+    p = __ffma2_rn(p, f, make_float2(0.99992809f, 0.99992809f));
+    float2 r;
+    r.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(xf.x) << 23));
+    r.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(xf.y) << 23));
+    return r;
+}
+// Column pair `c` goes to the polynomial when c % EVERY == EVERY - 1 (EVERY = 0: never).
+template <int EVERY>
+__device__ __forceinline__ constexpr bool use_poly(int c) {
+    return EVERY > 0 && (c % (EVERY > 0 ? EVERY : 1)) == EVERY - 1;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -538,10 +591,14 @@ __device__ __forceinline__ void reg_inc() {
 // bits 7.. (row >> 2, row >> 1, row for 32/64/128-byte rows).
 template <int ROW_BYTES>
 __device__ __forceinline__ uint32_t swz_off(int r, int c) {
-    static_assert(ROW_BYTES == 32 || ROW_BYTES == 64 || ROW_BYTES == 128, "swizzled row");
-    constexpr int SH = (ROW_BYTES == 128) ? 0 : (ROW_BYTES == 64 ? 1 : 2);
-    constexpr int MASK = ROW_BYTES / 16 - 1;
-    return r * ROW_BYTES + ((c ^ ((r >> SH) & MASK)) << 4);
+    static_assert(ROW_BYTES == 16 || ROW_BYTES == 32 || ROW_BYTES == 64 || ROW_BYTES == 128, "tile row");
+    if constexpr (ROW_BYTES == 16) {
+        return r * 16;                  // one chunk per row: nothing to swizzle
+    } else {
+        constexpr int SH = (ROW_BYTES == 128) ? 0 : (ROW_BYTES == 64 ? 1 : 2);
+        constexpr int MASK = ROW_BYTES / 16 - 1;
+        return r * ROW_BYTES + ((c ^ ((r >> SH) & MASK)) << 4);
+    }
 }
 
 constexpr float LOG2E = 1.4426950408889634f;
