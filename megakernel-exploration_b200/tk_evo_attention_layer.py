@@ -88,6 +88,35 @@ def _bf16c(x: torch.Tensor) -> torch.Tensor:
     return x.contiguous()
 
 
+# bf16 copies of fp32 pair-bias tensors: a model calls the layer with the same pair bias for every
+# block of a stack and, in evaluation, for every step, and the fp32 -> bf16 cast is the single largest
+# cost the reference measured around its forward (evo_h100/README.md:655-669).  An entry is served only
+# to the very tensor object it was made from (held by weak reference, so a new tensor that happens to
+# reuse the address of a freed one never matches) and only while its version counter, which every
+# in-place write bumps, is unchanged.
+_BIAS_CACHE: "dict[int, tuple]" = {}
+_BIAS_CACHE_MAX = 8
+
+
+def _bias_bf16(pair_bias: torch.Tensor, B: int, H: int, N: int) -> torch.Tensor:
+    """pair_bias (B, 1, H, N, N) as a contiguous bf16 (B, H, N, N) tensor, cast at most once per version."""
+    import weakref
+    pb = pair_bias.reshape(B, H, N, N)
+    if pb.dtype == torch.bfloat16:
+        return pb.contiguous()
+    key = id(pair_bias)
+    hit = _BIAS_CACHE.get(key)
+    if hit is not None and hit[0]() is pair_bias and hit[1] == pair_bias._version:
+        return hit[2]
+    out = pb.detach().to(torch.bfloat16).contiguous()
+    for k in [k for k, v in _BIAS_CACHE.items() if v[0]() is None]:      # entries of dead tensors
+        del _BIAS_CACHE[k]
+    if len(_BIAS_CACHE) >= _BIAS_CACHE_MAX:
+        _BIAS_CACHE.pop(next(iter(_BIAS_CACHE)))
+    _BIAS_CACHE[key] = (weakref.ref(pair_bias), pair_bias._version, out)
+    return out
+
+
 def _shared_view_strides(Q, K, V):
     """Strides (elements) if Q, K, V are bf16 views that the kernels can read in place: identical
     strides, contiguous head dim, 16-byte-aligned steps, (B, N_SEQ) flattenable, and DENSE (a
@@ -158,7 +187,7 @@ class TKEvoAttention(torch.autograd.Function):
             q = F.pad(q, (0, pad)).contiguous()
             k = F.pad(k, (0, pad)).contiguous()
             v = F.pad(v, (0, pad)).contiguous()
-        bias = _bf16c(pair_bias.reshape(B, H, N_CTX, N_CTX))
+        bias = _bias_bf16(pair_bias, B, H, N_CTX)
         mask = _bf16c(res_mask.reshape(B, N_SEQ, N_CTX))
 
         # softmax_scale is 1/sqrt(true D), not 1/sqrt(padded D) (reference layer.py:105)

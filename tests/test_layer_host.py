@@ -63,3 +63,19 @@ def test_strided_path_only_for_dense_views():
     assert L._shared_view_strides(t, t, t) is None                # contiguous: the plain path
     e = torch.zeros((B, 1, N, H, D), dtype=bf).expand(B, S, N, H, D)
     assert L._shared_view_strides(e, e, e) is None                # overlapping (stride 0)
+
+
+def test_bias_cast_is_cached_per_version():
+    """The bf16 copy of an fp32 pair bias is made once per version of the tensor: a second call with the
+    same tensor returns the same copy, an in-place write invalidates it."""
+    import tk_evo_attention_layer as L
+    B, H, N = 1, 2, 16
+    pb = torch.randn((B, 1, H, N, N))
+    a = L._bias_bf16(pb, B, H, N)
+    b = L._bias_bf16(pb, B, H, N)
+    assert a is b and a.dtype == torch.bfloat16 and a.shape == (B, H, N, N)
+    pb.add_(1.0)                                              # bumps the version counter
+    c = L._bias_bf16(pb, B, H, N)
+    assert c is not a and torch.equal(c, pb.reshape(B, H, N, N).to(torch.bfloat16))
+    h = torch.randn((B, 1, H, N, N)).to(torch.bfloat16)
+    assert L._bias_bf16(h, B, H, N).data_ptr() == h.data_ptr()   # bf16 input: no copy at all
