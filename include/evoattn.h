@@ -13,8 +13,10 @@
  *   lse                   fp32 [B][S][H][N]  natural-log log-sum-exp
  *                         (evo_h100/tk_evoattention.cu:330-334)
  *   dbias                 fp32 [B][H][N][N]        (tk_evoattention.cu:1113)
- * Supported: D in {32, 64}; N a multiple of 8 (any N >= 8, the last tile may be
- * ragged); N*H*D*S*B*2 bytes < 2^40.
+ * Supported: D in {16, 32, 64} (16 runs on the D = 32 kernels: their loads
+ * zero-fill and their stores clip the missing columns, no padded copy is made);
+ * N a multiple of 8 (any N >= 8, the last tile may be ragged);
+ * N*H*D*S*B*2 bytes < 2^40.
  */
 #ifndef EVOATTN_H_
 #define EVOATTN_H_

@@ -105,6 +105,7 @@ struct BwdCfg {
 
 struct BwdParams {
     int B, S, N, H;
+    int Dt;          // true head dim (16 runs on the D = 32 kernel: loads zero-filled, stores clipped)
     int NT;          // tiles per row: ceil(N / 128)
     int NTP;         // NT * 128
     int CPB;         // chunks per batch: ceil(S / RC)
@@ -428,6 +429,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                         if (kvrow < p.N) {
 #pragma unroll
                                             for (int c8 = 0; c8 < 4; ++c8) {
+                                                if (hf * 32 + c8 * 8 >= p.Dt) continue;
                                                 uint4 u;
                                                 u.x = pack_bf16(v[c8 * 8 + 0] * sc, v[c8 * 8 + 1] * sc);
                                                 u.y = pack_bf16(v[c8 * 8 + 2] * sc, v[c8 * 8 + 3] * sc);
@@ -584,7 +586,7 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
                                 const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
                                 const __nv_bfloat16* __restrict__ mask, uint4* __restrict__ xq,
                                 uint4* __restrict__ xk, float inv_scale, int BS, int N, int H,
-                                int NTP, ActLayout lay) {
+                                int NTP, ActLayout lay, int Dt) {
     constexpr uint32_t ONES = 0x3f803f80u;     // bf16 (1, 1)
     const size_t rows = static_cast<size_t>(BS) * N * H;
     const size_t gstride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -601,6 +603,7 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
         float s = 0.f;
 #pragma unroll
         for (int c = 0; c < DH / 8; ++c) {
+            if (c * 8 >= Dt) break;
             const uint4 a = po[c], b = pd[c];
             const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
             uint32_t rw[4] = {0u, 0u, 0u, 0u};
@@ -637,7 +640,7 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
 // fp32 accumulator [B*S][N][H][D] (contiguous) -> bf16 dQ in the activation layout, 8 elements per thread
 template <int DH>
 __global__ void cvt_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n8, int N, int H,
-                              ActLayout lay) {
+                              ActLayout lay, int Dt) {
     const size_t gstride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += gstride) {
         const float4 a = reinterpret_cast<const float4*>(src)[2 * i];
@@ -647,6 +650,7 @@ __global__ void cvt_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __re
         u.z = pack_bf16(b.x, b.y); u.w = pack_bf16(b.z, b.w);
         const size_t rowi = i / (DH / 8);                 // (bs, n, h) of this group of eight
         const int d8 = static_cast<int>(i % (DH / 8));
+        if (d8 * 8 >= Dt) continue;
         const int h = static_cast<int>(rowi % H);
         const size_t bn = rowi / H;
         const size_t off = (bn / N) * lay.row + (bn % N) * lay.n + static_cast<size_t>(h) * lay.h + d8 * 8;
@@ -666,7 +670,7 @@ static BwdWorkspace bwd_workspace(const EvoDims* d) {
     w.off_xq = 0;
     w.off_xk = up(w.off_xq + BS * d->H * NTP * 16);
     w.off_dq = up(w.off_xk + BS * NTP * 16);
-    w.total = up(w.off_dq + BS * d->N * d->H * d->D * 4);
+    w.total = up(w.off_dq + BS * d->N * d->H * (d->D < 32 ? 32 : d->D) * 4);     // fp32 dQ accumulator, kernel width
     return w;
 }
 
@@ -685,10 +689,11 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
 
     CUtensorMap tq, tk, tv, tdo, tb, tdq;
     int rc;
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    const int Dt = d->D;          // 16 on the D = 32 kernel: boxes of 32 columns over tensors of 16
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
     if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 32, 32))) return rc;
 
@@ -698,7 +703,8 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.NTP = NT * TILE;
     p.CPB = (d->S + C::RC - 1) / C::RC;
     p.total_items = d->B * p.CPB * d->H * NT;
-    p.scale = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH));
+    p.scale = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(Dt));
+    p.Dt = Dt;
     p.c1 = p.scale * LOG2E;
     p.xq = reinterpret_cast<const __nv_bfloat16*>(xq);
     p.xk = reinterpret_cast<const __nv_bfloat16*>(xk);
@@ -718,7 +724,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
         bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
             static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), xq, xk,
-            1.0f / p.scale, BS, d->N, d->H, p.NTP, lay);
+            1.0f / p.scale, BS, d->N, d->H, p.NTP, lay, Dt);
         if ((rc = cuda_err(cudaGetLastError()))) return rc;
         if ((rc = launch_dbias(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st))) return rc;
     }
@@ -736,7 +742,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     prof_end(1, st);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 
-    cvt_dq_kernel<DH><<<sms * 8, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), dq_bytes / 32, d->N, d->H, lay);
+    cvt_dq_kernel<DH><<<sms * 8, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), dq_bytes / 32, d->N, d->H, lay, Dt);
     return cuda_err(cudaGetLastError());
 }
 
@@ -836,7 +842,7 @@ extern "C" int evo_bwd_phased(const EvoDims* dims, const EvoStrides* strides, co
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    if (dims->D == 32)
+    if (dims->D <= 32)
         return evo::launch_bwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
                                    ws, scale, phases, reserved_sms, st);
     return evo::launch_bwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,

@@ -338,10 +338,10 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
 
     CUtensorMap tq, tk, tv, tdo;
     int rc;
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
 
     // Slices of S: enough items to fill the SMs evenly, each long enough that the
     // per-item set-up (bias load, pipeline fill, tile write) stays small.
@@ -363,7 +363,7 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
     p.SL = (d->S + best_z - 1) / best_z;
     p.Z = (d->S + p.SL - 1) / p.SL;
     p.total_items = static_cast<int>(base * p.Z);
-    const float sc = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH));
+    const float sc = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(d->D));
     p.c1 = sc * LOG2E;
     p.xq = static_cast<const __nv_bfloat16*>(xq);
     p.xk = static_cast<const __nv_bfloat16*>(xk);
@@ -385,7 +385,7 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
 int launch_dbias(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
                  const void* d_o, const void* xq, const void* xk, float* dbias,
                  float scale, int sms, cudaStream_t st) {
-    if (d->D == 32)
+    if (d->D <= 32)
         return launch_dbias_t<32>(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
     return launch_dbias_t<64>(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
 }

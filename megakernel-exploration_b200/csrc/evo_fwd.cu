@@ -93,6 +93,7 @@ struct FwdCfg {
 
 struct FwdParams {
     int B, S, N, H;
+    int Dt;            // true head dim (16 runs on the D = 32 kernel: loads zero-filled, stores clipped)
     int QT;            // q tiles (= kv tiles) per row: ceil(N / 128)
     int total_items;   // B*S*QT*H
     float c1;          // scale * log2(e)
@@ -369,7 +370,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
                 v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
                 sts128(aO + swz_off<HD * 2>(row, c8), v);
-                if (p.o_resid != nullptr && qrow < p.N) {
+                if (p.o_resid != nullptr && qrow < p.N && wg * HD + c8 * 8 < p.Dt) {
                     // rounding residual of O, straight to global memory
                     const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
                     uint32_t rw[4];
@@ -387,7 +388,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (wg == 0 && qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = ms * LN2 + __logf(lt);
             fence_async_smem();
             if (!group_sync()) return false;
-            if (row == 0) {
+            if (row == 0 && wg * HD < p.Dt) {
                 tma_store_4d(&tm_o, smem + C::OFF_O + wg * C::O_SLICE, wg * HD, ph, pqt * TILE, pbs);
                 tma_commit_group();
             }
@@ -619,17 +620,19 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
 
     CUtensorMap tq, tk, tv, tb, to;
     int rc;
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, DH, TILE, lay))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, DH, TILE, lay))) return rc;
+    const int Dt = d->D;          // 16 on the D = 32 kernel: boxes of 32 columns over tensors of 16
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
-    if ((rc = make_tmap_qkv_cols(&to, o, BS, d->N, d->H, DH, TILE, C::HD, lay))) return rc;   // one slice per group
+    if ((rc = make_tmap_qkv_cols(&to, o, BS, d->N, d->H, Dt, TILE, C::HD, lay))) return rc;   // one slice per group
 
     FwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
+    p.Dt = Dt;
     p.QT = QT;
     p.total_items = BS * QT * d->H;
-    p.c1 = ((scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(DH))) * LOG2E;
+    p.c1 = ((scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(Dt))) * LOG2E;
     p.mask = static_cast<const __nv_bfloat16*>(mask);
     p.lse = lse;
     p.o_resid = static_cast<__nv_bfloat16*>(o_resid);
@@ -674,7 +677,7 @@ extern "C" int evo_fwd_strided(const EvoDims* dims, const EvoStrides* strides, c
     if (all & 15u) return EVO_ERR_ALIGNMENT;
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dims->D == 32)
+    if (dims->D <= 32)
         return evo::launch_fwd<32, EVO_FWD_NG32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
     return evo::launch_fwd<64, 2>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
 }

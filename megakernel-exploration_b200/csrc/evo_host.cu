@@ -117,15 +117,16 @@ int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int ra
 }
 
 int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows,
-                  const ActLayout& lay) {
+                  const ActLayout& lay, int box_d) {
     const uint64_t e = 2;
+    if (box_d <= 0) box_d = D;
     TmapDim d[4] = {
-        {static_cast<uint64_t>(D), 0, static_cast<uint32_t>(D)},
+        {static_cast<uint64_t>(D), 0, static_cast<uint32_t>(box_d)},
         {static_cast<uint64_t>(H), static_cast<uint64_t>(lay.h) * e, 1},
         {static_cast<uint64_t>(N), static_cast<uint64_t>(lay.n) * e, static_cast<uint32_t>(rows)},
         {static_cast<uint64_t>(BS), static_cast<uint64_t>(lay.row) * e, 1},
     };
-    return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, d, row_swizzle(D));
+    return make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, d, row_swizzle(box_d));
 }
 
 int make_tmap_qkv_cols(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows, int cols,
@@ -319,7 +320,7 @@ int set_max_smem_once(const void* func, int bytes) {
 int check_dims(const EvoDims* d) {
     if (!d) return EVO_ERR_NULL_PTR;
     if (d->B <= 0 || d->S <= 0 || d->N <= 0 || d->H <= 0) return EVO_ERR_BAD_DIMS;
-    if (d->D != 32 && d->D != 64) return EVO_ERR_BAD_DIMS;
+    if (d->D != 16 && d->D != 32 && d->D != 64) return EVO_ERR_BAD_DIMS;
     if (d->N % 8 != 0) return EVO_ERR_BAD_DIMS;
     const double bytes = 2.0 * d->B * d->S * d->N * d->H * d->D;
     if (bytes >= 1099511627776.0) return EVO_ERR_BAD_DIMS;
@@ -411,7 +412,7 @@ int evo_profile_read(int kernel, float* total_ms, int* launches) {
 const char* evo_strerror(int code) {
     switch (code) {
         case EVO_OK: return "ok";
-        case EVO_ERR_BAD_DIMS: return "unsupported dimensions (need D in {32,64}, N % 8 == 0)";
+        case EVO_ERR_BAD_DIMS: return "unsupported dimensions (need D in {16,32,64}, N % 8 == 0)";
         case EVO_ERR_NULL_PTR: return "null pointer argument";
         case EVO_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
         case EVO_ERR_WORKSPACE: return "workspace too small or misaligned";

@@ -45,9 +45,10 @@ inline ActLayout contiguous_layout(int N, int H, int D) {
 int layout_from_strides(const EvoDims* d, const EvoStrides* s, ActLayout* out);
 
 // bf16 activation tensor viewed as (D, H, N, BS) with the strides of `lay`; box = one
-// head's [rows x D] tile, swizzled by row.
+// head's [rows x box_d] tile (box_d = 0: D), swizzled by box row.  A box wider than D (D = 16
+// read by the D = 32 kernels) is zero-filled past D on loads and clipped on stores.
 int make_tmap_qkv(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows,
-                  const ActLayout& lay);
+                  const ActLayout& lay, int box_d = 0);
 // The same view with a box of [rows x cols] head-dim columns (cols * 2 bytes = 32, 64 or 128), swizzled by box row.
 int make_tmap_qkv_cols(CUtensorMap* out, const void* base, int BS, int N, int H, int D, int rows, int cols,
                        const ActLayout& lay);

@@ -17,8 +17,10 @@ Backward returns (dQ, dK, dV, None, d_pair_bias) in the caller layouts
 Differences from the reference, all internal:
   * the kernels read and write the caller layout directly, so there are no
     transposes and no zero-padding of D (reference layer.py:81-102,112-113);
-  * native head dims are 32 and 64; D=16 is zero-padded to 32 here; D=96/128
-    raise ValueError (the reference pads them to 128, layer.py:47-56);
+  * head dims 16, 32 and 64 run without any padding copy (16 on the D=32 kernels,
+    whose loads zero-fill and whose stores clip the missing columns); other D <= 64
+    are zero-padded up to the next of those here; D=96/128 raise ValueError (the
+    reference pads them to 128, layer.py:47-56);
   * d_pair_bias is accumulated in fp32 and returned in the dtype of pair_bias
     (the reference rounds it to bf16 first, layer.py:176);
   * an optional sixth argument `process_group` shards the independent N_SEQ axis
@@ -68,8 +70,8 @@ def new_dbias_group(ranks=None, ctas: int = 0):
         return dist.new_group(ranks=ranks, pg_options=opts)
     return dist.new_group(ranks=ranks)
 
-# Head dims the kernels support natively; smaller ones are zero-padded up.
-TK_SUPPORTED_DIMS = (32, 64)
+# Head dims the library takes as they are; others below 64 are zero-padded up to the next one.
+TK_SUPPORTED_DIMS = (16, 32, 64)
 
 
 def _next_supported_dim(d: int) -> int:

@@ -326,3 +326,31 @@ def test_chunked_qkv_projection_views():
     got = {"o": O.detach().float().cpu(), "dq": g[..., :D], "dk": g[..., D:2 * D], "dv": g[..., 2 * D:],
            "dbias": PB.grad.float().cpu()}
     assert_parity(oracle_on_rounded(q, k, v, mask, bias, d_o), got, tag="chunked qkv")
+
+
+def test_head_dim_16_without_padding_copies():
+    """D = 16 through the C ABI directly (no padded copies anywhere: the D = 32 kernels read boxes of 32
+    columns over tensors of 16, zero-filled, and clip their stores), ragged N and a tail mask."""
+    import _evoattn
+    B, S, N, H, D = 2, 5, 200, 3, 16
+    q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "tail0to32", seed=77)
+    dev, bf = "cuda", torch.bfloat16
+    qd, kd, vd, dod = (t.to(dev, bf) for t in (q, k, v, d_o))
+    bd = bias.reshape(B, H, N, N).to(dev, bf)
+    md = mask.reshape(B, S, N).to(dev, bf)
+    dims = _evoattn.EvoDims(B, S, N, H, D)
+    st = torch.cuda.current_stream().cuda_stream
+    nan = float("nan")
+    o, ores = torch.full_like(qd, nan), torch.full_like(qd, nan)
+    lse = torch.empty((B, S, H, N), dtype=torch.float32, device=dev)
+    _evoattn.fwd(dims, qd, kd, vd, bd, md, o, ores, lse, 0.0, st)              # scale <= 0 -> 1/sqrt(16)
+    dq, dk, dv = (torch.full_like(qd, nan) for _ in range(3))
+    dbias = torch.empty((B, H, N, N), dtype=torch.float32, device=dev)
+    ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=dev)
+    _evoattn.bwd(dims, qd, kd, vd, bd, md, o, ores, lse, dod, dq, dk, dv, dbias, ws, 0.0, st)
+    _evoattn.device_status()
+    for t in (o, ores, dq, dk, dv):
+        assert torch.isfinite(t.float()).all()                                  # every element was written
+    got = {"o": o.float().cpu(), "dq": dq.float().cpu(), "dk": dk.float().cpu(), "dv": dv.float().cpu(),
+           "dbias": dbias.unsqueeze(1).cpu()}
+    assert_parity(oracle_on_rounded(q, k, v, mask, bias, d_o), got, tag="D=16")

@@ -12,8 +12,9 @@ def _inputs(B=1, S=2, N=16, H=2, D=32):
 def test_surface_names():
     import tk_evo_attention_layer as L
     assert hasattr(L, "TKEvoAttention") and issubclass(L.TKEvoAttention, torch.autograd.Function)
-    assert L.TK_SUPPORTED_DIMS == (32, 64)
-    assert L._next_supported_dim(16) == 32 and L._next_supported_dim(32) == 32
+    assert L.TK_SUPPORTED_DIMS == (16, 32, 64)
+    assert L._next_supported_dim(8) == 16 and L._next_supported_dim(16) == 16 and L._next_supported_dim(32) == 32
+    assert L._next_supported_dim(24) == 32
     assert L._next_supported_dim(33) == 64 and L._next_supported_dim(64) == 64
     with pytest.raises(ValueError):
         L._next_supported_dim(96)
