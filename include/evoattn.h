@@ -151,6 +151,31 @@ int evo_bwd_static_scratch(const EvoDims* dims, const void* q, const void* k, co
                            const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk,
                            void* dv, float* dbias, float scale, void* stream);
 
+/* Forward and backward with the sigmoid gate that follows this attention in the
+ * AlphaFold-3 / MegaFold blocks fused in: out = sigmoid(gate) * O.  The reference has
+ * no such entry point (its callers multiply in a separate elementwise pass,
+ * evo_h100/README.md:655-669 discusses the cost of the passes around the kernel);
+ * the arguments it shares with evo_fwd_strided / evo_bwd_phased mean the same.
+ *   gate     bf16, the layout of q: the gate's pre-activation logits
+ *   o        still receives the un-gated attention output: backward needs it
+ *   o_gated  bf16, the layout of q: sigmoid(gate) * O, formed from the unrounded O
+ * gate == NULL and o_gated == NULL together make this evo_fwd_strided. */
+int evo_fwd_gated(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                  const void* v, const void* pair_bias, const void* res_mask, const void* gate,
+                  void* o, void* o_gated, void* o_resid, float* lse, float scale, void* stream);
+/*   d_out    gradient of the loss with respect to o_gated (bf16, the layout of q)
+ *   d_gate   receives the gradient with respect to the gate logits (bf16, the layout of q):
+ *            d_out * O * sigmoid(gate) * (1 - sigmoid(gate))
+ * The gradient that flows into the attention, d_out * sigmoid(gate), is formed by the
+ * prep kernel into the workspace (evo_bwd_gated_workspace_bytes, larger than
+ * evo_bwd_workspace_bytes by one bf16 activation tensor). */
+size_t evo_bwd_gated_workspace_bytes(const EvoDims* dims);
+int evo_bwd_gated(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                  const void* v, const void* pair_bias, const void* res_mask, const void* gate,
+                  const void* o, const void* o_resid, const float* lse, const void* d_out, void* dq,
+                  void* dk, void* dv, void* d_gate, float* dbias, void* workspace, size_t workspace_bytes,
+                  float scale, unsigned phases, int reserved_sms, void* stream);
+
 /* Reads (and clears) the device status word that kernels set when a bounded
  * wait gives up.  Synchronises the device.  Returns EVO_OK, EVO_ERR_DEVICE_WAIT
  * (raw word in *raw if non-NULL) or EVO_ERR_CUDA.  The reference has no

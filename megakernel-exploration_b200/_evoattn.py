@@ -43,6 +43,10 @@ SYMBOLS = {
                         + [C.c_size_t, C.c_float, C.c_void_p]),
     "evo_bwd_phased": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 14
                        + [C.c_size_t, C.c_float, C.c_uint, C.c_int, C.c_void_p]),
+    "evo_fwd_gated": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 10 + [C.c_float, C.c_void_p]),
+    "evo_bwd_gated": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 16
+                      + [C.c_size_t, C.c_float, C.c_uint, C.c_int, C.c_void_p]),
+    "evo_bwd_gated_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
     "evo_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
     "evo_bwd": (C.c_int, [C.POINTER(EvoDims)] + [C.c_void_p] * 14 + [C.c_size_t, C.c_float, C.c_void_p]),
     "evo_bwd_static_scratch_capacity": (C.c_size_t, []),
@@ -131,6 +135,29 @@ def bwd_phased(dims: EvoDims, strides, q, k, v, bias, mask, o, o_resid, lse, d_o
                                _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbias), _ptr(workspace),
                                workspace.numel() * workspace.element_size(), float(scale), int(phases),
                                int(reserved_sms), stream), "evo_bwd_phased")
+
+
+def fwd_gated(dims: EvoDims, strides, q, k, v, bias, mask, gate, o, o_gated, o_resid, lse, scale: float,
+              stream: int) -> None:
+    """evo_fwd_strided with the sigmoid gate fused in: o receives the attention output, o_gated
+    sigmoid(gate) * O.  strides may be None (contiguous)."""
+    check(lib().evo_fwd_gated(C.byref(dims), C.byref(strides) if strides is not None else None,
+                              _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask), _ptr(gate), _ptr(o), _ptr(o_gated),
+                              _ptr(o_resid), _ptr(lse), float(scale), stream), "evo_fwd_gated")
+
+
+def bwd_gated_workspace_bytes(dims: EvoDims) -> int:
+    return int(lib().evo_bwd_gated_workspace_bytes(C.byref(dims)))
+
+
+def bwd_gated(dims: EvoDims, strides, q, k, v, bias, mask, gate, o, o_resid, lse, d_out, dq, dk, dv, d_gate, dbias,
+              workspace, scale: float, phases: int, reserved_sms: int, stream: int) -> None:
+    """Backward of fwd_gated: d_out is the gradient of the gated output; d_gate receives the gate's."""
+    check(lib().evo_bwd_gated(C.byref(dims), C.byref(strides) if strides is not None else None,
+                              _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask), _ptr(gate), _ptr(o), _ptr(o_resid),
+                              _ptr(lse), _ptr(d_out), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(d_gate), _ptr(dbias),
+                              _ptr(workspace), workspace.numel() * workspace.element_size(), float(scale),
+                              int(phases), int(reserved_sms), stream), "evo_bwd_gated")
 
 
 def bwd_workspace_bytes(dims: EvoDims) -> int:

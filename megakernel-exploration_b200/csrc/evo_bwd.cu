@@ -581,12 +581,17 @@ __device__ __forceinline__ uint32_t split_bf16(float v) {
     return static_cast<uint32_t>(__bfloat16_as_ushort(hi)) | (static_cast<uint32_t>(__bfloat16_as_ushort(lo)) << 16);
 }
 
+// With a gate (evo_bwd_gated) d_o is the gradient of the GATED output: the kernel then also forms
+// sig = sigmoid(gate), writes the gradient that enters the attention, bf16(d_o * sig), to do_att
+// (contiguous [B*S][N][H][Dt], what the main kernels read as their dO) and the gate's gradient
+// d_o * O * sig * (1 - sig) to d_gate, and takes delta from the rounded do_att.
 template <int DH>
 __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ o_resid,
                                 const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse,
                                 const __nv_bfloat16* __restrict__ mask, uint4* __restrict__ xq,
                                 uint4* __restrict__ xk, float inv_scale, int BS, int N, int H,
-                                int NTP, ActLayout lay, int Dt) {
+                                int NTP, ActLayout lay, int Dt, const __nv_bfloat16* __restrict__ gate,
+                                __nv_bfloat16* __restrict__ do_att, __nv_bfloat16* __restrict__ d_gate) {
     constexpr uint32_t ONES = 0x3f803f80u;     // bf16 (1, 1)
     const size_t rows = static_cast<size_t>(BS) * N * H;
     const size_t gstride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -600,17 +605,37 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
         const uint4* po = reinterpret_cast<const uint4*>(o + off);
         const uint4* pr = o_resid ? reinterpret_cast<const uint4*>(o_resid + off) : nullptr;
         const uint4* pd = reinterpret_cast<const uint4*>(d_o + off);
+        const uint4* pg = gate ? reinterpret_cast<const uint4*>(gate + off) : nullptr;
         float s = 0.f;
 #pragma unroll
         for (int c = 0; c < DH / 8; ++c) {
             if (c * 8 >= Dt) break;
-            const uint4 a = po[c], b = pd[c];
-            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+            const uint4 a = po[c];
+            uint4 b = pd[c];
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
             uint32_t rw[4] = {0u, 0u, 0u, 0u};
             if (pr) {
                 const uint4 rr = pr[c];
                 rw[0] = rr.x; rw[1] = rr.y; rw[2] = rr.z; rw[3] = rr.w;
             }
+            if (pg) {
+                const uint4 g4 = pg[c];
+                const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, dw[4] = {b.x, b.y, b.z, b.w};
+                uint32_t aw2[4], gg[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float s0 = 1.0f / (1.0f + ex2(-bf16_lo(gw[e]) * LOG2E));
+                    const float s1 = 1.0f / (1.0f + ex2(-bf16_hi(gw[e]) * LOG2E));
+                    const float d0 = bf16_lo(dw[e]), d1 = bf16_hi(dw[e]);
+                    const float o0 = bf16_lo(aw[e]) + bf16_lo(rw[e]), o1 = bf16_hi(aw[e]) + bf16_hi(rw[e]);
+                    aw2[e] = pack_bf16(d0 * s0, d1 * s1);
+                    gg[e] = pack_bf16(d0 * o0 * s0 * (1.0f - s0), d1 * o1 * s1 * (1.0f - s1));
+                }
+                b = make_uint4(aw2[0], aw2[1], aw2[2], aw2[3]);
+                reinterpret_cast<uint4*>(do_att + ((bs * N + n) * H + h) * static_cast<size_t>(Dt))[c] = b;
+                reinterpret_cast<uint4*>(d_gate + off)[c] = make_uint4(gg[0], gg[1], gg[2], gg[3]);
+            }
+            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 s = fmaf(bf16_lo(aw[e]) + bf16_lo(rw[e]), bf16_lo(bw[e]), s);
@@ -659,10 +684,10 @@ __global__ void cvt_dq_kernel(const float* __restrict__ src, __nv_bfloat16* __re
 }
 
 struct BwdWorkspace {
-    size_t off_xq, off_xk, off_dq, total;
+    size_t off_xq, off_xk, off_dq, off_do, total;
 };
 
-static BwdWorkspace bwd_workspace(const EvoDims* d) {
+static BwdWorkspace bwd_workspace(const EvoDims* d, bool gated = false) {
     const size_t BS = static_cast<size_t>(d->B) * d->S;
     const size_t NTP = static_cast<size_t>((d->N + TILE - 1) / TILE) * TILE;
     auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
@@ -670,19 +695,23 @@ static BwdWorkspace bwd_workspace(const EvoDims* d) {
     w.off_xq = 0;
     w.off_xk = up(w.off_xq + BS * d->H * NTP * 16);
     w.off_dq = up(w.off_xk + BS * NTP * 16);
-    w.total = up(w.off_dq + BS * d->N * d->H * (d->D < 32 ? 32 : d->D) * 4);     // fp32 dQ accumulator, kernel width
+    w.off_do = up(w.off_dq + BS * d->N * d->H * (d->D < 32 ? 32 : d->D) * 4);    // fp32 dQ accumulator, kernel width
+    w.total = gated ? up(w.off_do + BS * d->N * d->H * d->D * 2) : w.off_do;     // bf16 d_out * sigmoid(gate)
     return w;
 }
 
 template <int DH>
 static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
-                      const void* mask, const void* o, const void* o_resid, const float* lse, const void* d_o,
+                      const void* mask, const void* o, const void* o_resid, const float* lse, const void* d_o_in,
                       void* dq, void* dk, void* dv, float* dbias, uint8_t* ws, float scale, unsigned phases,
-                      int reserved_sms, cudaStream_t st) {
+                      int reserved_sms, cudaStream_t st, const void* gate = nullptr, void* d_gate = nullptr) {
     using C = BwdCfg<DH>;
     const int BS = d->B * d->S;
     const int NT = (d->N + TILE - 1) / TILE;
-    const BwdWorkspace w = bwd_workspace(d);
+    const BwdWorkspace w = bwd_workspace(d, gate != nullptr);
+    // with a gate the kernels read the gradient entering the attention from the workspace (contiguous)
+    const void* d_o = gate ? static_cast<const void*>(ws + w.off_do) : d_o_in;
+    const ActLayout lay_do = gate ? contiguous_layout(d->N, d->H, d->D) : lay;
     uint4* xq = reinterpret_cast<uint4*>(ws + w.off_xq);
     uint4* xk = reinterpret_cast<uint4*>(ws + w.off_xk);
     float* dq_acc = reinterpret_cast<float*>(ws + w.off_dq);
@@ -693,7 +722,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
     if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, Dt, TILE, lay_do, DH))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
     if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 32, 32))) return rc;
 
@@ -723,10 +752,11 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
         if ((rc = cuda_err(cudaMemsetAsync(dbias, 0, db_bytes, st)))) return rc;
         bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
-            static_cast<const __nv_bfloat16*>(d_o), lse, static_cast<const __nv_bfloat16*>(mask), xq, xk,
-            1.0f / p.scale, BS, d->N, d->H, p.NTP, lay, Dt);
+            static_cast<const __nv_bfloat16*>(d_o_in), lse, static_cast<const __nv_bfloat16*>(mask), xq, xk,
+            1.0f / p.scale, BS, d->N, d->H, p.NTP, lay, Dt, static_cast<const __nv_bfloat16*>(gate),
+            reinterpret_cast<__nv_bfloat16*>(ws + w.off_do), static_cast<__nv_bfloat16*>(d_gate));
         if ((rc = cuda_err(cudaGetLastError()))) return rc;
-        if ((rc = launch_dbias(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st))) return rc;
+        if ((rc = launch_dbias(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st))) return rc;
     }
     if (!(phases & EVO_BWD_PHASE_DQKV)) return EVO_OK;
 
@@ -822,6 +852,21 @@ extern "C" int evo_bwd_phased(const EvoDims* dims, const EvoStrides* strides, co
                               const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk,
                               void* dv, float* dbias, void* workspace, size_t workspace_bytes, float scale,
                               unsigned phases, int reserved_sms, void* stream) {
+    return evo_bwd_gated(dims, strides, q, k, v, pair_bias, res_mask, nullptr, o, o_resid, lse, d_o, dq, dk, dv, nullptr,
+                         dbias, workspace, workspace_bytes, scale, phases, reserved_sms, stream);
+}
+
+extern "C" size_t evo_bwd_gated_workspace_bytes(const EvoDims* dims) {
+    if (evo::check_dims(dims) != EVO_OK) return 0;
+    return evo::bwd_workspace(dims, true).total;
+}
+
+extern "C" int evo_bwd_gated(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                             const void* v, const void* pair_bias, const void* res_mask, const void* gate,
+                             const void* o, const void* o_resid, const float* lse, const void* d_o, void* dq,
+                             void* dk, void* dv, void* d_gate, float* dbias, void* workspace,
+                             size_t workspace_bytes, float scale, unsigned phases, int reserved_sms,
+                             void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
     if (!(phases & (EVO_BWD_PHASE_DBIAS | EVO_BWD_PHASE_DQKV))) return EVO_ERR_BAD_DIMS;
@@ -830,21 +875,24 @@ extern "C" int evo_bwd_phased(const EvoDims* dims, const EvoStrides* strides, co
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse || !d_o || !dq || !dk || !dv || !dbias ||
         !workspace)
         return EVO_ERR_NULL_PTR;
+    if ((gate == nullptr) != (d_gate == nullptr)) return EVO_ERR_NULL_PTR;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(pair_bias) |
                           reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o) |
                           reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
                           reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(dbias) |
-                          reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(o_resid);
+                          reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(o_resid) |
+                          reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(d_gate);
     if (all & 15u) return EVO_ERR_ALIGNMENT;
-    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < evo::bwd_workspace(dims).total)
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) ||
+        workspace_bytes < evo::bwd_workspace(dims, gate != nullptr).total)
         return EVO_ERR_WORKSPACE;
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     if (dims->D <= 32)
         return evo::launch_bwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
-                                   ws, scale, phases, reserved_sms, st);
+                                   ws, scale, phases, reserved_sms, st, gate, d_gate);
     return evo::launch_bwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
-                               scale, phases, reserved_sms, st);
+                               scale, phases, reserved_sms, st, gate, d_gate);
 }

@@ -328,7 +328,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #endif
 
 template <int DH>
-static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
+static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const ActLayout& lay_do, const void* q, const void* k, const void* v, const void* bias,
                           const void* d_o, const void* xq, const void* xk,
                           float* dbias, float scale, int sms, cudaStream_t st) {
     constexpr int NG = EVO_DBIAS_GROUPS;
@@ -341,7 +341,7 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
     if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
     if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, d->D, TILE, lay_do, DH))) return rc;
 
     // Slices of S: enough items to fill the SMs evenly, each long enough that the
     // per-item set-up (bias load, pipeline fill, tile write) stays small.
@@ -382,12 +382,12 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const void* q,
     return cuda_err(cudaGetLastError());
 }
 
-int launch_dbias(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
+int launch_dbias(const EvoDims* d, const ActLayout& lay, const ActLayout& lay_do, const void* q, const void* k, const void* v, const void* bias,
                  const void* d_o, const void* xq, const void* xk, float* dbias,
                  float scale, int sms, cudaStream_t st) {
     if (d->D <= 32)
-        return launch_dbias_t<32>(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
-    return launch_dbias_t<64>(d, lay, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
+        return launch_dbias_t<32>(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
+    return launch_dbias_t<64>(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
 }
 
 }  // namespace evo

@@ -100,6 +100,8 @@ struct FwdParams {
     const __nv_bfloat16* mask;   // [B*S][N]
     float* lse;                  // [B*S][H][N]
     __nv_bfloat16* o_resid;      // activation layout `lay`, or nullptr
+    const __nv_bfloat16* gate;   // activation layout `lay`, or nullptr: pre-activation gate logits
+    __nv_bfloat16* o_gated;      // activation layout `lay` (with gate): O * sigmoid(gate)
     ActLayout lay;               // element strides of the activation tensors
     unsigned int* status;
 };
@@ -108,7 +110,9 @@ struct FwdParams {
 // contiguous and the residual's address is formed from N and H alone.  (The generic address
 // arithmetic, in the epilogue, cost 4-10 % of the kernel when it was the only version: the
 // contiguous case keeps its own instantiation.)
-template <int DH, bool STRIDED, int NG>
+// GATED: the epilogue also writes sigmoid(gate) * O (its own instantiation: the extra loads and
+// arithmetic, even behind a uniform branch, cost the plain kernel 5 %).
+template <int DH, bool STRIDED, int NG, bool GATED>
 __global__ void __launch_bounds__((FwdCfg<DH, NG>::THREADS), 1)
 evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
@@ -324,6 +328,24 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // groups meet: every wait is for something another group did a whole tile earlier.
         auto epilogue = [&](int k, int pbs, int pqt, int ph, float pm, float pl) -> bool {
             EVO_TS(t_epi);
+            // offset of this thread's slice (row, head, first column) in the activation tensors
+            const int qrow = pqt * TILE + row;
+            size_t act_off;
+            if constexpr (STRIDED)
+                act_off = pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + wg * HD;
+            else
+                act_off = ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + wg * HD;
+            // gate logits of the slice, fetched now so that they have arrived when the merge is done
+            uint4 gv[HD / 8];
+            constexpr bool gated = GATED;
+            if constexpr (GATED) {
+#pragma unroll
+                for (int c8 = 0; c8 < HD / 8; ++c8) {
+                    gv[c8] = make_uint4(0u, 0u, 0u, 0u);
+                    if (qrow < p.N && wg * HD + c8 * 8 < p.Dt)
+                        gv[c8] = __ldg(reinterpret_cast<const uint4*>(p.gate + act_off + c8 * 8));
+                }
+            }
             float gm[NG], gl[NG];
 #pragma unroll
             for (int og = 0; og < NG; ++og) {
@@ -361,7 +383,6 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // the previous store of this group's slice must have finished reading it
             if (row == 0) tma_wait_group_read<0>();
             if (!group_sync()) return false;
-            const int qrow = pqt * TILE + row;
 #pragma unroll
             for (int c8 = 0; c8 < HD / 8; ++c8) {
                 uint4 v;
@@ -370,19 +391,28 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
                 v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
                 sts128(aO + swz_off<HD * 2>(row, c8), v);
-                if (p.o_resid != nullptr && qrow < p.N && wg * HD + c8 * 8 < p.Dt) {
-                    // rounding residual of O, straight to global memory
-                    const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-                    uint32_t rw[4];
+                if (qrow < p.N && wg * HD + c8 * 8 < p.Dt) {
+                    if (p.o_resid != nullptr) {
+                        // rounding residual of O, straight to global memory
+                        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                        uint32_t rw[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]), outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
-                    __nv_bfloat16* dst;
-                    if constexpr (STRIDED)
-                        dst = p.o_resid + pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + wg * HD + c8 * 8;
-                    else
-                        dst = p.o_resid + ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + wg * HD + c8 * 8;
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                        for (int e = 0; e < 4; ++e)
+                            rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]), outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
+                        *reinterpret_cast<uint4*>(p.o_resid + act_off + c8 * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                    }
+                    if constexpr (GATED) {
+                        // O * sigmoid(gate), from the unrounded O
+                        const uint32_t gw[4] = {gv[c8].x, gv[c8].y, gv[c8].z, gv[c8].w};
+                        uint32_t ow[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float s0 = 1.0f / (1.0f + ex2(-bf16_lo(gw[e]) * LOG2E));
+                            const float s1 = 1.0f / (1.0f + ex2(-bf16_hi(gw[e]) * LOG2E));
+                            ow[e] = pack_bf16(outv[c8 * 8 + 2 * e] * s0, outv[c8 * 8 + 2 * e + 1] * s1);
+                        }
+                        *reinterpret_cast<uint4*>(p.o_gated + act_off + c8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    }
                 }
             }
             if (wg == 0 && qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = ms * LN2 + __logf(lt);
@@ -612,8 +642,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 template <int DH, int NG>
 static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v,
-                      const void* bias, const void* mask, void* o, void* o_resid, float* lse, float scale,
-                      cudaStream_t st) {
+                      const void* bias, const void* mask, const void* gate, void* o, void* o_gated, void* o_resid,
+                      float* lse, float scale, cudaStream_t st) {
     using C = FwdCfg<DH, NG>;
     const int BS = d->B * d->S;
     const int QT = (d->N + TILE - 1) / TILE;
@@ -636,6 +666,8 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.mask = static_cast<const __nv_bfloat16*>(mask);
     p.lse = lse;
     p.o_resid = static_cast<__nv_bfloat16*>(o_resid);
+    p.gate = static_cast<const __nv_bfloat16*>(gate);
+    p.o_gated = static_cast<__nv_bfloat16*>(o_gated);
     p.lay = lay;
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
@@ -644,7 +676,8 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     if ((rc = sm_count(&sms))) return rc;
     const ActLayout cl = contiguous_layout(d->N, d->H, DH);
     const bool strided = (lay.row != cl.row || lay.n != cl.n || lay.h != cl.h);
-    auto kernel = strided ? evo_fwd_kernel<DH, true, NG> : evo_fwd_kernel<DH, false, NG>;
+    auto kernel = gate ? (strided ? evo_fwd_kernel<DH, true, NG, true> : evo_fwd_kernel<DH, false, NG, true>)
+                       : (strided ? evo_fwd_kernel<DH, true, NG, false> : evo_fwd_kernel<DH, false, NG, false>);
     if ((rc = set_max_smem_once(reinterpret_cast<const void*>(kernel), static_cast<int>(C::SMEM_BYTES))))
         return rc;
     const int grid = p.total_items < sms ? p.total_items : sms;
@@ -659,25 +692,34 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
 extern "C" int evo_fwd(const EvoDims* dims, const void* q, const void* k, const void* v,
                        const void* pair_bias, const void* res_mask, void* o, void* o_resid, float* lse,
                        float scale, void* stream) {
-    return evo_fwd_strided(dims, nullptr, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, stream);
+    return evo_fwd_gated(dims, nullptr, q, k, v, pair_bias, res_mask, nullptr, o, nullptr, o_resid, lse, scale, stream);
 }
 
 extern "C" int evo_fwd_strided(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
                                const void* v, const void* pair_bias, const void* res_mask, void* o,
                                void* o_resid, float* lse, float scale, void* stream) {
+    return evo_fwd_gated(dims, strides, q, k, v, pair_bias, res_mask, nullptr, o, nullptr, o_resid, lse, scale, stream);
+}
+
+extern "C" int evo_fwd_gated(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
+                             const void* v, const void* pair_bias, const void* res_mask, const void* gate,
+                             void* o, void* o_gated, void* o_resid, float* lse, float scale, void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
     evo::ActLayout lay;
     if ((rc = evo::layout_from_strides(dims, strides, &lay))) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse) return EVO_ERR_NULL_PTR;
+    if ((gate == nullptr) != (o_gated == nullptr)) return EVO_ERR_NULL_PTR;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(pair_bias) |
                           reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(o_resid) |
-                          reinterpret_cast<uintptr_t>(res_mask);
+                          reinterpret_cast<uintptr_t>(res_mask) | reinterpret_cast<uintptr_t>(gate) |
+                          reinterpret_cast<uintptr_t>(o_gated);
     if (all & 15u) return EVO_ERR_ALIGNMENT;
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dims->D <= 32)
-        return evo::launch_fwd<32, EVO_FWD_NG32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
-    return evo::launch_fwd<64, 2>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, scale, st);
+        return evo::launch_fwd<32, EVO_FWD_NG32>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid,
+                                                 lse, scale, st);
+    return evo::launch_fwd<64, 2>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse, scale, st);
 }

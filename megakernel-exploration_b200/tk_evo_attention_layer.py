@@ -25,7 +25,11 @@ Differences from the reference, all internal:
     (the reference rounds it to bf16 first, layer.py:176);
   * an optional sixth argument `process_group` shards the independent N_SEQ axis
     over ranks: every rank passes its own rows of Q/K/V/res_mask and the full
-    (replicated) pair_bias, and backward all-reduces d_pair_bias over the group.
+    (replicated) pair_bias, and backward all-reduces d_pair_bias over the group;
+  * an optional seventh argument `gate` (the shape of Q: the logits of the sigmoid
+    gate that follows this attention in the AlphaFold-3 / MegaFold blocks) makes the
+    call return sigmoid(gate) * O, formed in the forward kernel's epilogue, and
+    backward return the gate's gradient as well.
 
 HostStreamedEvoAttention (end of this file) is an addition without a reference
 counterpart: forward + backward for callers whose tensors live in host memory,
@@ -165,7 +169,7 @@ class TKEvoAttention(torch.autograd.Function):
     """Evo / triangle attention: softmax(Q K^T / sqrt(D) + pair_bias + res_mask) V."""
 
     @staticmethod
-    def forward(ctx, Q, K, V, res_mask, pair_bias, process_group=None):
+    def forward(ctx, Q, K, V, res_mask, pair_bias, process_group=None, gate=None):
         B, N_SEQ, N_CTX, H, D = Q.shape
         assert K.shape == (B, N_SEQ, N_CTX, H, D), f"K shape mismatch: {K.shape}"
         assert V.shape == (B, N_SEQ, N_CTX, H, D), f"V shape mismatch: {V.shape}"
@@ -177,6 +181,10 @@ class TKEvoAttention(torch.autograd.Function):
         )
         padded_D = _next_supported_dim(D)
         _check_device(Q)
+        if gate is not None:
+            assert gate.shape == (B, N_SEQ, N_CTX, H, D), f"gate shape mismatch: {gate.shape}"
+            if padded_D != D:
+                raise ValueError(f"the fused gate needs a head dim the library takes as it is {TK_SUPPORTED_DIMS}, got {D}")
         if N_CTX % 8 != 0:
             raise ValueError(f"N_CTX must be a multiple of 8, got {N_CTX}")
 
@@ -198,31 +206,53 @@ class TKEvoAttention(torch.autograd.Function):
         like = (lambda: torch.empty_strided(q.shape, strides, dtype=q.dtype, device=q.device)) \
             if strides is not None else (lambda: torch.empty_like(q))
         o = like()
+        g = o_gated = None
+        if gate is not None:
+            # the gate travels in the layout of q
+            if strides is not None and gate.dtype == torch.bfloat16 and tuple(gate.stride()) == strides \
+                    and gate.data_ptr() % 16 == 0:
+                g = gate
+            else:
+                g = like()
+                g.copy_(gate)
+            o_gated = like()
         # rounding residual of O, kept for backward only (accurate delta -> accurate dBias)
         o_resid = like() if any(ctx.needs_input_grad) else None
         lse = torch.empty((B, N_SEQ, H, N_CTX), dtype=torch.float32, device=q.device)
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
         with _device_ctx(q):
-            if strides is not None:
-                _evoattn.fwd_strided(dims, _evoattn.EvoStrides(*strides[:4]), q, k, v, bias, mask, o, o_resid,
-                                     lse, softmax_scale, _stream())
+            st_ = _evoattn.EvoStrides(*strides[:4]) if strides is not None else None
+            if g is not None:
+                _evoattn.fwd_gated(dims, st_, q, k, v, bias, mask, g, o, o_gated, o_resid, lse, softmax_scale, _stream())
+            elif strides is not None:
+                _evoattn.fwd_strided(dims, st_, q, k, v, bias, mask, o, o_resid, lse, softmax_scale, _stream())
             else:
                 _evoattn.fwd(dims, q, k, v, bias, mask, o, o_resid, lse, softmax_scale, _stream())
         ctx.strides = strides
+        ctx.gated = g is not None
 
-        ctx.save_for_backward(q, k, v, bias, mask, o, o_resid, lse)
+        if g is not None:
+            ctx.save_for_backward(q, k, v, bias, mask, o, o_resid, lse, g)
+        else:
+            ctx.save_for_backward(q, k, v, bias, mask, o, o_resid, lse)
         ctx.softmax_scale = softmax_scale
         ctx.true_D = D
         ctx.padded_D = padded_D
         ctx.dims = (B, N_SEQ, N_CTX, H)
         ctx.bias_dtype = pair_bias.dtype
         ctx.process_group = process_group
-        ctx.n_inputs = 6 if process_group is not None else 5
+        ctx.n_inputs = 7 if gate is not None else (6 if process_group is not None else 5)
+        if g is not None:
+            return o_gated
         return o[..., :D].contiguous() if padded_D != D else o
 
     @staticmethod
     def backward(ctx, dO):
-        q, k, v, bias, mask, o, o_resid, lse = ctx.saved_tensors
+        if ctx.gated:
+            q, k, v, bias, mask, o, o_resid, lse, g = ctx.saved_tensors
+        else:
+            q, k, v, bias, mask, o, o_resid, lse = ctx.saved_tensors
+            g = None
         B, N_SEQ, N_CTX, H = ctx.dims
         D, padded_D = ctx.true_D, ctx.padded_D
 
@@ -241,13 +271,28 @@ class TKEvoAttention(torch.autograd.Function):
                 d_o = F.pad(d_o, (0, padded_D - D)).contiguous()
 
         dq, dk, dv = like(), like(), like()
+        d_gate = like() if g is not None else None
         dbias = torch.empty((B, H, N_CTX, N_CTX), dtype=torch.float32, device=q.device)
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
-        ws = torch.empty(_evoattn.bwd_workspace_bytes(dims), dtype=torch.uint8, device=q.device)
+        ws_bytes = _evoattn.bwd_gated_workspace_bytes(dims) if g is not None else _evoattn.bwd_workspace_bytes(dims)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
         st_ = _evoattn.EvoStrides(*strides[:4]) if strides is not None else None
         args = (dims, st_, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws, ctx.softmax_scale)
         with _device_ctx(q):
-            if ctx.process_group is None:
+            if g is not None:
+                both = _evoattn.BWD_PHASE_DBIAS | _evoattn.BWD_PHASE_DQKV
+                gargs = (dims, st_, q, k, v, bias, mask, g, o, o_resid, lse, d_o, dq, dk, dv, d_gate, dbias, ws,
+                         ctx.softmax_scale)
+                if ctx.process_group is None:
+                    _evoattn.bwd_gated(*gargs, both, 0, _stream())
+                else:
+                    import torch.distributed as dist
+                    _evoattn.bwd_gated(*gargs, _evoattn.BWD_PHASE_DBIAS, 0, _stream())
+                    work = dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.process_group, async_op=True)
+                    reserve = ALLREDUCE_RESERVED_SMS if dist.get_world_size(ctx.process_group) >= ALLREDUCE_MIN_GROUP else 0
+                    _evoattn.bwd_gated(*gargs, _evoattn.BWD_PHASE_DQKV, reserve, _stream())
+                    work.wait()
+            elif ctx.process_group is None:
                 _evoattn.bwd_phased(*args, _evoattn.BWD_PHASE_DBIAS | _evoattn.BWD_PHASE_DQKV, 0, _stream())
             else:
                 # Rows of N_SEQ are sharded over the group and pair_bias is replicated: d_pair_bias is
@@ -267,6 +312,8 @@ class TKEvoAttention(torch.autograd.Function):
         if ctx.bias_dtype != torch.float32:
             d_pair_bias = d_pair_bias.to(ctx.bias_dtype)
         grads = (dq, dk, dv, None, d_pair_bias)
+        if ctx.n_inputs == 7:
+            return grads + (None, d_gate)
         return grads + (None,) if ctx.n_inputs == 6 else grads
 
 
@@ -277,7 +324,9 @@ class EvoAttention(torch.nn.Module):
         super().__init__()
         self.process_group = process_group
 
-    def forward(self, Q, K, V, res_mask, pair_bias):
+    def forward(self, Q, K, V, res_mask, pair_bias, gate=None):
+        if gate is not None:
+            return TKEvoAttention.apply(Q, K, V, res_mask, pair_bias, self.process_group, gate)
         if self.process_group is None:
             return TKEvoAttention.apply(Q, K, V, res_mask, pair_bias)
         return TKEvoAttention.apply(Q, K, V, res_mask, pair_bias, self.process_group)

@@ -76,8 +76,13 @@ def evo_lse_ref(q, k, res_mask, pair_bias, softmax_scale=None,
 
 def evo_attention_fwd_bwd_ref(q, k, v, res_mask, pair_bias, d_o,
                               softmax_scale=None, dtype=torch.float32,
-                              s_chunk: int = 32) -> Dict[str, torch.Tensor]:
+                              s_chunk: int = 32, gate=None) -> Dict[str, torch.Tensor]:
     """Forward + backward through autograd, chunked over S to bound memory.
+
+    With `gate` (the shape of q) the output is sigmoid(gate) * O, the gating that follows
+    this attention in the AlphaFold-3 / MegaFold blocks (the reference applies it outside
+    its kernel); d_o is then the gradient of that gated output, "o" in the result is the
+    gated output and "dgate" the gradient of the gate logits.
 
     Rows of S are independent attention problems that share only the read-only
     pair bias, so dBias is the sum of the per-chunk bias gradients
@@ -93,6 +98,7 @@ def evo_attention_fwd_bwd_ref(q, k, v, res_mask, pair_bias, d_o,
     dk = torch.empty_like(o)
     dv = torch.empty_like(o)
     dbias = torch.zeros((B, 1, H, N, N), dtype=dtype)
+    dgate = torch.empty_like(o) if gate is not None else None
     for s0 in range(0, S, s_chunk):
         s1 = min(S, s0 + s_chunk)
         qc = q[:, s0:s1].detach().to(dtype).requires_grad_(True)
@@ -100,13 +106,21 @@ def evo_attention_fwd_bwd_ref(q, k, v, res_mask, pair_bias, d_o,
         vc = v[:, s0:s1].detach().to(dtype).requires_grad_(True)
         bc = pair_bias.detach().to(dtype).requires_grad_(True)
         oc = evo_attention_ref(qc, kc, vc, res_mask[:, s0:s1], bc, softmax_scale, dtype)
+        if gate is not None:
+            gc = gate[:, s0:s1].detach().to(dtype).requires_grad_(True)
+            oc = oc * torch.sigmoid(gc)
         oc.backward(d_o[:, s0:s1].to(dtype))
+        if gate is not None:
+            dgate[:, s0:s1] = gc.grad
         o[:, s0:s1] = oc.detach()
         dq[:, s0:s1] = qc.grad
         dk[:, s0:s1] = kc.grad
         dv[:, s0:s1] = vc.grad
         dbias += bc.grad
-    return {"o": o, "dq": dq, "dk": dk, "dv": dv, "dbias": dbias}
+    out = {"o": o, "dq": dq, "dk": dk, "dv": dv, "dbias": dbias}
+    if gate is not None:
+        out["dgate"] = dgate
+    return out
 
 
 # ---------------------------------------------------------------------------

@@ -30,7 +30,7 @@ def oracle_on_rounded(q, k, v, mask, bias, d_o, s_chunk=32):
     return evo_ref.evo_attention_fwd_bwd_ref(qr, kr, vr, mr, br, dor, s_chunk=s_chunk)
 
 
-BF16_OUTPUTS = ("o", "dq", "dk", "dv")
+BF16_OUTPUTS = ("o", "dq", "dk", "dv", "dgate")
 
 
 def abs_tol(name, ref, strict=False):

@@ -354,3 +354,35 @@ def test_head_dim_16_without_padding_copies():
     got = {"o": o.float().cpu(), "dq": dq.float().cpu(), "dk": dk.float().cpu(), "dv": dv.float().cpu(),
            "dbias": dbias.unsqueeze(1).cpu()}
     assert_parity(oracle_on_rounded(q, k, v, mask, bias, d_o), got, tag="D=16")
+
+
+@pytest.mark.parametrize("case", [
+    (1, 6, 200, 2, 32, None),                   # contiguous, ragged N
+    (2, 3, 136, 3, 64, None),                   # D = 64, B = 2
+    (1, 8, 128, 2, 16, None),                   # D = 16
+    (1, 12, 200, 2, 32, (0, 2, 1, 3, 4)),       # "ending node" storage order, gate stored the same way
+])
+def test_fused_sigmoid_gate(case):
+    """out = sigmoid(gate) * attention(...), the gate applied in the forward kernel's epilogue and its
+    gradient formed by the backward's prep kernel: all six results against the oracle with the gate."""
+    from tk_evo_attention_layer import TKEvoAttention
+    import _evoattn
+    B, S, N, H, D, order = case
+    q, k, v, mask, bias, d_out = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "tail0to32", seed=41 + D)
+    gate = torch.randn((B, S, N, H, D), generator=torch.Generator().manual_seed(43))
+    dev, bf = "cuda", torch.bfloat16
+    if order is None:
+        view = lambda t: t.to(dev, bf)
+    else:
+        inv = [order.index(i) for i in range(5)]
+        view = lambda t: t.to(dev, bf).permute(*order).contiguous().permute(*inv)
+    Q, K, V, G = (view(t).requires_grad_(True) for t in (q, k, v, gate))
+    PB = bias.to(dev, torch.float32).requires_grad_(True)
+    out = TKEvoAttention.apply(Q, K, V, mask.to(dev), PB, None, G)
+    out.backward(view(d_out))
+    _evoattn.device_status()
+    rq, rk, rv, rb, rm, rdo, rg = (t.to(bf).float() for t in (q, k, v, bias, mask, d_out, gate))
+    ref = evo_ref.evo_attention_fwd_bwd_ref(rq, rk, rv, rm, rb, rdo, gate=rg)
+    got = {"o": out.detach().float().cpu(), "dq": Q.grad.float().cpu(), "dk": K.grad.float().cpu(),
+           "dv": V.grad.float().cpu(), "dbias": PB.grad.float().cpu(), "dgate": G.grad.float().cpu()}
+    assert_parity(ref, got, names=("o", "dq", "dk", "dv", "dbias", "dgate"), tag=f"gate {case}")

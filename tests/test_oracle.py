@@ -124,3 +124,18 @@ def test_workload_shapes_and_flops():
     assert abs(evo_ref.algorithmic_bytes(B, S, N, H, D) - 1.231e9) / 1.231e9 < 2e-3
     m = evo_ref.make_mask("tail10pct", 1, 2, 768, torch.Generator().manual_seed(0))
     assert int((m < 0).sum()) == 2 * 77
+
+
+def test_gate_matches_manual_product_rule():
+    """The gated form of the oracle: out = sigmoid(gate) * O; its gradients against the product rule
+    applied by hand to the un-gated oracle."""
+    B, S, N, H, D = 1, 2, 16, 2, 8
+    q, k, v, mask, bias, d_out = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "bernoulli0.9", seed=5)
+    gate = torch.randn((B, S, N, H, D), generator=torch.Generator().manual_seed(6))
+    got = evo_ref.evo_attention_fwd_bwd_ref(q, k, v, mask, bias, d_out, dtype=torch.float64, gate=gate)
+    sig = torch.sigmoid(gate.double())
+    plain = evo_ref.evo_attention_fwd_bwd_ref(q, k, v, mask, bias, d_out.double() * sig, dtype=torch.float64)
+    assert torch.allclose(got["o"], plain["o"] * sig, atol=1e-12)
+    for n in ("dq", "dk", "dv", "dbias"):
+        assert torch.allclose(got[n], plain[n], atol=1e-10), n
+    assert torch.allclose(got["dgate"], d_out.double() * plain["o"] * sig * (1 - sig), atol=1e-12)
