@@ -337,7 +337,6 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 act_off = ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + wg * HD;
             // gate logits of the slice, fetched now so that they have arrived when the merge is done
             uint4 gv[HD / 8];
-            constexpr bool gated = GATED;
             if constexpr (GATED) {
 #pragma unroll
                 for (int c8 = 0; c8 < HD / 8; ++c8) {
