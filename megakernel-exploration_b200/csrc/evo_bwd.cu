@@ -53,7 +53,6 @@ constexpr int BWD_WARP_DRAIN = 8, BWD_WARP_PRODUCER = 12, BWD_WARP_MMA = 13;   /
 constexpr uint32_t BWD_TMEM_COLS = 512;
 constexpr int BWD_REGS_COMPUTE = 176;
 constexpr int BWD_REGS_OTHER = 80;
-constexpr int BWD_DQ_BUFS = 2;             // dQ accumulators in tensor memory
 // the CTA's register pool is the launch count (cap for 512 threads: 128) times the threads;
 // a setmaxnreg increase that the pool cannot satisfy blocks for ever
 static_assert(BWD_REGS_COMPUTE * 256 + BWD_REGS_OTHER * 256 <= 128 * BWD_THREADS, "register pool");
@@ -64,9 +63,14 @@ struct BwdCfg {
 #ifndef EVO_BWD_QS32
 #define EVO_BWD_QS32 3
 #endif
-    static constexpr int QS = (DH == 32) ? EVO_BWD_QS32 : 2;     // load stages
-    // D=32: K/V travel with every step's stage; D=64: one resident K/V buffer per item
-    static constexpr bool KV_RESIDENT = (DH == 64);
+    static constexpr int QS = (DH == 32) ? EVO_BWD_QS32 : (DH == 64 ? 2 : 1);     // load stages
+    // D=32: K/V travel with every step's stage; D>=64: one resident K/V buffer per item
+    static constexpr bool KV_RESIDENT = (DH >= 64);
+    // D=128 is short of shared and tensor memory: one load stage, the bias slice of a thread read
+    // straight from global memory (no staged tile), and ONE dQ accumulator that shares its tensor
+    // memory columns with S' (S' of step n+1 is issued once dQ of step n is drained).
+    static constexpr bool BIAS_STAGED = (DH <= 64);
+    static constexpr int DQ_BUFS = (DH <= 64) ? 2 : 1;
     static constexpr int HALF = DH / 2;               // head-dim columns drained per group
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;
     // one stage: Q, dO [, K, V] tiles, then the extra tile of the q rows [and of the kv rows]
@@ -82,7 +86,7 @@ struct BwdCfg {
     static constexpr uint32_t OFF_STAGE = 0;
     static constexpr uint32_t OFF_KV = OFF_STAGE + QS * STAGE_STRIDE;
     static constexpr uint32_t OFF_BIAS = OFF_KV + KV_BYTES;
-    static constexpr uint32_t OFF_P = OFF_BIAS + SQ_BYTES;
+    static constexpr uint32_t OFF_P = OFF_BIAS + (BIAS_STAGED ? SQ_BYTES : 0);
     static constexpr uint32_t OFF_DS = OFF_P + SQ_BYTES;
     // per drain warp: dQ slot [32 rows][32 fp32]
     static constexpr uint32_t WQ_BYTES = 32 * 32 * 4;
@@ -96,8 +100,8 @@ struct BwdCfg {
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + alignment slack
     static constexpr uint32_t TMEM_S = 0;
     static constexpr uint32_t TMEM_DP = 128;
-    static constexpr uint32_t TMEM_DQ = 256;                                // two accumulators, + (step & 1)*DH
-    static constexpr uint32_t TMEM_DKV = 256 + 2 * DH;                      // + r*2*DH (dK), + DH (dV)
+    static constexpr uint32_t TMEM_DQ = (DQ_BUFS == 2) ? 256 : TMEM_S;      // DQ_BUFS accumulators, + (step % DQ_BUFS)*DH
+    static constexpr uint32_t TMEM_DKV = (DQ_BUFS == 2) ? 256 + 2 * DH : 256;   // + r*2*DH (dK), + DH (dV)
     static_assert(TMEM_DKV + RC * 2 * DH <= BWD_TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
     static_assert(OFF_KV % 1024 == 0 && OFF_BIAS % 1024 == 0 && WQ_BYTES % 1024 == 0, "tile alignment");
@@ -114,6 +118,7 @@ struct BwdParams {
     float c1;        // scale * log2(e)
     const __nv_bfloat16* xq;   // [B*S][H][NTP][8] extra tiles of the q rows  (bwd_prep_kernel)
     const __nv_bfloat16* xk;   // [B*S][NTP][8]    extra tiles of the kv rows
+    const __nv_bfloat16* bias; // [B][H][N][N] (read directly when the bias tile is not staged)
     __nv_bfloat16* dk;    // activation layout `lay`
     __nv_bfloat16* dv;
     ActLayout lay;        // element strides of the activation tensors
@@ -233,8 +238,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     uint8_t* kvb = smem + C::OFF_KV;
                     mbar_arrive_expect_tx(kv_full, x.nr * C::KV_TX);
                     for (int r = 0; r < x.nr; ++r) {
-                        tma_load_4d(kvb + r * C::ROWT, &tm_k, kv_full, 0, x.h, x.j * TILE, x.bs0 + r);
-                        tma_load_4d(kvb + (RC + r) * C::ROWT, &tm_v, kv_full, 0, x.h, x.j * TILE, x.bs0 + r);
+                        tma_load_row_tile<DH>(kvb + r * C::ROWT, &tm_k, kv_full, x.h, x.j * TILE, x.bs0 + r);
+                        tma_load_row_tile<DH>(kvb + (RC + r) * C::ROWT, &tm_v, kv_full, x.h, x.j * TILE, x.bs0 + r);
                         bulk_load(kvb + 2 * RC * C::ROWT + r * XT_BYTES,
                                   p.xk + (static_cast<size_t>(x.bs0 + r) * p.NTP + x.j * TILE) * 8, XT_BYTES, kv_full);
                     }
@@ -242,7 +247,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 for (int n = 0; n < nsteps && ok; ++n, ++gs) {
                     const int i = n / x.nr, r = n - i * x.nr;
                     const int st = gs % QS;
-                    if (r == 0) {
+                    if (C::BIAS_STAGED && r == 0) {
                         if (gb > 0) ok = mbar_wait(bias_empty, (gb - 1) & 1, wc, 0x41);
                         if (!ok) break;
                         mbar_arrive_expect_tx(bias_full, SQ_BYTES);
@@ -256,11 +261,11 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     const int bs = x.bs0 + r;
                     uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
                     mbar_arrive_expect_tx(&st_full[st], C::STAGE_TX);
-                    tma_load_4d(sb + C::ST_Q, &tm_q, &st_full[st], 0, x.h, i * TILE, bs);
-                    tma_load_4d(sb + C::ST_DO, &tm_do, &st_full[st], 0, x.h, i * TILE, bs);
+                    tma_load_row_tile<DH>(sb + C::ST_Q, &tm_q, &st_full[st], x.h, i * TILE, bs);
+                    tma_load_row_tile<DH>(sb + C::ST_DO, &tm_do, &st_full[st], x.h, i * TILE, bs);
                     if (!KVR) {
-                        tma_load_4d(sb + C::ST_K, &tm_k, &st_full[st], 0, x.h, x.j * TILE, bs);
-                        tma_load_4d(sb + C::ST_V, &tm_v, &st_full[st], 0, x.h, x.j * TILE, bs);
+                        tma_load_row_tile<DH>(sb + C::ST_K, &tm_k, &st_full[st], x.h, x.j * TILE, bs);
+                        tma_load_row_tile<DH>(sb + C::ST_V, &tm_v, &st_full[st], x.h, x.j * TILE, bs);
                         bulk_load(sb + C::ST_XK, p.xk + (static_cast<size_t>(bs) * p.NTP + x.j * TILE) * 8, XT_BYTES,
                                   &st_full[st]);
                     }
@@ -300,6 +305,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x50));
                         if (ok && KVR && n == 0) ok = warp_all(mbar_wait(kv_full, it & 1, wc, 0x51));
                         if (ok && gs > 0) ok = warp_all(mbar_wait(sdp_free, (gs - 1) & 1, wc, 0x52));
+                        // S' shares its columns with the single dQ accumulator: the previous step's dQ is drained
+                        if (ok && C::DQ_BUFS == 1 && gs > 0) ok = warp_all(mbar_wait(&dq_free[0], (gs - 1) & 1, wc, 0x56));
                         if (!ok) break;
                         tc_fence_after();
                         if (elect_one()) {
@@ -343,18 +350,18 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         __syncwarp();
                     } else if (role == 2) {
                         ok = warp_all(mbar_wait(pds_ready, gs & 1, wc, 0x53));
-                        if (ok && gs >= BWD_DQ_BUFS)
-                            ok = warp_all(mbar_wait(&dq_free[gs % BWD_DQ_BUFS], ((gs / BWD_DQ_BUFS) - 1) & 1, wc, 0x54));
+                        if (ok && gs >= C::DQ_BUFS)
+                            ok = warp_all(mbar_wait(&dq_free[gs % C::DQ_BUFS], ((gs / C::DQ_BUFS) - 1) & 1, wc, 0x54));
                         if (!ok) break;
                         tc_fence_after();
                         if (elect_one()) {
                             const uint32_t ds_k_lo = SqDesc::kmajor_lo(smem_u32(smem + C::OFF_DS));
                             const uint32_t k_lo = RD::mnmajor_lo(k_tile);
-                            const uint32_t t_dq = tmem + C::TMEM_DQ + (gs % BWD_DQ_BUFS) * DH;
+                            const uint32_t t_dq = tmem + C::TMEM_DQ + (gs % C::DQ_BUFS) * DH;
 #pragma unroll
                             for (int kk = 0; kk < 8; ++kk)
                                 umma_ss(t_dq, SqDesc::kmajor(ds_k_lo, kk), RD::mnmajor(k_lo, kk), IDESC_DQ, kk > 0);
-                            umma_commit(&dq_full[gs % BWD_DQ_BUFS]);
+                            umma_commit(&dq_full[gs % C::DQ_BUFS]);
                             umma_commit(&tail_done[gs & 1]);
                             umma_commit(&st_empty[st]);
                             if (KVR && n == nsteps - 1) umma_commit(kv_empty);
@@ -376,8 +383,8 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int nsteps = NT * x.nr;
                 int i = 0, r = 0;
                 for (int n = 0; n < nsteps && ok; ++n, ++gs) {
-                    const int b = gs % BWD_DQ_BUFS;
-                    ok = warp_all(mbar_wait(&dq_full[b], (gs / BWD_DQ_BUFS) & 1, wc, 0x68));
+                    const int b = gs % C::DQ_BUFS;
+                    ok = warp_all(mbar_wait(&dq_full[b], (gs / C::DQ_BUFS) & 1, wc, 0x68));
                     if (!ok) break;
                     tc_fence_after();
                     // dQ of this step: tensor memory -> this warp's slot -> fp32 reduce-add
@@ -473,10 +480,23 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const int nsteps = NT * x.nr;
             int r = 0;                       // row of the chunk, innermost
             for (int n = 0; n < nsteps && ok; ++n, ++gs) {
+                if (!C::BIAS_STAGED && r == 0) {
+                    // this thread's 64 bias values of q tile n / nr, straight from global memory,
+                    // requested before the wait so that they arrive while the MMAs run
+                    const int qrow = (n / x.nr) * TILE + row, col0 = x.j * TILE + 64 * wg;
+                    const __nv_bfloat16* bp = p.bias + ((static_cast<size_t>(x.b) * p.H + x.h) * p.N + qrow) * p.N + col0;
+#pragma unroll
+                    for (int c8 = 0; c8 < 8; ++c8) {
+                        uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+                        if (qrow < p.N && col0 + c8 * 8 < p.N) bv = __ldg(reinterpret_cast<const uint4*>(bp + c8 * 8));
+                        bias_pk[c8 * 4 + 0] = bv.x; bias_pk[c8 * 4 + 1] = bv.y;
+                        bias_pk[c8 * 4 + 2] = bv.z; bias_pk[c8 * 4 + 3] = bv.w;
+                    }
+                }
                 ok = warp_all(mbar_wait(sdp_full, gs & 1, wc, 0x63));
                 if (!ok) break;
                 EVO_TS(t_cmp);
-                if (r == 0) {
+                if (C::BIAS_STAGED && r == 0) {
                     ok = warp_all(mbar_wait(bias_full, gb & 1, wc, 0x64));
                     if (!ok) break;
                     uint32_t dep = 0;
@@ -695,7 +715,8 @@ static BwdWorkspace bwd_workspace(const EvoDims* d, bool gated = false) {
     w.off_xq = 0;
     w.off_xk = up(w.off_xq + BS * d->H * NTP * 16);
     w.off_dq = up(w.off_xk + BS * NTP * 16);
-    w.off_do = up(w.off_dq + BS * d->N * d->H * (d->D < 32 ? 32 : d->D) * 4);    // fp32 dQ accumulator, kernel width
+    const size_t dh = d->D <= 32 ? 32 : (d->D <= 64 ? 64 : 128);
+    w.off_do = up(w.off_dq + BS * d->N * d->H * dh * 4);                         // fp32 dQ accumulator, kernel width
     w.total = gated ? up(w.off_do + BS * d->N * d->H * d->D * 2) : w.off_do;     // bf16 d_out * sigmoid(gate)
     return w;
 }
@@ -719,10 +740,10 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     CUtensorMap tq, tk, tv, tdo, tb, tdq;
     int rc;
     const int Dt = d->D;          // 16 on the D = 32 kernel: boxes of 32 columns over tensors of 16
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, Dt, TILE, lay_do, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, Dt, TILE, lay_do, RowTile<DH>::BOX_D))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
     if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 32, 32))) return rc;
 
@@ -737,6 +758,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.c1 = p.scale * LOG2E;
     p.xq = reinterpret_cast<const __nv_bfloat16*>(xq);
     p.xk = reinterpret_cast<const __nv_bfloat16*>(xk);
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
     p.lay = lay;
     p.status = status_word();
@@ -893,6 +915,9 @@ extern "C" int evo_bwd_gated(const EvoDims* dims, const EvoStrides* strides, con
     if (dims->D <= 32)
         return evo::launch_bwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
                                    ws, scale, phases, reserved_sms, st, gate, d_gate);
-    return evo::launch_bwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
-                               scale, phases, reserved_sms, st, gate, d_gate);
+    if (dims->D <= 64)
+        return evo::launch_bwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+                                   ws, scale, phases, reserved_sms, st, gate, d_gate);
+    return evo::launch_bwd<128>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
+                                scale, phases, reserved_sms, st, gate, d_gate);
 }

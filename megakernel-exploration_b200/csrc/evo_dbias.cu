@@ -48,12 +48,17 @@ struct DbCfg {
     static constexpr int REGS_COMPUTE = (NG == 2) ? 224 : 112;
     static constexpr int REGS_OTHER = (NG == 2) ? 56 : 32;
     static_assert(REGS_COMPUTE * NCW * 32 + REGS_OTHER * 128 <= REGS_LAUNCH * THREADS, "register pool");
+    // D <= 64: a stage holds the four operand tiles of a step.  D = 128 (four tiles are 128 KB):
+    // a stage holds ONE operand pair, (Q, K) of a step or (dO, V) of a step, alternately; each of
+    // the two issuer warps waits for and releases its own pair.
+    static constexpr int SPLIT = (DH == 128) ? 2 : 1;     // stages per step
     static constexpr int QS = (DH == 32) ? 6 : 3;         // load stages
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;
-    static constexpr uint32_t ST_Q = 0, ST_DO = ROWT, ST_K = 2 * ROWT, ST_V = 3 * ROWT;
-    static constexpr uint32_t ST_XQ = 4 * ROWT, ST_XK = ST_XQ + XT_BYTES;     // extra tiles of the step
-    static constexpr uint32_t STAGE_TX = 4 * ROWT + 2 * XT_BYTES;
-    static constexpr uint32_t STAGE_STRIDE = 4 * ROWT + 2 * XT_BYTES;
+    static constexpr uint32_t ST_Q = 0, ST_DO = (SPLIT == 2) ? 0 : ROWT;
+    static constexpr uint32_t ST_K = (SPLIT == 2) ? ROWT : 2 * ROWT, ST_V = (SPLIT == 2) ? ROWT : 3 * ROWT;
+    static constexpr uint32_t ST_XQ = (4 / SPLIT) * ROWT, ST_XK = ST_XQ + XT_BYTES;     // extra tiles of the step
+    static constexpr uint32_t STAGE_TX = 4 * ROWT + 2 * XT_BYTES;            // SPLIT == 1
+    static constexpr uint32_t STAGE_STRIDE = (4 / SPLIT) * ROWT + 2 * XT_BYTES;
     // constant extra tiles, above every stage (the zero tile must sit above the tiles that refer to it)
     static constexpr uint32_t OFF_XDP = QS * STAGE_STRIDE;                    // column selector of -delta
     static constexpr uint32_t OFF_ZERO = OFF_XDP + XT_BYTES;
@@ -111,7 +116,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 2); }
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 2 / C::SPLIT); }
         for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 2); mbar_init(&sdp_free[i], NCW); }
         fence_mbar_init();
         fence_async_smem();
@@ -164,24 +169,35 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 for (int it = 0; it < n_items && ok; ++it) {
                     const DbItem x = decode(it);
                     for (int n = 0; n < x.ns && ok; ++n, ++gs) {
-                        const int st = gs % QS;
-                        if (gs >= QS) ok = mbar_wait(&st_empty[st], ((gs / QS) - 1) & 1, wc, 0x82);
-                        if (!ok) break;
                         const int bs = x.b * p.S + x.s0 + n;
-                        uint8_t* sb = smem + st * C::STAGE_STRIDE;
-                        mbar_arrive_expect_tx(&st_full[st], C::STAGE_TX);
-                        tma_load_4d(sb + C::ST_Q, &tm_q, &st_full[st], 0, x.h, x.i * TILE, bs);
-                        tma_load_4d(sb + C::ST_K, &tm_k, &st_full[st], 0, x.h, x.j * TILE, bs);
-                        tma_load_4d(sb + C::ST_DO, &tm_do, &st_full[st], 0, x.h, x.i * TILE, bs);
-                        tma_load_4d(sb + C::ST_V, &tm_v, &st_full[st], 0, x.h, x.j * TILE, bs);
                         const size_t ro = (static_cast<size_t>(bs) * p.H + x.h) * p.NTP + x.i * TILE;
-                        bulk_load(sb + C::ST_XQ, p.xq + ro * 8, XT_BYTES, &st_full[st]);
-                        bulk_load(sb + C::ST_XK, p.xk + (static_cast<size_t>(bs) * p.NTP + x.j * TILE) * 8, XT_BYTES,
-                                  &st_full[st]);
+#pragma unroll
+                        for (int hf = 0; hf < C::SPLIT; ++hf) {
+                            const int ld = gs * C::SPLIT + hf;        // running load counter
+                            const int st = ld % QS;
+                            if (ld >= QS) ok = mbar_wait(&st_empty[st], ((ld / QS) - 1) & 1, wc, 0x82);
+                            if (!ok) break;
+                            uint8_t* sb = smem + st * C::STAGE_STRIDE;
+                            const bool with_s = (C::SPLIT == 1 || hf == 0), with_dp = (C::SPLIT == 1 || hf == 1);
+                            mbar_arrive_expect_tx(&st_full[st], C::SPLIT == 1 ? C::STAGE_TX
+                                                                             : 2 * C::ROWT + (hf == 0 ? 2 : 1) * XT_BYTES);
+                            if (with_s) {
+                                tma_load_row_tile<DH>(sb + C::ST_Q, &tm_q, &st_full[st], x.h, x.i * TILE, bs);
+                                tma_load_row_tile<DH>(sb + C::ST_K, &tm_k, &st_full[st], x.h, x.j * TILE, bs);
+                                bulk_load(sb + C::ST_XK, p.xk + (static_cast<size_t>(bs) * p.NTP + x.j * TILE) * 8,
+                                          XT_BYTES, &st_full[st]);
+                            }
+                            if (with_dp) {
+                                tma_load_row_tile<DH>(sb + C::ST_DO, &tm_do, &st_full[st], x.h, x.i * TILE, bs);
+                                tma_load_row_tile<DH>(sb + C::ST_V, &tm_v, &st_full[st], x.h, x.j * TILE, bs);
+                            }
+                            bulk_load(sb + C::ST_XQ, p.xq + ro * 8, XT_BYTES, &st_full[st]);
+                        }
                     }
                 }
                 // the most recent loads have landed before the CTA exits
-                for (int k = (gs > QS ? gs - QS : 0); k < gs; ++k)
+                const int loads = gs * C::SPLIT;
+                for (int k = (loads > QS ? loads - QS : 0); k < loads; ++k)
                     (void)mbar_wait(&st_full[k % QS], (k / QS) & 1, wc, 0x83);
             }
         } else if (warp == NCW + 1 || warp == NCW + 2) {
@@ -199,8 +215,9 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             for (int it = 0; it < n_items && ok; ++it) {
                 const DbItem x = decode(it);
                 for (int n = 0; n < x.ns && ok; ++n, ++gs) {
-                    const int st = gs % QS, buf = gs & 1;
-                    ok = warp_all(mbar_wait(&st_full[st], (gs / QS) & 1, wc, 0x90));
+                    const int ld = gs * C::SPLIT + ((C::SPLIT == 2 && is_dp) ? 1 : 0);
+                    const int st = ld % QS, buf = gs & 1;
+                    ok = warp_all(mbar_wait(&st_full[st], (ld / QS) & 1, wc, 0x90));
                     if (ok && gs >= 2) ok = warp_all(mbar_wait(&sdp_free[buf], ((gs >> 1) - 1) & 1, wc, 0x91));
                     if (!ok) break;
                     tc_fence_after();
@@ -338,10 +355,10 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const ActLayou
 
     CUtensorMap tq, tk, tv, tdo;
     int rc;
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, d->D, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, d->D, TILE, lay_do, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, d->D, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, d->D, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, d->D, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, d->D, TILE, lay_do, RowTile<DH>::BOX_D))) return rc;
 
     // Slices of S: enough items to fill the SMs evenly, each long enough that the
     // per-item set-up (bias load, pipeline fill, tile write) stays small.
@@ -387,7 +404,9 @@ int launch_dbias(const EvoDims* d, const ActLayout& lay, const ActLayout& lay_do
                  float scale, int sms, cudaStream_t st) {
     if (d->D <= 32)
         return launch_dbias_t<32>(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
-    return launch_dbias_t<64>(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
+    if (d->D <= 64)
+        return launch_dbias_t<64>(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
+    return launch_dbias_t<128>(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st);
 }
 
 }  // namespace evo

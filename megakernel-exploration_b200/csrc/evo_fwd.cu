@@ -66,11 +66,17 @@ struct FwdCfg {
     static_assert(REGS_SOFTMAX * NSW * 32 + REGS_OTHER * 128 <= REGS_LAUNCH * THREADS, "register pool");
     static constexpr int STAGES = (DH == 32) ? 3 : 2;
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;          // one [128][DH] bf16 tile
+    // D = 128 is short of shared and tensor memory: one Q buffer instead of two, the bias slice of
+    // a thread read straight from global memory instead of a staged tile, and P (bf16) written
+    // over the S columns it was computed from (S of tile j+2 then waits for PV of tile j).
+    static constexpr bool WIDE = (DH == 128);
+    static constexpr int NQ = WIDE ? 1 : 2;                        // Q buffers
+    static constexpr uint32_t BIAS_BYTES = WIDE ? 0 : SQ_BYTES;
     // one stage: K tile, V tile, bias tile (two [128][64] halves), raw bf16 mask row
-    static constexpr uint32_t ST_K = 0, ST_V = ROWT, ST_BIAS = 2 * ROWT, ST_MASK = 2 * ROWT + SQ_BYTES;
-    static constexpr uint32_t STAGE_STRIDE = 2 * ROWT + SQ_BYTES + 1024;
-    static constexpr uint32_t OFF_Q = 0;                           // 2 buffers
-    static constexpr uint32_t OFF_STAGE = OFF_Q + 2 * ROWT;
+    static constexpr uint32_t ST_K = 0, ST_V = ROWT, ST_BIAS = 2 * ROWT, ST_MASK = 2 * ROWT + BIAS_BYTES;
+    static constexpr uint32_t STAGE_STRIDE = 2 * ROWT + BIAS_BYTES + 1024;
+    static constexpr uint32_t OFF_Q = 0;                           // NQ buffers
+    static constexpr uint32_t OFF_STAGE = OFF_Q + NQ * ROWT;
     // O staging: one [128][DH/NG] slice per softmax group (each group stores its own head-dim columns)
     static constexpr uint32_t OFF_O = OFF_STAGE + STAGES * STAGE_STRIDE;
     static constexpr int HD = DH / NG;                             // head-dim columns a group finalises
@@ -84,9 +90,13 @@ struct FwdCfg {
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
     static constexpr uint32_t TMEM_S = 0;                          // two buffers: + (tile & 1) * 128 + g * CW
     static constexpr uint32_t TMEM_PV = 256;                       // + g * DH
-    static constexpr uint32_t TMEM_P = 256 + NG * DH;              // + g * CW/2: CW bf16 per lane
+    static constexpr uint32_t TMEM_P = 256 + NG * DH;              // + g * CW/2: CW bf16 per lane (not WIDE)
     static constexpr uint32_t TMEM_COLS = 512;
-    static_assert(TMEM_P + 64 <= TMEM_COLS, "tensor memory budget");
+    static_assert(WIDE ? (TMEM_PV + NG * DH <= TMEM_COLS) : (TMEM_P + 64 <= TMEM_COLS), "tensor memory budget");
+    // tensor-memory column (without the lane part) of group w's P of running tile g
+    __device__ static __forceinline__ uint32_t p_col(int w, int g) {
+        return WIDE ? TMEM_S + (g & 1) * 128 + CW * w : TMEM_P + w * (CW / 2);
+    }
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
     static_assert(OFF_STAGE % 1024 == 0 && STAGE_STRIDE % 1024 == 0 && OFF_O % 1024 == 0, "tile alignment");
 };
@@ -98,6 +108,7 @@ struct FwdParams {
     int total_items;   // B*S*QT*H
     float c1;          // scale * log2(e)
     const __nv_bfloat16* mask;   // [B*S][N]
+    const __nv_bfloat16* bias;   // [B][H][N][N] (read directly when the bias tile is not staged)
     float* lse;                  // [B*S][H][N]
     __nv_bfloat16* o_resid;      // activation layout `lay`, or nullptr
     const __nv_bfloat16* gate;   // activation layout `lay`, or nullptr: pre-activation gate logits
@@ -150,7 +161,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
         for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], NSW + 1); }
-        for (int i = 0; i < 2 * NG; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); mbar_init(&xch_ready[i], 4); }
+        for (int i = 0; i < 2 * NG; ++i) {
+            mbar_init(&s_full[i], 1); mbar_init(&s_free[i], C::WIDE ? 1 : 4); mbar_init(&xch_ready[i], 4);
+        }
         for (int i = 0; i < NG; ++i) {
             mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1);
             mbar_init(&o_read[i], 4); mbar_init(&g_bar[i], 4);
@@ -198,22 +211,24 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     int bs, qt, h;
                     decode(it, bs, qt, h);
                     const int b = bs / p.S;
-                    const int qb = it & 1;
-                    if (it >= 2) ok = mbar_wait(&q_empty[qb], ((it >> 1) - 1) & 1, wc, 0x10);
+                    const int qb = it % C::NQ;
+                    if (it >= C::NQ) ok = mbar_wait(&q_empty[qb], ((it / C::NQ) - 1) & 1, wc, 0x10);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&q_full[qb], C::ROWT);
-                    tma_load_4d(smem + C::OFF_Q + qb * C::ROWT, &tm_q, &q_full[qb], 0, h, qt * TILE, bs);
+                    tma_load_row_tile<DH>(smem + C::OFF_Q + qb * C::ROWT, &tm_q, &q_full[qb], h, qt * TILE, bs);
                     for (int j = 0; j < NT; ++j, ++g) {
                         const int st = g % ST;
                         if (g >= ST) ok = mbar_wait(&kv_empty[st], ((g / ST) - 1) & 1, wc, 0x11);
                         if (!ok) break;
                         uint8_t* sb = smem + C::OFF_STAGE + st * C::STAGE_STRIDE;
                         const int ncol = (p.N - j * TILE < TILE) ? (p.N - j * TILE) : TILE;   // multiple of 8
-                        mbar_arrive_expect_tx(&kv_full[st], 2 * C::ROWT + SQ_BYTES + ncol * 2);
-                        tma_load_4d(sb + C::ST_K, &tm_k, &kv_full[st], 0, h, j * TILE, bs);
-                        tma_load_4d(sb + C::ST_V, &tm_v, &kv_full[st], 0, h, j * TILE, bs);
-                        tma_load_4d(sb + C::ST_BIAS, &tm_bias, &kv_full[st], j * TILE, qt * TILE, h, b);
-                        tma_load_4d(sb + C::ST_BIAS + SQ_SUB_BYTES, &tm_bias, &kv_full[st], j * TILE + 64, qt * TILE, h, b);
+                        mbar_arrive_expect_tx(&kv_full[st], 2 * C::ROWT + C::BIAS_BYTES + ncol * 2);
+                        tma_load_row_tile<DH>(sb + C::ST_K, &tm_k, &kv_full[st], h, j * TILE, bs);
+                        tma_load_row_tile<DH>(sb + C::ST_V, &tm_v, &kv_full[st], h, j * TILE, bs);
+                        if (!C::WIDE) {
+                            tma_load_4d(sb + C::ST_BIAS, &tm_bias, &kv_full[st], j * TILE, qt * TILE, h, b);
+                            tma_load_4d(sb + C::ST_BIAS + SQ_SUB_BYTES, &tm_bias, &kv_full[st], j * TILE + 64, qt * TILE, h, b);
+                        }
                         bulk_load(sb + C::ST_MASK, p.mask + static_cast<size_t>(bs) * p.N + j * TILE, ncol * 2, &kv_full[st]);
                     }
                 }
@@ -221,8 +236,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int issued = g;
                 for (int k = (issued > ST ? issued - ST : 0); k < issued; ++k)
                     (void)mbar_wait(&kv_full[k % ST], (k / ST) & 1, wc, 0x12);
-                for (int it = (n_items > 2 ? n_items - 2 : 0); it < n_items; ++it)
-                    (void)mbar_wait(&q_full[it & 1], (it >> 1) & 1, wc, 0x13);
+                for (int it = (n_items > C::NQ ? n_items - C::NQ : 0); it < n_items; ++it)
+                    (void)mbar_wait(&q_full[it % C::NQ], (it / C::NQ) & 1, wc, 0x13);
             }
         } else if (warp == W_S) {
             // ------------------------------ S issuer ------------------------------
@@ -234,10 +249,10 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = true;
             int g = 0;
             for (int it = 0; it < n_items && ok; ++it) {
-                const int qb = it & 1;
+                const int qb = it % C::NQ;
                 for (int j = 0; j < NT && ok; ++j, ++g) {
                     const int st = g % ST;
-                    if (j == 0) ok = warp_all(mbar_wait(&q_full[qb], (it >> 1) & 1, wc, 0x20));
+                    if (j == 0) ok = warp_all(mbar_wait(&q_full[qb], (it / C::NQ) & 1, wc, 0x20));
                     if (ok) ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x21));
 #pragma unroll
                     for (int w = 0; w < NG; ++w) {
@@ -279,10 +294,11 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         if (elect_one()) {
 #pragma unroll
                             for (int kk = 0; kk < CW / 16; ++kk)
-                                umma_ts(tmem + C::TMEM_PV + w * DH, tmem + C::TMEM_P + w * (CW / 2) + kk * 8,
+                                umma_ts(tmem + C::TMEM_PV + w * DH, tmem + C::p_col(w, g) + kk * 8,
                                         RT::mnmajor(aSt + st * C::STAGE_STRIDE + C::ST_V, (CW / 16) * w + kk), IDESC_PV,
                                         (kk > 0 || j > 0) ? 1u : 0u);
                             umma_commit(&pv_full[w]);
+                            if (C::WIDE) umma_commit(&s_free[w + NG * (g & 1)]);   // P sat in this S buffer
                             if (w == NG - 1) umma_commit(&kv_empty[st]);   // every group's PV of the tile issued
                         }
                         __syncwarp();
@@ -365,52 +381,63 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
             for (int og = 0; og < NG; ++og) { gf[og] = ex2(gm[og] - ms); lt += gl[og] * gf[og]; }
             const float inv = 1.f / lt;
-            float outv[HD];
+            // the slice in passes of EC columns (register budget): merge, normalise, stage, store
+            constexpr int EC = (HD < 32) ? HD : 32;
 #pragma unroll
-            for (int e = 0; e < HD; ++e) outv[e] = 0.f;
+            for (int hc = 0; hc < HD / EC; ++hc) {
+                float outv[EC];
 #pragma unroll
-            for (int og = 0; og < NG; ++og) {
-                float part[HD];
-                tmem_ld_f32<HD>(lane_base + C::TMEM_PV + og * DH + wg * HD, part);
-                const float fs = gf[og] * inv;
+                for (int e = 0; e < EC; ++e) outv[e] = 0.f;
 #pragma unroll
-                for (int e = 0; e < HD; ++e) outv[e] = fmaf(part[e], fs, outv[e]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&o_read[wg]);       // this warp is done with every accumulator
-            // the previous store of this group's slice must have finished reading it
-            if (row == 0) tma_wait_group_read<0>();
-            if (!group_sync()) return false;
+                for (int og = 0; og < NG; ++og) {
+                    float part[EC];
+                    tmem_ld_f32<EC>(lane_base + C::TMEM_PV + og * DH + wg * HD + hc * EC, part);
+                    const float fs = gf[og] * inv;
 #pragma unroll
-            for (int c8 = 0; c8 < HD / 8; ++c8) {
-                uint4 v;
-                v.x = pack_bf16(outv[c8 * 8 + 0], outv[c8 * 8 + 1]);
-                v.y = pack_bf16(outv[c8 * 8 + 2], outv[c8 * 8 + 3]);
-                v.z = pack_bf16(outv[c8 * 8 + 4], outv[c8 * 8 + 5]);
-                v.w = pack_bf16(outv[c8 * 8 + 6], outv[c8 * 8 + 7]);
-                sts128(aO + swz_off<HD * 2>(row, c8), v);
-                if (qrow < p.N && wg * HD + c8 * 8 < p.Dt) {
-                    if (p.o_resid != nullptr) {
-                        // rounding residual of O, straight to global memory
-                        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-                        uint32_t rw[4];
+                    for (int e = 0; e < EC; ++e) outv[e] = fmaf(part[e], fs, outv[e]);
+                }
+                if (hc == HD / EC - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&o_read[wg]);       // this warp is done with every accumulator
+                }
+                if (hc == 0) {
+                    // the previous store of this group's slice must have finished reading it
+                    if (row == 0) tma_wait_group_read<0>();
+                    if (!group_sync()) return false;
+                }
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            rw[e] = pack_bf16(outv[c8 * 8 + 2 * e] - bf16_lo(vw[e]), outv[c8 * 8 + 2 * e + 1] - bf16_hi(vw[e]));
-                        *reinterpret_cast<uint4*>(p.o_resid + act_off + c8 * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
-                    }
-                    if constexpr (GATED) {
-                        // O * sigmoid(gate), from the unrounded O
-                        const uint32_t gw[4] = {gv[c8].x, gv[c8].y, gv[c8].z, gv[c8].w};
-                        uint32_t ow[4];
+                for (int c8l = 0; c8l < EC / 8; ++c8l) {
+                    const int c8 = hc * (EC / 8) + c8l;
+                    uint4 v;
+                    v.x = pack_bf16(outv[c8l * 8 + 0], outv[c8l * 8 + 1]);
+                    v.y = pack_bf16(outv[c8l * 8 + 2], outv[c8l * 8 + 3]);
+                    v.z = pack_bf16(outv[c8l * 8 + 4], outv[c8l * 8 + 5]);
+                    v.w = pack_bf16(outv[c8l * 8 + 6], outv[c8l * 8 + 7]);
+                    sts128(aO + swz_off<HD * 2>(row, c8), v);
+                    if (qrow < p.N && wg * HD + c8 * 8 < p.Dt) {
+                        if (p.o_resid != nullptr) {
+                            // rounding residual of O, straight to global memory
+                            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                            uint32_t rw[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float s0 = 1.0f / (1.0f + ex2(-bf16_lo(gw[e]) * LOG2E));
-                            const float s1 = 1.0f / (1.0f + ex2(-bf16_hi(gw[e]) * LOG2E));
-                            ow[e] = pack_bf16(outv[c8 * 8 + 2 * e] * s0, outv[c8 * 8 + 2 * e + 1] * s1);
+                            for (int e = 0; e < 4; ++e)
+                                rw[e] = pack_bf16(outv[c8l * 8 + 2 * e] - bf16_lo(vw[e]),
+                                                  outv[c8l * 8 + 2 * e + 1] - bf16_hi(vw[e]));
+                            *reinterpret_cast<uint4*>(p.o_resid + act_off + c8 * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
                         }
-                        *reinterpret_cast<uint4*>(p.o_gated + act_off + c8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                        if constexpr (GATED) {
+                            // O * sigmoid(gate), from the unrounded O
+                            const uint32_t gw[4] = {gv[c8].x, gv[c8].y, gv[c8].z, gv[c8].w};
+                            uint32_t ow[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float s0 = 1.0f / (1.0f + ex2(-bf16_lo(gw[e]) * LOG2E));
+                                const float s1 = 1.0f / (1.0f + ex2(-bf16_hi(gw[e]) * LOG2E));
+                                ow[e] = pack_bf16(outv[c8l * 8 + 2 * e] * s0, outv[c8l * 8 + 2 * e + 1] * s1);
+                            }
+                            *reinterpret_cast<uint4*>(p.o_gated + act_off + c8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                        }
                     }
                 }
             }
@@ -444,6 +471,19 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int sbuf = wg + NG * (g & 1);
                 const uint32_t tS = lane_base + C::TMEM_S + (g & 1) * 128 + CW * wg;
                 if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 0);
+                // without a staged bias tile: this thread's CW bias values of the tile, straight from
+                // global memory, requested before the wait so that they arrive while the MMA runs
+                uint4 bg[C::WIDE ? CW / 8 : 1];
+                if constexpr (C::WIDE) {
+                    const int qrow = qt * TILE + row, col0 = j * TILE + CW * wg;
+                    const __nv_bfloat16* bp =
+                        p.bias + ((static_cast<size_t>(bs / p.S) * p.H + h) * p.N + qrow) * p.N + col0;
+#pragma unroll
+                    for (int c8 = 0; c8 < CW / 8; ++c8) {
+                        bg[c8] = make_uint4(0u, 0u, 0u, 0u);
+                        if (qrow < p.N && col0 + c8 * 8 < p.N) bg[c8] = __ldg(reinterpret_cast<const uint4*>(bp + c8 * 8));
+                    }
+                }
                 ok = warp_all(mbar_wait(&s_full[sbuf], (g >> 1) & 1, wc, 0x31));
                 if (!ok) break;
                 if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 1);
@@ -454,12 +494,14 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
                 ok = warp_all(mbar_wait(&kv_full[st], (g / ST) & 1, wc, 0x32));
                 if (!ok) break;
+                uint32_t dep = 0;      // data the release of the stage must wait for
                 {
                     // this warp's copy of the mask row slice: bf16 -> fp32 * log2e, -inf past N
                     if constexpr (CW == 64) {
                         const uint32_t mraw = sb + C::ST_MASK + 2 * CW * wg + 4 * lane;      // two bf16 per lane
                         uint32_t mw;
                         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(mw) : "r"(mraw));
+                        dep = mw;
                         const int c = j * TILE + CW * wg + 2 * lane;
                         const float m0 = (c < p.N) ? bf16_lo(mw) * LOG2E : -INFINITY;
                         const float m1 = (c + 1 < p.N) ? bf16_hi(mw) * LOG2E : -INFINITY;
@@ -468,6 +510,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const uint32_t mraw = sb + C::ST_MASK + 2 * CW * wg + 2 * lane;      // one bf16 per lane
                         uint16_t mw;
                         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(mw) : "r"(mraw));
+                        dep = mw;
                         const int c = j * TILE + CW * wg + lane;
                         const float m0 = (c < p.N) ? __uint_as_float(static_cast<uint32_t>(mw) << 16) * LOG2E : -INFINITY;
                         asm volatile("st.shared.f32 [%0], %1;" ::"r"(aWmask + 4 * lane), "f"(m0) : "memory");
@@ -478,7 +521,6 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // load of chunk ch+1 is in flight during the arithmetic of chunk ch
                 float2 x2[CW / 2];
                 float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: ILP
-                uint32_t dep = 0;
                 const uint32_t sbias = sb + C::ST_BIAS + bias_sub;
 #pragma unroll
                 for (int ch = 0; ch < CW / 16; ++ch) {
@@ -486,14 +528,20 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tmem_wait_ld();
                     if (ch + 1 < CW / 16) {
                         tmem_ld16(tS + 16 * (ch + 1), sv[cb ^ 1]);
-                    } else {
+                    } else if (!C::WIDE) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&s_free[sbuf]);
                     }
-                    const uint4 b0 = lds128(sbias + swz_off<128>(row, bias_c0 + 2 * ch));
-                    const uint4 b1 = lds128(sbias + swz_off<128>(row, bias_c0 + 2 * ch + 1));
-                    dep ^= b0.x ^ b1.x;
+                    uint4 b0, b1;
+                    if constexpr (C::WIDE) {
+                        b0 = bg[2 * ch];
+                        b1 = bg[2 * ch + 1];
+                    } else {
+                        b0 = lds128(sbias + swz_off<128>(row, bias_c0 + 2 * ch));
+                        b1 = lds128(sbias + swz_off<128>(row, bias_c0 + 2 * ch + 1));
+                        dep ^= b0.x ^ b1.x;
+                    }
                     const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
                     float2 mm[8];
 #pragma unroll
@@ -598,8 +646,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 l += rsum;
                 // P (bf16 pairs) into this group's columns of tensor memory
-                if constexpr (CW == 64) tmem_st32(lane_base + C::TMEM_P + wg * 32, pk);
-                else tmem_st16(lane_base + C::TMEM_P + wg * 16, pk);
+                if constexpr (CW == 64) tmem_st32(lane_base + C::p_col(wg, g), pk);
+                else tmem_st16(lane_base + C::p_col(wg, g), pk);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -650,9 +698,9 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     CUtensorMap tq, tk, tv, tb, to;
     int rc;
     const int Dt = d->D;          // 16 on the D = 32 kernel: boxes of 32 columns over tensors of 16
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, DH))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
     if ((rc = make_tmap_qkv_cols(&to, o, BS, d->N, d->H, Dt, TILE, C::HD, lay))) return rc;   // one slice per group
 
@@ -663,6 +711,7 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.total_items = BS * QT * d->H;
     p.c1 = ((scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(Dt))) * LOG2E;
     p.mask = static_cast<const __nv_bfloat16*>(mask);
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.lse = lse;
     p.o_resid = static_cast<__nv_bfloat16*>(o_resid);
     p.gate = static_cast<const __nv_bfloat16*>(gate);
@@ -720,5 +769,7 @@ extern "C" int evo_fwd_gated(const EvoDims* dims, const EvoStrides* strides, con
     if (dims->D <= 32)
         return evo::launch_fwd<32, EVO_FWD_NG32>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid,
                                                  lse, scale, st);
-    return evo::launch_fwd<64, 2>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse, scale, st);
+    if (dims->D <= 64)
+        return evo::launch_fwd<64, 2>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse, scale, st);
+    return evo::launch_fwd<128, 2>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse, scale, st);
 }

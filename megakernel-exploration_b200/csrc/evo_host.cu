@@ -320,7 +320,7 @@ int set_max_smem_once(const void* func, int bytes) {
 int check_dims(const EvoDims* d) {
     if (!d) return EVO_ERR_NULL_PTR;
     if (d->B <= 0 || d->S <= 0 || d->N <= 0 || d->H <= 0) return EVO_ERR_BAD_DIMS;
-    if (d->D != 16 && d->D != 32 && d->D != 64) return EVO_ERR_BAD_DIMS;
+    if (d->D != 16 && d->D != 32 && d->D != 64 && d->D != 96 && d->D != 128) return EVO_ERR_BAD_DIMS;
     if (d->N % 8 != 0) return EVO_ERR_BAD_DIMS;
     const double bytes = 2.0 * d->B * d->S * d->N * d->H * d->D;
     if (bytes >= 1099511627776.0) return EVO_ERR_BAD_DIMS;
@@ -412,7 +412,7 @@ int evo_profile_read(int kernel, float* total_ms, int* launches) {
 const char* evo_strerror(int code) {
     switch (code) {
         case EVO_OK: return "ok";
-        case EVO_ERR_BAD_DIMS: return "unsupported dimensions (need D in {16,32,64}, N % 8 == 0)";
+        case EVO_ERR_BAD_DIMS: return "unsupported dimensions (need D in {16,32,64,96,128}, N % 8 == 0)";
         case EVO_ERR_NULL_PTR: return "null pointer argument";
         case EVO_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
         case EVO_ERR_WORKSPACE: return "workspace too small or misaligned";

@@ -19,7 +19,7 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
     uint8_t* sY = sX + SQ_BYTES;                       // row tile
     uint8_t* sZ = sY + RowTile<DH>::BYTES;             // row tile
     uint64_t* bars = reinterpret_cast<uint64_t*>(sZ + RowTile<DH>::BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     const int tid = threadIdx.x, warp = tid >> 5;
     WaitCtx wc{abort_flag, status};
@@ -28,6 +28,7 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
         *abort_flag = 0;
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
+        mbar_init(&bars[2], 1);
         fence_mbar_init();
         fence_async_smem();
     }
@@ -49,7 +50,7 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     constexpr uint32_t T_A = 128 + 2 * DH;      // X as a bf16 A operand in tensor memory: 64 columns
-    constexpr uint32_t T_TS = T_A + 64;         // its product with y
+    constexpr uint32_t T_TS = 0;                // its product with y: second phase, over the first product
     {
         // row `tid` of X: 64 words of two bf16 each, into this thread's lane
         const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + T_A;
@@ -69,8 +70,8 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
 
     if (tid == 0) {
         mbar_arrive_expect_tx(&bars[0], 2 * RowTile<DH>::BYTES);
-        tma_load_4d(sY, &tm_y, &bars[0], 0, 0, 0, 0);
-        tma_load_4d(sZ, &tm_z, &bars[0], 0, 0, 0, 0);
+        tma_load_row_tile<DH>(sY, &tm_y, &bars[0], 0, 0, 0);
+        tma_load_row_tile<DH>(sZ, &tm_z, &bars[0], 0, 0, 0);
         if (mbar_wait(&bars[0], 0, wc, 1)) {
             tc_fence_after();
             const uint32_t aX = smem_u32(sX), aY = smem_u32(sY), aZ = smem_u32(sZ);
@@ -86,17 +87,13 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
             for (int kb = 0; kb < 8; ++kb)
                 umma_ss(tmem + 128 + DH, sq_mnmajor(aX, kb), RowTile<DH>::mnmajor(aY, kb),
                         make_idesc_bf16(128, DH, 1, 1), kb > 0);
-#pragma unroll
-            for (int kb = 0; kb < 8; ++kb)
-                umma_ts(tmem + T_TS, tmem + T_A + kb * 8, RowTile<DH>::mnmajor(aY, kb),
-                        make_idesc_bf16(128, DH, 0, 1), kb > 0);
             umma_commit(&bars[1]);
         }
     }
     __syncwarp();
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     if (warp_all(mbar_wait(&bars[1], 0, wc, 2))) {
         tc_fence_after();
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         uint32_t r[32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -115,6 +112,26 @@ selftest_mma_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_const
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) out_xty[tid * DH + c * 32 + i] = __uint_as_float(r[i]);
+        }
+    }
+    // second phase: the A operand from tensor memory, its product over the columns read above
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (tid == 0 && *abort_flag == 0u) {
+        const uint32_t aY = smem_u32(sY);
+#pragma unroll
+        for (int kb = 0; kb < 8; ++kb)
+            umma_ts(tmem + T_TS, tmem + T_A + kb * 8, RowTile<DH>::mnmajor(aY, kb),
+                    make_idesc_bf16(128, DH, 0, 1), kb > 0);
+        umma_commit(&bars[2]);
+    }
+    __syncwarp();
+    if (*abort_flag == 0u && warp_all(mbar_wait(&bars[2], 0, wc, 5))) {
+        tc_fence_after();
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
             tmem_ld32(lane_base + T_TS + c * 32, r);
             tmem_wait_ld();
 #pragma unroll
@@ -130,9 +147,9 @@ template <int DH>
 static int launch_selftest(const void* x, const void* y, const void* z, float* o0, float* o1,
                            float* o2, float* o3, cudaStream_t st) {
     CUtensorMap tm_y, tm_z;
-    int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH));
+    int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH), RowTile<DH>::BOX_D);
     if (rc) return rc;
-    rc = make_tmap_qkv(&tm_z, z, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH));
+    rc = make_tmap_qkv(&tm_z, z, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH), RowTile<DH>::BOX_D);
     if (rc) return rc;
     unsigned int* status = status_word();
     if (!status) return EVO_ERR_CUDA;
@@ -183,8 +200,8 @@ selftest_xt_kernel(const __grid_constant__ CUtensorMap tm_y, const __grid_consta
     const uint32_t tmem = *tmem_slot;
     if (tid == 0) {
         mbar_arrive_expect_tx(&bars[0], 2 * RowTile<DH>::BYTES + 2 * XT_BYTES);
-        tma_load_4d(sY, &tm_y, &bars[0], 0, 0, 0, 0);
-        tma_load_4d(sZ, &tm_z, &bars[0], 0, 0, 0, 0);
+        tma_load_row_tile<DH>(sY, &tm_y, &bars[0], 0, 0, 0);
+        tma_load_row_tile<DH>(sZ, &tm_z, &bars[0], 0, 0, 0);
         bulk_load(sA, a, XT_BYTES, &bars[0]);
         bulk_load(sB, b, XT_BYTES, &bars[0]);
         if (mbar_wait(&bars[0], 0, wc, 3)) {
@@ -221,13 +238,15 @@ template <int DH>
 static int launch_selftest_xt(const void* y, const void* z, const void* a, const void* b, float* out,
                               cudaStream_t st) {
     CUtensorMap tm_y, tm_z;
-    int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH));
+    int rc = make_tmap_qkv(&tm_y, y, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH), RowTile<DH>::BOX_D);
     if (rc) return rc;
-    rc = make_tmap_qkv(&tm_z, z, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH));
+    rc = make_tmap_qkv(&tm_z, z, 1, 128, 1, DH, 128, contiguous_layout(128, 1, DH), RowTile<DH>::BOX_D);
     if (rc) return rc;
     unsigned int* status = status_word();
     if (!status) return EVO_ERR_CUDA;
     const int smem = 2 * RowTile<DH>::BYTES + 3 * XT_BYTES + 64 + 1024;
+    rc = cuda_err(cudaFuncSetAttribute(selftest_xt_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (rc) return rc;
     selftest_xt_kernel<DH><<<1, 128, smem, st>>>(tm_y, tm_z, static_cast<const __nv_bfloat16*>(a),
                                                   static_cast<const __nv_bfloat16*>(b), out, status);
     return cuda_err(cudaGetLastError());
@@ -278,21 +297,23 @@ extern "C" int evo_selftest_wait_timeout(unsigned long long limit_ns, unsigned i
 extern "C" int evo_selftest_mma_extra(int D, const void* y, const void* z, const void* a, const void* b,
                                       float* out, void* stream) {
     if (!y || !z || !a || !b || !out) return EVO_ERR_NULL_PTR;
-    if (D != 32 && D != 64) return EVO_ERR_BAD_DIMS;
+    if (D != 32 && D != 64 && D != 128) return EVO_ERR_BAD_DIMS;
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) return EVO_ERR_ALIGNMENT;
     if (int rc = evo::ensure_context()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (D == 32) return evo::launch_selftest_xt<32>(y, z, a, b, out, st);
-    return evo::launch_selftest_xt<64>(y, z, a, b, out, st);
+    if (D == 64) return evo::launch_selftest_xt<64>(y, z, a, b, out, st);
+    return evo::launch_selftest_xt<128>(y, z, a, b, out, st);
 }
 
 extern "C" int evo_selftest_mma(int D, const void* x, const void* y, const void* z, float* out_yzt,
                                 float* out_xy, float* out_xty, float* out_ts, void* stream) {
     if (!x || !y || !z || !out_yzt || !out_xy || !out_xty || !out_ts) return EVO_ERR_NULL_PTR;
-    if (D != 32 && D != 64) return EVO_ERR_BAD_DIMS;
+    if (D != 32 && D != 64 && D != 128) return EVO_ERR_BAD_DIMS;
     if (int rc = evo::ensure_context()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (D == 32) return evo::launch_selftest<32>(x, y, z, out_yzt, out_xy, out_xty, out_ts, st);
     if (D == 64) return evo::launch_selftest<64>(x, y, z, out_yzt, out_xy, out_xty, out_ts, st);
+    if (D == 128) return evo::launch_selftest<128>(x, y, z, out_yzt, out_xy, out_xty, out_ts, st);
     return EVO_ERR_BAD_DIMS;
 }

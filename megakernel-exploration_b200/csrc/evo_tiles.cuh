@@ -1,12 +1,15 @@
 // Shared-memory tile conventions used by every kernel of this library, and the
 // UMMA descriptors that address them.
 //
-// ROW TILE  [R rows][DH bf16], DH in {32, 64}: what one TMA box load of a
-//   q/k/v/dO tile produces.  Row pitch 2*DH bytes (64 B or 128 B), swizzled
-//   with the matching TMA mode (SWIZZLE_64B / SWIZZLE_128B); the tile base is
-//   1024-byte aligned.
+// ROW TILE  [R rows][DH bf16], DH in {32, 64, 128}: what one TMA box load (DH = 128:
+//   two box loads of 64 columns) of a q/k/v/dO tile produces.  DH <= 64: row pitch
+//   2*DH bytes (64 B or 128 B), swizzled with the matching TMA mode (SWIZZLE_64B /
+//   SWIZZLE_128B); the tile base is 1024-byte aligned.  DH = 128: two sub-tiles of
+//   [128 rows][64 bf16], 16 KB apart, each laid out like the DH = 64 tile (the layout
+//   of the square tile below).
 //     * as a K-major operand  (rows index M or N, DH is the contraction axis)
-//     * as an MN-major operand (rows index K, DH is the M or N axis)
+//     * as an MN-major operand (rows index K, DH is the M or N axis; at DH = 128 the
+//       two 64-wide swizzle atoms are reached through the leading-dimension offset)
 //
 // SQUARE TILE [128 rows][128 bf16]: P / dS, written by threads.  Stored as two
 //   sub-tiles of [128 rows][64 bf16] (16 KB each, 128-byte rows, 128B swizzle):
@@ -25,22 +28,34 @@ constexpr uint32_t SQ_BYTES = 2 * SQ_SUB_BYTES;
 
 template <int DH>
 struct RowTile {
-    static_assert(DH == 32 || DH == 64, "head dim 32 or 64");
-    static constexpr uint32_t ROW_BYTES = DH * 2;
+    static_assert(DH == 32 || DH == 64 || DH == 128, "head dim 32, 64 or 128");
+    static constexpr int SUBS = (DH == 128) ? 2 : 1;     // sub-tiles of BOX_D columns
+    static constexpr int BOX_D = DH / SUBS;              // columns of one TMA box
+    static constexpr uint32_t ROW_BYTES = BOX_D * 2;     // row pitch inside a sub-tile
     static constexpr uint32_t SWZ = (DH == 32) ? SWZ_64B : SWZ_128B;
     static constexpr uint32_t SBO = 8 * ROW_BYTES;       // eight rows
-    static constexpr uint32_t BYTES = TILE * ROW_BYTES;  // 128-row tile
+    static constexpr uint32_t SUB_BYTES = TILE * ROW_BYTES;
+    static constexpr uint32_t BYTES = SUBS * SUB_BYTES;  // 128-row tile
     static constexpr int KBLOCKS = DH / 16;              // UMMA K = 16 for bf16
 
-    // K-major operand, contraction block kb (16 bf16 = 32 bytes along the row).
+    // K-major operand, contraction block kb (16 bf16 = 32 bytes along the row; four blocks per sub-tile).
     __device__ static __forceinline__ uint64_t kmajor(uint32_t saddr, int kb) {
-        return make_smem_desc(saddr + kb * 32, 16, SBO, SWZ);
+        return make_smem_desc(saddr + (kb >> 2) * SUB_BYTES + (kb & 3) * 32, 16, SBO, SWZ);
     }
     // MN-major operand, contraction block kb = rows 16*kb .. 16*kb+15.
     __device__ static __forceinline__ uint64_t mnmajor(uint32_t saddr, int kb) {
-        return make_smem_desc(saddr + kb * 16 * ROW_BYTES, BYTES, SBO, SWZ);
+        return make_smem_desc(saddr + kb * 16 * ROW_BYTES, SUB_BYTES, SBO, SWZ);
     }
 };
+
+// One row tile by TMA: box (BOX_D columns, one head, 128 rows, one row of B*S) per sub-tile.
+template <int DH>
+__device__ __forceinline__ void tma_load_row_tile(void* dst, const CUtensorMap* tm, uint64_t* bar, int h, int n0,
+                                                  int bs) {
+#pragma unroll
+    for (int s = 0; s < RowTile<DH>::SUBS; ++s)
+        tma_load_4d(static_cast<uint8_t*>(dst) + s * RowTile<DH>::SUB_BYTES, tm, bar, s * RowTile<DH>::BOX_D, h, n0, bs);
+}
 
 // Byte offset of the 16-byte chunk `cc` (0..15, eight bf16 columns each) of row r.
 __device__ __forceinline__ uint32_t sq_chunk_off(int r, int cc) {
@@ -91,9 +106,11 @@ struct RowDesc {
     using RT = RowTile<DH>;
     static constexpr uint32_t HI = desc_hi(RT::SBO, RT::SWZ);
     __device__ static __forceinline__ uint32_t kmajor_lo(uint32_t saddr) { return desc_lo(saddr, 16); }
-    __device__ static __forceinline__ uint32_t mnmajor_lo(uint32_t saddr) { return desc_lo(saddr, RT::BYTES); }
+    __device__ static __forceinline__ uint32_t mnmajor_lo(uint32_t saddr) { return desc_lo(saddr, RT::SUB_BYTES); }
     // contraction block kb of an operand whose lower word is `lo`
-    __device__ static __forceinline__ uint64_t kmajor(uint32_t lo, int kb) { return desc_join(lo + kb * 2, HI); }
+    __device__ static __forceinline__ uint64_t kmajor(uint32_t lo, int kb) {
+        return desc_join(lo + (kb >> 2) * static_cast<int>(RT::SUB_BYTES >> 4) + (kb & 3) * 2, HI);
+    }
     __device__ static __forceinline__ uint64_t mnmajor(uint32_t lo, int kb) {
         return desc_join(lo + kb * static_cast<int>(RT::ROW_BYTES), HI);
     }

@@ -74,8 +74,8 @@ def new_dbias_group(ranks=None, ctas: int = 0):
         return dist.new_group(ranks=ranks, pg_options=opts)
     return dist.new_group(ranks=ranks)
 
-# Head dims the library takes as they are; others below 64 are zero-padded up to the next one.
-TK_SUPPORTED_DIMS = (16, 32, 64)
+# Head dims the library takes as they are; others below 128 are zero-padded up to the next one.
+TK_SUPPORTED_DIMS = (16, 32, 64, 96, 128)
 
 
 def _next_supported_dim(d: int) -> int:
@@ -83,8 +83,7 @@ def _next_supported_dim(d: int) -> int:
         if d <= t:
             return t
     raise ValueError(
-        f"head_dim {d} exceeds max supported head_dim {TK_SUPPORTED_DIMS[-1]} "
-        f"(D=96/128 are not yet supported by the sm_100a kernels)"
+        f"head_dim {d} exceeds max supported head_dim {TK_SUPPORTED_DIMS[-1]}"
     )
 
 
@@ -348,7 +347,7 @@ class HostStreamedEvoAttention:
         eng = HostStreamedEvoAttention(device, chunk_rows=64)
         eng.run(q, k, v, res_mask, pair_bias, dO, out)   # all host tensors
 
-    q, k, v, dO: bf16 (B, N_SEQ, N_CTX, H, D), D in (32, 64); res_mask: bf16
+    q, k, v, dO: bf16 (B, N_SEQ, N_CTX, H, D), D in TK_SUPPORTED_DIMS; res_mask: bf16
     (B, N_SEQ, 1, 1, N_CTX) or (B, N_SEQ, N_CTX); pair_bias: bf16 (B, 1, H, N, N) or
     (B, H, N, N).  `out` = dict(o, dq, dk, dv: bf16 like q; dbias: fp32 like
     pair_bias).  Host tensors should be pinned (page-locked), otherwise the copies

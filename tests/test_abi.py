@@ -40,7 +40,7 @@ def test_argument_validation_without_gpu():
     lib = _evoattn.lib()
     good = _evoattn.EvoDims(1, 4, 128, 2, 32)
     assert lib.evo_bwd_workspace_bytes(C.byref(good)) > 4 * 4 * 128 * 2 * 32
-    for bad in (_evoattn.EvoDims(1, 4, 128, 2, 128), _evoattn.EvoDims(1, 4, 100, 2, 32),
+    for bad in (_evoattn.EvoDims(1, 4, 128, 2, 256), _evoattn.EvoDims(1, 4, 100, 2, 32),
                 _evoattn.EvoDims(0, 4, 128, 2, 32), _evoattn.EvoDims(1, 4, 128, 2, 48), _evoattn.EvoDims(1, 4, 128, 2, 8)):
         assert lib.evo_bwd_workspace_bytes(C.byref(bad)) == 0
         rc = lib.evo_fwd(C.byref(bad), 16, 16, 16, 16, 16, 16, None, 16, 0.0, None)

@@ -7,7 +7,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("D", [32, 64])
+@pytest.mark.parametrize("D", [32, 64, 128])
 def test_mma_operand_layouts(D):
     import _evoattn
     g = torch.Generator().manual_seed(7 + D)
@@ -31,7 +31,7 @@ def test_mma_operand_layouts(D):
         assert err < 1e-3, f"D={D} {name}: max abs err {err}"
 
 
-@pytest.mark.parametrize("D", [32, 64])
+@pytest.mark.parametrize("D", [32, 64, 128])
 def test_extra_contraction_block(D):
     """y z^T + a b^T with a, b as [128][8] extra tiles (un-swizzled 16-byte rows, second half of the
     contraction block read from a zero tile): the form in which the backward kernels add the mask,

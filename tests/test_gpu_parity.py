@@ -14,12 +14,14 @@ from _util import assert_parity, oracle_on_rounded, run_layer
 pytestmark = pytest.mark.gpu
 
 # (B, S, H, N, D): the reference's own case grid (evo_h100/test_tk_evoattention.py:80-103,
-# evo_h100/test_tk_evoattention_bwd.py:102-112) restricted to the head dims built
-# here (D=96/128 are not), with the reference's input distributions.
+# evo_h100/test_tk_evoattention_bwd.py:102-112), every head dim of it, with the reference's
+# input distributions; forward and backward are checked on every case.
 REFERENCE_GRID = [
     (1, 1, 4, 128, 64), (1, 1, 4, 256, 64), (1, 1, 4, 384, 64), (2, 1, 16, 384, 64),
     (4, 1, 16, 256, 64), (1, 32, 4, 384, 64), (1, 64, 4, 256, 64), (2, 1, 16, 256, 64),
     (1, 4, 4, 256, 64),
+    (1, 1, 4, 256, 128), (1, 4, 4, 384, 128), (1, 1, 4, 384, 128),
+    (1, 1, 4, 384, 96), (2, 1, 16, 256, 96), (1, 16, 4, 384, 96),
     (1, 1, 4, 384, 32), (1, 32, 4, 256, 32), (2, 4, 8, 384, 32),
     (1, 1, 4, 384, 16), (1, 16, 4, 256, 16),
 ]
@@ -42,6 +44,9 @@ EDGE_CASES = [
     (2, 3, 3, 136, 64, "bernoulli0.95"),    # ragged N, D=64, odd H
     (1, 2, 2, 520, 32, "tail10pct"),        # five tiles, ragged
     (1, 7, 1, 384, 32, "valid"),            # one head
+    (2, 3, 3, 136, 128, "bernoulli0.95"),   # ragged N, D=128, odd H
+    (1, 5, 2, 200, 96, "tail0to32"),        # ragged N, D=96, odd S
+    (1, 2, 1, 8, 128, "valid"),             # smallest N, D=128
 ]
 
 
@@ -188,6 +193,8 @@ def test_host_streamed_matches_layer():
     # (B, S, N, H, D, storage order as a permutation of (B, S, N, H, D) axes)
     (1, 24, 200, 2, 32, (0, 2, 1, 3, 4)),     # "ending node": stored [B][N_CTX][N_SEQ][H][D]
     (2, 5, 136, 3, 64, (0, 1, 3, 2, 4)),      # head-major, the reference kernel's own [B*S][H][N][D]
+    (1, 6, 200, 2, 128, (0, 2, 1, 3, 4)),     # "ending node", D = 128
+    (1, 3, 136, 3, 96, (0, 1, 3, 2, 4)),      # head-major, D = 96
 ])
 def test_permuted_view_in_place(case):
     """Q/K/V stored in another axis order and passed as permuted (B, S, N, H, D) views.  The layer reads
@@ -300,7 +307,7 @@ def test_c_abi_direct():
     lse_ref = evo_ref.evo_lse_ref(qr, kr, mr, br)
     assert evo_ref.max_abs_err(lse_ref, lse.cpu()) < 1e-2
     # argument validation returns codes, never throws from C
-    bad = _evoattn.EvoDims(B, S, N, H, 128)
+    bad = _evoattn.EvoDims(B, S, N, H, 48)
     with pytest.raises(_evoattn.EvoAttnError) as ei:
         _evoattn.fwd(bad, qd, kd, vd, bd, md, o, None, lse, 0.0, st)
     assert ei.value.code == -1
@@ -361,6 +368,8 @@ def test_head_dim_16_without_padding_copies():
     (2, 3, 136, 3, 64, None),                   # D = 64, B = 2
     (1, 8, 128, 2, 16, None),                   # D = 16
     (1, 12, 200, 2, 32, (0, 2, 1, 3, 4)),       # "ending node" storage order, gate stored the same way
+    (1, 3, 264, 2, 128, None),                  # D = 128
+    (2, 2, 136, 2, 96, (0, 2, 1, 3, 4)),        # D = 96, "ending node" storage order
 ])
 def test_fused_sigmoid_gate(case):
     """out = sigmoid(gate) * attention(...), the gate applied in the forward kernel's epilogue and its

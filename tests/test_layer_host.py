@@ -12,14 +12,16 @@ def _inputs(B=1, S=2, N=16, H=2, D=32):
 def test_surface_names():
     import tk_evo_attention_layer as L
     assert hasattr(L, "TKEvoAttention") and issubclass(L.TKEvoAttention, torch.autograd.Function)
-    assert L.TK_SUPPORTED_DIMS == (16, 32, 64)
+    assert L.TK_SUPPORTED_DIMS == (16, 32, 64, 96, 128)
     assert L._next_supported_dim(8) == 16 and L._next_supported_dim(16) == 16 and L._next_supported_dim(32) == 32
     assert L._next_supported_dim(24) == 32
     assert L._next_supported_dim(33) == 64 and L._next_supported_dim(64) == 64
+    assert L._next_supported_dim(65) == 96 and L._next_supported_dim(96) == 96
+    assert L._next_supported_dim(100) == 128 and L._next_supported_dim(128) == 128
     with pytest.raises(ValueError):
-        L._next_supported_dim(96)
+        L._next_supported_dim(129)
     with pytest.raises(ValueError):
-        L._next_supported_dim(128)
+        L._next_supported_dim(256)
 
 
 def test_shape_errors_are_assertions():
