@@ -44,7 +44,7 @@ def test_no_cpu_fallback():
 
 def test_unsupported_head_dim():
     from tk_evo_attention_layer import TKEvoAttention
-    q, k, v, m, b = _inputs(D=128)
+    q, k, v, m, b = _inputs(D=136)
     with pytest.raises(ValueError):
         TKEvoAttention.apply(q, k, v, m, b)
 
