@@ -13,8 +13,10 @@
  *   lse                   fp32 [B][S][H][N]  natural-log log-sum-exp
  *                         (evo_h100/tk_evoattention.cu:330-334)
  *   dbias                 fp32 [B][H][N][N]        (tk_evoattention.cu:1113)
- * Supported: D in {16, 32, 64} (16 runs on the D = 32 kernels: their loads
- * zero-fill and their stores clip the missing columns, no padded copy is made);
+ * Supported: D in {16, 32, 64, 96, 128}, the head dims of the reference's kernels
+ * and test grids (evo_h100/test_tk_evoattention.py:89-103).  16 runs on the D = 32
+ * kernels and 96 on the D = 128 kernels: their loads zero-fill and their stores clip
+ * the missing columns, no padded copy is made;
  * N a multiple of 8 (any N >= 8, the last tile may be ragged);
  * N*H*D*S*B*2 bytes < 2^40.
  */
@@ -108,7 +110,8 @@ int evo_bwd_phased(const EvoDims* dims, const EvoStrides* strides, const void* q
                    float* dbias, void* workspace, size_t workspace_bytes, float scale, unsigned phases,
                    int reserved_sms, void* stream);
 
-/* Bytes of scratch evo_bwd needs for these dims (delta rows + fp32 dQ accumulator). */
+/* Bytes of scratch evo_bwd needs for these dims (per-row and per-column extra tiles of the
+ * logits + fp32 dQ accumulator). */
 size_t evo_bwd_workspace_bytes(const EvoDims* dims);
 
 /* Backward.  Replaces evoattention_backward (tk_evoattention.cu:1051-1197):

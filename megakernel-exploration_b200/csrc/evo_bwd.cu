@@ -9,8 +9,10 @@
 //   dBias[b,h,q,kv] = sum over s of dS        (unscaled, tk_evoattention.cu:824-833)
 //
 // Four launches on one stream:
-//   1. bwd_prep_kernel    delta, -LSE*log2e and mask*log2e rows, padded to whole
-//                         tiles so the main kernels need no edge predicates
+//   1. bwd_prep_kernel    delta and the extra tiles through which the main kernels add
+//                         (mask - LSE) / scale to S and -delta to dP inside the tensor
+//                         core (evo_tiles.cuh, "EXTRA TILE"), padded to whole tiles so
+//                         the main kernels need no edge predicates
 //   2. evo_dbias_kernel   dBias (evo_dbias.cu): one CTA per pair-bias tile keeps its
 //                         sum over the S rows in registers, no reduction traffic
 //   3. evo_bwd_kernel     dQ, dK, dV (below)
@@ -22,21 +24,24 @@
 // RC steps.  dK/dV of every row of the chunk stay in tensor memory for the item.
 //
 //   warps 0-3, 4-7     two compute groups; group g owns kv columns 64g..64g+63
-//                      (thread = one q row).  Per step: P and dS from S and dP,
-//                      kept packed in registers until the previous step's
-//                      dV/dK/dQ MMAs have finished reading the P/dS tiles, then
-//                      written to shared memory as MMA operands.
+//                      (thread = one q row).  Per step: P = exp2(S' c1 + bias log2e)
+//                      and dS = P dP' from the two accumulators, kept packed in
+//                      registers until the previous step's dV/dK/dQ MMAs have
+//                      finished reading the P/dS tiles, then written to shared
+//                      memory as MMA operands.
 //   warps 8-11 (drain) warp w owns tensor-memory lanes 32(w-8)..: after every step
-//                      it stages its 32 rows of dQ (one of two accumulators) in its
-//                      own shared-memory slot and issues a TMA reduce-add (fp32)
-//                      for them; after an item, dK/dV go out as bf16 stores.  None
-//                      of this is on the compute groups' path.
-//   warp 12 (producer) TMA per step: Q, dO tiles and the -LSE / delta rows; K, V
-//                      tiles and the mask row per step (D=32) or per item (D=64);
-//                      the pair-bias tile per q tile
-//   warp 13 (mma)      tcgen05.mma, issued in whatever order operands become
-//                      ready: S = Q K^T and dP = dO V^T of the next step, or
-//                      dV += P^T dO, dK += dS^T Q, dQ = dS K of the current one
+//                      it stages its 32 rows of dQ in its own shared-memory slot and
+//                      issues a TMA reduce-add (fp32) for them; after an item, dK/dV
+//                      go out as bf16 stores.  None of this is on the compute groups'
+//                      path.
+//   warp 12 (producer) TMA per step: Q, dO tiles and the extra tile of the q rows; K, V
+//                      tiles and the extra tile of the kv rows per step (D=32) or per
+//                      item (D>=64); the pair-bias tile per q tile (D<=64)
+//   warps 13, 14, 15   tcgen05.mma issuers, one chain family each, so that no chain
+//                      queues behind another's issue: S' = Q K^T + extra block and
+//                      dP' = dO V^T + extra block of the next step (13);
+//                      dV += P^T dO and dK += dS^T Q (14); dQ = dS K (15).  Each warp
+//                      runs its loop with all lanes and elects one lane to issue.
 #include "evo_dbias.cuh"
 #include "evo_host.cuh"
 #include "evo_ptx.cuh"

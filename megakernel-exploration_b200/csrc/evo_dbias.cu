@@ -50,7 +50,7 @@ struct DbCfg {
     static_assert(REGS_COMPUTE * NCW * 32 + REGS_OTHER * 128 <= REGS_LAUNCH * THREADS, "register pool");
     // D <= 64: a stage holds the four operand tiles of a step.  D = 128 (four tiles are 128 KB):
     // a stage holds ONE operand pair, (Q, K) of a step or (dO, V) of a step, alternately; each of
-    // the two issuer warps waits for and releases its own pair.
+    // the two issuer warps issues from its own pair and both release every stage.
     static constexpr int SPLIT = (DH == 128) ? 2 : 1;     // stages per step
     static constexpr int QS = (DH == 32) ? 6 : 3;         // load stages
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;
@@ -116,7 +116,7 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 2 / C::SPLIT); }
+        for (int i = 0; i < QS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 2); }
         for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 2); mbar_init(&sdp_free[i], NCW); }
         fence_mbar_init();
         fence_async_smem();
@@ -217,7 +217,19 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 for (int n = 0; n < x.ns && ok; ++n, ++gs) {
                     const int ld = gs * C::SPLIT + ((C::SPLIT == 2 && is_dp) ? 1 : 0);
                     const int st = ld % QS, buf = gs & 1;
-                    ok = warp_all(mbar_wait(&st_full[st], (ld / QS) & 1, wc, 0x90));
+                    if (C::SPLIT == 2) {
+                        // The other issuer's stage of this step: observed and released unused, in load
+                        // order.  A parity wait tells "this phase is over" only to a waiter that saw
+                        // the previous phase end; a warp that skipped the other warp's uses of a stage
+                        // could take a load that has not landed yet for its own, two uses later.
+                        const int lo = gs * 2 + (is_dp ? 0 : 1);
+                        if (is_dp) {
+                            ok = warp_all(mbar_wait(&st_full[lo % QS], (lo / QS) & 1, wc, 0x92));
+                            if (ok && elect_one()) mbar_arrive(&st_empty[lo % QS]);
+                            __syncwarp();
+                        }
+                    }
+                    if (ok) ok = warp_all(mbar_wait(&st_full[st], (ld / QS) & 1, wc, 0x90));
                     if (ok && gs >= 2) ok = warp_all(mbar_wait(&sdp_free[buf], ((gs >> 1) - 1) & 1, wc, 0x91));
                     if (!ok) break;
                     tc_fence_after();
@@ -236,6 +248,12 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         umma_commit(&st_empty[st]);
                     }
                     __syncwarp();
+                    if (C::SPLIT == 2 && !is_dp) {
+                        const int lo = gs * 2 + 1;
+                        ok = warp_all(mbar_wait(&st_full[lo % QS], (lo / QS) & 1, wc, 0x92));
+                        if (ok && elect_one()) mbar_arrive(&st_empty[lo % QS]);
+                        __syncwarp();
+                    }
                 }
             }
         }

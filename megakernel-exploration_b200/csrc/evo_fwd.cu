@@ -9,26 +9,26 @@
 //
 // One persistent CTA per SM walks work items (b*s, q-tile of 128 rows, h), h
 // fastest so that CTAs running side by side touch the same 128-byte lines of
-// q/k/v.  Per item it streams kv tiles of 128 residues:
+// q/k/v.  Per item it streams kv tiles of 128 residues (NG = 2 softmax groups):
 //
-//   warp 8  (producer)  TMA: Q tile (double buffered), then per kv tile K, V, the
-//                       [128 x 128] bf16 pair-bias tile and the mask row into a
-//                       ring of stages
-//   warp 9  (mma)       tcgen05.mma, issued in whatever order operands become
-//                       ready, separately for the two softmax groups g:
-//                       S_g = Q K[64g:64g+64, :]^T into tensor memory and
-//                       PV_g = P_g V[64g:64g+64, :] with P_g read from tensor
-//                       memory.  The groups share no barrier inside an item, so
-//                       they drift apart and one group's exp2 phase overlaps the
-//                       other's FMA phase
+//   warp 8  (producer)  TMA: Q tile (double buffered; one buffer at D = 128), then per
+//                       kv tile K, V, the [128 x 128] bf16 pair-bias tile (D <= 64)
+//                       and the mask row into a ring of stages
+//   warp 9  (S issuer)  tcgen05.mma S_g = Q K[64g:64g+64, :]^T into tensor memory for
+//                       each softmax group g, a tile ahead of the softmax (two buffers)
+//   warp 10 (PV issuer) PV_g (+)= P_g V[64g:64g+64, :] with P_g read from tensor
+//                       memory; the accumulator stays in tensor memory for the item.
+//                       The groups share no barrier inside an item, so they drift
+//                       apart and one group's exp2 phase overlaps the other's FMA phase
 //   warps 0-3, 4-7      two softmax groups.  Group g owns kv columns 64g..64g+63
 //                       of every tile and runs its own online softmax over them
 //                       (thread = one q row): x = S*scale*log2e + bias*log2e +
 //                       mask*log2e, running max, exp2, P (bf16) back into tensor
-//                       memory, O_g = (O_g + PV_g) * alpha.  After an item, group 1
-//                       hands its partial (m, l, O) to group 0, which merges the
-//                       two (split-kv merge) and sends O out by TMA.  That
-//                       epilogue is deferred into the next item's first tile, so
+//                       memory; when the row maximum rises the accumulator is
+//                       rescaled in place.  After an item each group publishes its
+//                       (m, l); each group then merges, normalises and stores half of
+//                       the head-dim columns of O, reading both groups' accumulators.
+//                       That epilogue is deferred into the next item's first tile, so
 //                       the last PV of an item is never waited for idly.
 //
 // LSE is stored in natural log (tk_evoattention.cu:330-334).
