@@ -124,6 +124,7 @@ struct BwdParams {
     const __nv_bfloat16* xq;   // [B*S][H][NTP][8] extra tiles of the q rows  (bwd_prep_kernel)
     const __nv_bfloat16* xk;   // [B*S][NTP][8]    extra tiles of the kv rows
     const __nv_bfloat16* bias; // [B][H][N][N] (read directly when the bias tile is not staged)
+    float* dbias;              // [B][H][N][N] (written by this kernel only when S = 1)
     __nv_bfloat16* dk;    // activation layout `lay`
     __nv_bfloat16* dv;
     ActLayout lay;        // element strides of the activation tensors
@@ -134,7 +135,10 @@ struct BwdItem {
     int b, bs0, nr, h, j;
 };
 
-template <int DH>
+// DBIAS_HERE (S = 1 only): dBias is dS itself, no sum over rows, so the compute groups store their
+// fp32 dS straight to d_pair_bias and the dBias kernel (which would recompute S and dP for one step
+// per item) is not launched.
+template <int DH, bool DBIAS_HERE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -544,11 +548,25 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const float2 x2 = ffma2(u2f2(sv[cb][2 * k], sv[cb][2 * k + 1]), c1x2, b2);
                         p2[k] = make_float2(ex2(x2.x), ex2(x2.y));
                     }
+                    float2 dsv[8];
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
                         const float2 ds2 = fmul2(p2[k], u2f2(dv[cb][2 * k], dv[cb][2 * k + 1]));
                         pkp[ch * 8 + k] = pack_bf16(p2[k].x, p2[k].y);
                         pkd[ch * 8 + k] = pack_bf16(ds2.x, ds2.y);
+                        dsv[k] = ds2;
+                    }
+                    if constexpr (DBIAS_HERE) {
+                        // one S row: this step's dS tile is the dBias tile (q tile n, kv tile j)
+                        const int qrow = (n / x.nr) * TILE + row, c0 = x.j * TILE + 64 * wg + 16 * ch;
+                        if (qrow < p.N) {
+                            float* out = p.dbias + ((static_cast<size_t>(x.b) * p.H + x.h) * p.N + qrow) * p.N + c0;
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4)
+                                if (c0 + q4 * 4 < p.N)
+                                    *reinterpret_cast<float4*>(out + q4 * 4) =
+                                        make_float4(dsv[2 * q4].x, dsv[2 * q4].y, dsv[2 * q4 + 1].x, dsv[2 * q4 + 1].y);
+                        }
                     }
                 }
                 EVO_TE(t_cmp, p.status, 0x70);
@@ -775,27 +793,32 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     const size_t dq_bytes = static_cast<size_t>(BS) * d->N * d->H * DH * 4;
     const size_t db_bytes = static_cast<size_t>(d->B) * d->H * d->N * d->N * 4;
 
+    // one S row and the whole backward in this call: the dQ/dK/dV kernel writes dBias (= dS) itself
+    const bool dbias_here = (d->S == 1) && (phases & EVO_BWD_PHASE_DBIAS) && (phases & EVO_BWD_PHASE_DQKV);
+    p.dbias = dbias;
     if (phases & EVO_BWD_PHASE_DBIAS) {
-        if ((rc = cuda_err(cudaMemsetAsync(dbias, 0, db_bytes, st)))) return rc;
+        if (!dbias_here && (rc = cuda_err(cudaMemsetAsync(dbias, 0, db_bytes, st)))) return rc;
         bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
             static_cast<const __nv_bfloat16*>(d_o_in), lse, static_cast<const __nv_bfloat16*>(mask), xq, xk,
             1.0f / p.scale, BS, d->N, d->H, p.NTP, lay, Dt, static_cast<const __nv_bfloat16*>(gate),
             reinterpret_cast<__nv_bfloat16*>(ws + w.off_do), static_cast<__nv_bfloat16*>(d_gate));
         if ((rc = cuda_err(cudaGetLastError()))) return rc;
-        if ((rc = launch_dbias(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st))) return rc;
+        if (!dbias_here && (rc = launch_dbias(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st)))
+            return rc;
     }
     if (!(phases & EVO_BWD_PHASE_DQKV)) return EVO_OK;
 
     if ((rc = cuda_err(cudaMemsetAsync(dq_acc, 0, dq_bytes, st)))) return rc;
-    if ((rc = set_max_smem_once(reinterpret_cast<const void*>(evo_bwd_kernel<DH>), static_cast<int>(C::SMEM_BYTES))))
+    auto kernel = dbias_here ? evo_bwd_kernel<DH, true> : evo_bwd_kernel<DH, false>;
+    if ((rc = set_max_smem_once(reinterpret_cast<const void*>(kernel), static_cast<int>(C::SMEM_BYTES))))
         return rc;
     // SMs left to other work (a collective on another stream) while this kernel runs
     int use_sms = sms - (reserved_sms > 0 ? reserved_sms : 0);
     if (use_sms < 1) use_sms = 1;
     const int grid = p.total_items < use_sms ? p.total_items : use_sms;
     prof_begin(1, st);
-    evo_bwd_kernel<DH><<<grid, BWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tb, tdq, p);
+    kernel<<<grid, BWD_THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tb, tdq, p);
     prof_end(1, st);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 

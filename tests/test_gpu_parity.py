@@ -242,12 +242,17 @@ def test_strided_abi_rejects_bad_strides():
     assert e.value.code == -1
 
 
-def test_phased_backward_equals_single_call():
+@pytest.mark.parametrize("B,S,N,H,D", [
+    (1, 12, 384, 4, 32),
+    # one S row: the single call writes dBias from the dQ/dK/dV kernel (no dBias kernel), the phased
+    # call from the dBias kernel; ragged N so that the clipped stores of the last tile are covered
+    (2, 1, 328, 3, 32), (2, 1, 264, 2, 64), (1, 1, 200, 2, 128),
+])
+def test_phased_backward_equals_single_call(B, S, N, H, D):
     """evo_bwd_phased: the dBias phase followed by the dQ/dK/dV phase on fewer SMs (what the layer issues
     around the all-reduce on several GPUs) gives the same dK and dV bits as evo_bwd, dBias to fp32
     rounding and dQ to one bf16 step."""
     import _evoattn
-    B, S, N, H, D = 1, 12, 384, 4, 32
     q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 0.5, 1.0, "tail0to32", seed=17)
     dev, bf = "cuda", torch.bfloat16
     qd, kd, vd, dod = (t.to(dev, bf) for t in (q, k, v, d_o))
