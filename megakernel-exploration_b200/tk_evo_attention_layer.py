@@ -52,13 +52,16 @@ if HERE not in sys.path:
 
 import _evoattn  # noqa: E402  (ctypes binding of libevoattn.so)
 
-# SMs the dQ/dK/dV kernel leaves to the d_pair_bias all-reduce that runs beside it (groups of four
-# ranks or more).  The collective only overlaps if its kernel fits on them: create the process group
-# with new_dbias_group() (or run with NCCL_MAX_CTAS set to this number).  Measured on 8 B200s, config 4
-# split over S: 1.55 ms per step without the reservation, 1.48 ms with 4 SMs and 4 collective CTAs;
-# with more collective CTAs than reserved SMs the reservation only costs (1.56-1.60 ms).
+# SMs the dQ/dK/dV kernel leaves to the d_pair_bias all-reduce that runs beside it.  The collective
+# only overlaps if its kernel fits on them: create the process group with new_dbias_group() (or run
+# with NCCL_MAX_CTAS set to this number).  Measured on 8 B200s, config 4 split over S: 1.55 ms per
+# step without the reservation, 1.48 ms with 4 SMs and 4 collective CTAs; with more collective CTAs
+# than reserved SMs the reservation only costs (1.56-1.60 ms).  On 2 B200s, 512 rows of config 2 per
+# GPU: 1.337 ms per step without the reservation (the small-CTA collective then runs after the
+# kernel), 1.287 ms with it; config 4 split in two 4.50 against 4.31 ms.
 ALLREDUCE_RESERVED_SMS = int(os.environ.get("EVO_ALLREDUCE_RESERVED_SMS", "4"))
-ALLREDUCE_MIN_GROUP = 4
+# smallest group for which SMs are reserved
+ALLREDUCE_MIN_GROUP = int(os.environ.get("EVO_ALLREDUCE_MIN_GROUP", "2"))
 
 
 def new_dbias_group(ranks=None, ctas: int = 0):

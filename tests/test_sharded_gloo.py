@@ -79,7 +79,7 @@ def _worker(rank, world, port, out_dir):
     O.backward(d_o.to(torch.bfloat16))
     # with a process group the backward is issued in two phases around the all-reduce, and the second
     # phase leaves SMs to the collective
-    assert [c[0] for c in L._bwd_calls] == [1, 2] and L._bwd_calls[1][1] == 0     # two ranks: nothing reserved
+    assert [c[0] for c in L._bwd_calls] == [1, 2] and L._bwd_calls[1][1] == L.ALLREDUCE_RESERVED_SMS   # SMs left to the collective
     torch.save({"o": O.detach().float(), "dq": Q.grad.float(), "dk": K.grad.float(), "dv": V.grad.float(),
                 "dbias": PB.grad.float()}, os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
