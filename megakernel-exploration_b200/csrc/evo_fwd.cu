@@ -57,13 +57,17 @@ struct FwdCfg {
     static_assert(NG == 2 || NG == 4, "two or four softmax groups");
     static constexpr int CW = TILE / NG;                       // kv columns per group
     static constexpr int NSW = NG * 4;                         // softmax warps
-    static constexpr int THREADS = (NSW + 4) * 32;             // + producer, S issuer, PV issuer, one idle warp
-    // setmaxnreg budgets: the CTA's register pool is the launch count (the cap ptxas derives from
-    // the launch bound) times the threads; an increase that the pool cannot satisfy blocks for ever
+    // + an epilogue warpgroup (warps NSW .. NSW+3: warp & 3 is its quarter of the tensor-memory
+    // lanes) + a warpgroup of producer, S issuer, PV issuer and one idle warp
+    static constexpr int THREADS = (NSW + 8) * 32;
+    // setmaxnreg budgets (one value per warpgroup): the CTA's register pool is the launch count (the
+    // cap ptxas derives from the launch bound) times the threads; an increase that the pool cannot
+    // satisfy blocks for ever
     static constexpr int REGS_LAUNCH = (65536 / THREADS) & ~7;
-    static constexpr int REGS_SOFTMAX = (NG == 2) ? 208 : 112;
-    static constexpr int REGS_OTHER = (NG == 2) ? 88 : 32;
-    static_assert(REGS_SOFTMAX * NSW * 32 + REGS_OTHER * 128 <= REGS_LAUNCH * THREADS, "register pool");
+    static constexpr int REGS_SOFTMAX = (NG == 2) ? 200 : 96;
+    static constexpr int REGS_EPI = (NG == 2) ? 56 : 40;
+    static constexpr int REGS_OTHER = (NG == 2) ? 56 : 40;
+    static_assert((REGS_SOFTMAX * NSW + REGS_EPI * 4 + REGS_OTHER * 4) * 32 <= REGS_LAUNCH * THREADS, "register pool");
     static constexpr int STAGES = (DH == 32) ? 3 : 2;
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;          // one [128][DH] bf16 tile
     // D = 128 is short of shared and tensor memory: one Q buffer instead of two, the bias slice of
@@ -77,15 +81,13 @@ struct FwdCfg {
     static constexpr uint32_t STAGE_STRIDE = 2 * ROWT + BIAS_BYTES + 1024;
     static constexpr uint32_t OFF_Q = 0;                           // NQ buffers
     static constexpr uint32_t OFF_STAGE = OFF_Q + NQ * ROWT;
-    // O staging: one [128][DH/NG] slice per softmax group (each group stores its own head-dim columns)
+    // O staging: one row tile, written by the epilogue warpgroup, sent out by TMA
     static constexpr uint32_t OFF_O = OFF_STAGE + STAGES * STAGE_STRIDE;
-    static constexpr int HD = DH / NG;                             // head-dim columns a group finalises
-    static constexpr uint32_t O_SLICE = ROWT / NG;
     // exchange of the groups' (m, l) per row: [item parity][group][128 rows]
     static constexpr uint32_t OFF_XCH = OFF_O + ROWT;
     static constexpr uint32_t OFF_WMASK = OFF_XCH + 2 * NG * 128 * 8;      // NSW warps x CW floats
     static constexpr uint32_t OFF_BARS = OFF_WMASK + NSW * CW * 4;
-    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 4 * NG + 2 * NG + 2 * NG + 2 * NG + 2;
+    static constexpr uint32_t NUM_BARS = 4 + 2 * STAGES + 4 * NG + 2 * NG + 2 * NG + 3 + 2;
     static constexpr uint32_t OFF_MISC = OFF_BARS + NUM_BARS * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;   // + alignment slack
     static constexpr uint32_t TMEM_S = 0;                          // two buffers: + (tile & 1) * 128 + g * CW
@@ -130,8 +132,8 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                const __grid_constant__ CUtensorMap tm_o, const FwdParams p) {
     using C = FwdCfg<DH, NG>;
     using RT = RowTile<DH>;
-    constexpr int ST = C::STAGES, CW = C::CW, NSW = C::NSW, HD = C::HD;
-    constexpr int W_PROD = NSW, W_S = NSW + 1, W_PV = NSW + 2;
+    constexpr int ST = C::STAGES, CW = C::CW, NSW = C::NSW;
+    constexpr int W_EPI = NSW, W_PROD = NSW + 4, W_S = NSW + 5, W_PV = NSW + 6;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -145,9 +147,10 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* p_ready = s_free + 2 * NG;     // [NG] per softmax group
     uint64_t* pv_full = p_ready + NG;        // [NG]
     uint64_t* xch_ready = pv_full + NG;      // [item parity][group]: the group's final (m, l) of an item are written
-    uint64_t* o_read = xch_ready + 2 * NG;   // [group]: the group has read every accumulator of the finished item
-    uint64_t* g_bar = o_read + NG;           // [group]: rendezvous of the group's four warps
-    uint64_t* xu_done = g_bar + NG;          // [2]: a half of the groups has finished the exp2 pass of a tile
+    uint64_t* acc_full = xch_ready + 2 * NG; // every PV MMA of an item is complete
+    uint64_t* acc_free = acc_full + 1;       // the epilogue has read the item's accumulators and (m, l)
+    uint64_t* e_bar = acc_free + 1;          // rendezvous of the four epilogue warps
+    uint64_t* xu_done = e_bar + 1;           // [2]: a half of the groups has finished the exp2 pass of a tile
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -164,10 +167,10 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int i = 0; i < 2 * NG; ++i) {
             mbar_init(&s_full[i], 1); mbar_init(&s_free[i], C::WIDE ? 1 : 4); mbar_init(&xch_ready[i], 4);
         }
-        for (int i = 0; i < NG; ++i) {
-            mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1);
-            mbar_init(&o_read[i], 4); mbar_init(&g_bar[i], 4);
-        }
+        for (int i = 0; i < NG; ++i) { mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1); }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_free, 4);
+        mbar_init(e_bar, 4);
         for (int i = 0; i < 2; ++i) mbar_init(&xu_done[i], NSW / 2);
         fence_mbar_init();
         fence_async_smem();
@@ -200,7 +203,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bs = r / p.QT;
     };
 
-    if (warp >= NSW) {
+    if (warp >= NSW + 4) {
         reg_dec<C::REGS_OTHER>();
         if (warp == W_PROD) {
             if (lane == 0) {
@@ -286,9 +289,11 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int it = 0; it < n_items && ok; ++it) {
                 for (int j = 0; j < NT && ok; ++j, ++g) {
                     const int st = g % ST;
+                    // the first PV of an item overwrites the accumulators: the epilogue has read the previous item's
+                    if (j == 0 && it > 0) ok = warp_all(mbar_wait(acc_free, (it - 1) & 1, wc, 0x24));
 #pragma unroll
                     for (int w = 0; w < NG; ++w) {
-                        ok = warp_all(mbar_wait(&p_ready[w], g & 1, wc, 0x23));
+                        if (ok) ok = warp_all(mbar_wait(&p_ready[w], g & 1, wc, 0x23));
                         if (!ok) break;
                         tc_fence_after();
                         if (elect_one()) {
@@ -300,12 +305,136 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             umma_commit(&pv_full[w]);
                             if (C::WIDE) umma_commit(&s_free[w + NG * (g & 1)]);   // P sat in this S buffer
                             if (w == NG - 1) umma_commit(&kv_empty[st]);   // every group's PV of the tile issued
+                            if (w == NG - 1 && j == NT - 1) umma_commit(acc_full);   // ... and of the item
                         }
                         __syncwarp();
                     }
                 }
             }
         }
+    } else if (warp >= W_EPI) {
+        reg_dec<C::REGS_EPI>();
+        // ------------------------------ epilogue warpgroup ------------------------------
+        // Finishes item k while the softmax groups are already in item k+1: merges the groups'
+        // partial results (split-kv merge), normalises, writes O through shared memory and TMA, the
+        // log-sum-exp, the rounding residual and the gated output.  Thread = one q row; warp e reads
+        // tensor-memory lanes 32e .. 32e+31.
+        const int row = tid & 127;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        const uint32_t aO = smem_u32(smem + C::OFF_O);
+        const uint32_t aXch = smem_u32(smem + C::OFF_XCH);
+        bool ok = true;
+        uint32_t e_phase = 0;
+        auto epi_sync = [&]() -> bool {      // rendezvous of the four epilogue warps (bounded)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(e_bar);
+            const bool r = warp_all(mbar_wait(e_bar, e_phase, wc, 0x30));
+            e_phase ^= 1u;
+            return r;
+        };
+        constexpr int EC = 16;               // head-dim columns per pass (register budget)
+        for (int it = 0; it < n_items && ok; ++it) {
+            int bs, qt, h;
+            decode(it, bs, qt, h);
+            EVO_TS(t_epi);
+            const int qrow = qt * TILE + row;
+            size_t act_off;
+            if constexpr (STRIDED)
+                act_off = bs * p.lay.row + qrow * p.lay.n + h * p.lay.h;
+            else
+                act_off = ((static_cast<size_t>(bs) * p.N + qrow) * p.H + h) * DH;
+            // every group's (m, l) of the item, then every PV MMA of the item
+            float gm[NG], gl[NG];
+#pragma unroll
+            for (int og = 0; og < NG; ++og) {
+                if (ok) ok = warp_all(mbar_wait(&xch_ready[(it & 1) * NG + og], (it >> 1) & 1, wc, 0x35));
+                if (!ok) break;
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(gm[og]), "=f"(gl[og])
+                             : "r"(aXch + (((it & 1) * NG + og) * 128 + row) * 8));
+            }
+            if (ok) ok = warp_all(mbar_wait(acc_full, it & 1, wc, 0x37));
+            if (!ok) break;
+            tc_fence_after();
+            float mt = gm[0];
+#pragma unroll
+            for (int og = 1; og < NG; ++og) mt = fmaxf(mt, gm[og]);
+            const float ms = (mt == -INFINITY) ? 0.f : mt;
+            float gf[NG], lt = 0.f;
+#pragma unroll
+            for (int og = 0; og < NG; ++og) { gf[og] = ex2(gm[og] - ms); lt += gl[og] * gf[og]; }
+            const float inv = 1.f / lt;
+#pragma unroll
+            for (int og = 0; og < NG; ++og) gf[og] *= inv;
+            // the previous item's TMA store must have finished reading the staging tile
+            if (row == 0) tma_wait_group_read<0>();
+            if (!epi_sync()) { ok = false; break; }
+#pragma unroll
+            for (int hc = 0; hc < DH / EC; ++hc) {
+                float outv[EC];
+#pragma unroll
+                for (int e = 0; e < EC; ++e) outv[e] = 0.f;
+#pragma unroll
+                for (int og = 0; og < NG; ++og) {
+                    float part[EC];
+                    tmem_ld_f32<EC>(lane_base + C::TMEM_PV + og * DH + hc * EC, part);
+#pragma unroll
+                    for (int e = 0; e < EC; ++e) outv[e] = fmaf(part[e], gf[og], outv[e]);
+                }
+                if (hc == DH / EC - 1) {
+                    // accumulators and (m, l) are read: the next item's first PV may overwrite them
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_free);
+                }
+#pragma unroll
+                for (int c8l = 0; c8l < EC / 8; ++c8l) {
+                    const int col = hc * EC + c8l * 8;                 // first head-dim column of this 16-byte chunk
+                    uint4 v;
+                    v.x = pack_bf16(outv[c8l * 8 + 0], outv[c8l * 8 + 1]);
+                    v.y = pack_bf16(outv[c8l * 8 + 2], outv[c8l * 8 + 3]);
+                    v.z = pack_bf16(outv[c8l * 8 + 4], outv[c8l * 8 + 5]);
+                    v.w = pack_bf16(outv[c8l * 8 + 6], outv[c8l * 8 + 7]);
+                    sts128(aO + (col / RT::BOX_D) * RT::SUB_BYTES + swz_off<RT::ROW_BYTES>(row, (col % RT::BOX_D) / 8), v);
+                    if (qrow < p.N && col < p.Dt) {
+                        if (p.o_resid != nullptr) {
+                            // rounding residual of O, straight to global memory
+                            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                            uint32_t rw[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                rw[e] = pack_bf16(outv[c8l * 8 + 2 * e] - bf16_lo(vw[e]),
+                                                  outv[c8l * 8 + 2 * e + 1] - bf16_hi(vw[e]));
+                            *reinterpret_cast<uint4*>(p.o_resid + act_off + col) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                        }
+                        if constexpr (GATED) {
+                            // O * sigmoid(gate), from the unrounded O
+                            const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(p.gate + act_off + col));
+                            const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+                            uint32_t ow[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float s0 = 1.0f / (1.0f + ex2(-bf16_lo(gw[e]) * LOG2E));
+                                const float s1 = 1.0f / (1.0f + ex2(-bf16_hi(gw[e]) * LOG2E));
+                                ow[e] = pack_bf16(outv[c8l * 8 + 2 * e] * s0, outv[c8l * 8 + 2 * e + 1] * s1);
+                            }
+                            *reinterpret_cast<uint4*>(p.o_gated + act_off + col) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                        }
+                    }
+                }
+            }
+            if (qrow < p.N) p.lse[(static_cast<size_t>(bs) * p.H + h) * p.N + qrow] = ms * LN2 + __logf(lt);
+            fence_async_smem();
+            if (!epi_sync()) { ok = false; break; }
+            if (row == 0) {
+#pragma unroll
+                for (int sub = 0; sub < RT::SUBS; ++sub)
+                    if (sub * RT::BOX_D < p.Dt)
+                        tma_store_4d(&tm_o, smem + C::OFF_O + sub * RT::SUB_BYTES, sub * RT::BOX_D, h, qt * TILE, bs);
+                tma_commit_group();
+            }
+            EVO_TE(t_epi, p.status, 0x79);
+        }
+        if (row == 0) tma_wait_group<0>();
     } else {
         reg_inc<C::REGS_SOFTMAX>();
         // ------------------------------ softmax groups ------------------------------
@@ -313,7 +442,6 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int row = tid & 127;           // q row within the tile == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         const uint32_t aStage = smem_u32(smem + C::OFF_STAGE);
-        const uint32_t aO = smem_u32(smem + C::OFF_O) + wg * C::O_SLICE;
         const uint32_t aXch = smem_u32(smem + C::OFF_XCH);            // [parity][group][128 rows] (m, l)
         const uint32_t aWmask = smem_u32(smem + C::OFF_WMASK) + warp * CW * 4;
         const uint32_t scratch_w = smem_u32(tmem_slot + 2);           // a word nobody reads
@@ -325,140 +453,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         (void)CH0_MASK;
         bool ok = true;
         int g = 0;
-        uint32_t g_phase = 0;
-        // rendezvous of this group's four warps (bounded)
-        auto group_sync = [&]() -> bool {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&g_bar[wg]);
-            const bool r = warp_all(mbar_wait(&g_bar[wg], g_phase, wc, 0x30));
-            g_phase ^= 1u;
-            return r;
-        };
-
         float m_used = -INFINITY, l = 0.f;
-
-        // Finishes item `k` (coordinates pbs/pqt/ph).  Each group merges, normalises and stores
-        // head-dim columns wg*HD .. of O, reading EVERY group's accumulator from tensor memory
-        // (any warp can read any column of its lanes); the other groups' (m, l) come through
-        // shared memory, written when those groups finished the item.  Nothing here makes the
-        // groups meet: every wait is for something another group did a whole tile earlier.
-        auto epilogue = [&](int k, int pbs, int pqt, int ph, float pm, float pl) -> bool {
-            EVO_TS(t_epi);
-            // offset of this thread's slice (row, head, first column) in the activation tensors
-            const int qrow = pqt * TILE + row;
-            size_t act_off;
-            if constexpr (STRIDED)
-                act_off = pbs * p.lay.row + qrow * p.lay.n + ph * p.lay.h + wg * HD;
-            else
-                act_off = ((static_cast<size_t>(pbs) * p.N + qrow) * p.H + ph) * DH + wg * HD;
-            // gate logits of the slice, fetched now so that they have arrived when the merge is done
-            uint4 gv[HD / 8];
-            if constexpr (GATED) {
-#pragma unroll
-                for (int c8 = 0; c8 < HD / 8; ++c8) {
-                    gv[c8] = make_uint4(0u, 0u, 0u, 0u);
-                    if (qrow < p.N && wg * HD + c8 * 8 < p.Dt)
-                        gv[c8] = __ldg(reinterpret_cast<const uint4*>(p.gate + act_off + c8 * 8));
-                }
-            }
-            float gm[NG], gl[NG];
-#pragma unroll
-            for (int og = 0; og < NG; ++og) {
-                if (og == wg) { gm[og] = pm; gl[og] = pl; continue; }
-                if (!warp_all(mbar_wait(&xch_ready[(k & 1) * NG + og], (k >> 1) & 1, wc, 0x35))) return false;
-                // that group's last PV of the item (its accumulator is read below); the barrier cannot
-                // run a phase ahead: that group's next PV waits for this group's o_read arrival
-                if (!warp_all(mbar_wait(&pv_full[og], ((k + 1) * NT - 1) & 1, wc, 0x37))) return false;
-                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(gm[og]), "=f"(gl[og])
-                             : "r"(aXch + (((k & 1) * NG + og) * 128 + row) * 8));
-            }
-            tc_fence_after();
-            float mt = gm[0];
-#pragma unroll
-            for (int og = 1; og < NG; ++og) mt = fmaxf(mt, gm[og]);
-            const float ms = (mt == -INFINITY) ? 0.f : mt;
-            float gf[NG], lt = 0.f;
-#pragma unroll
-            for (int og = 0; og < NG; ++og) { gf[og] = ex2(gm[og] - ms); lt += gl[og] * gf[og]; }
-            const float inv = 1.f / lt;
-            // the slice in passes of EC columns (register budget): merge, normalise, stage, store
-            constexpr int EC = (HD < 32) ? HD : 32;
-#pragma unroll
-            for (int hc = 0; hc < HD / EC; ++hc) {
-                float outv[EC];
-#pragma unroll
-                for (int e = 0; e < EC; ++e) outv[e] = 0.f;
-#pragma unroll
-                for (int og = 0; og < NG; ++og) {
-                    float part[EC];
-                    tmem_ld_f32<EC>(lane_base + C::TMEM_PV + og * DH + wg * HD + hc * EC, part);
-                    const float fs = gf[og] * inv;
-#pragma unroll
-                    for (int e = 0; e < EC; ++e) outv[e] = fmaf(part[e], fs, outv[e]);
-                }
-                if (hc == HD / EC - 1) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&o_read[wg]);       // this warp is done with every accumulator
-                }
-                if (hc == 0) {
-                    // the previous store of this group's slice must have finished reading it
-                    if (row == 0) tma_wait_group_read<0>();
-                    if (!group_sync()) return false;
-                }
-#pragma unroll
-                for (int c8l = 0; c8l < EC / 8; ++c8l) {
-                    const int c8 = hc * (EC / 8) + c8l;
-                    uint4 v;
-                    v.x = pack_bf16(outv[c8l * 8 + 0], outv[c8l * 8 + 1]);
-                    v.y = pack_bf16(outv[c8l * 8 + 2], outv[c8l * 8 + 3]);
-                    v.z = pack_bf16(outv[c8l * 8 + 4], outv[c8l * 8 + 5]);
-                    v.w = pack_bf16(outv[c8l * 8 + 6], outv[c8l * 8 + 7]);
-                    sts128(aO + swz_off<HD * 2>(row, c8), v);
-                    if (qrow < p.N && wg * HD + c8 * 8 < p.Dt) {
-                        if (p.o_resid != nullptr) {
-                            // rounding residual of O, straight to global memory
-                            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-                            uint32_t rw[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                rw[e] = pack_bf16(outv[c8l * 8 + 2 * e] - bf16_lo(vw[e]),
-                                                  outv[c8l * 8 + 2 * e + 1] - bf16_hi(vw[e]));
-                            *reinterpret_cast<uint4*>(p.o_resid + act_off + c8 * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
-                        }
-                        if constexpr (GATED) {
-                            // O * sigmoid(gate), from the unrounded O
-                            const uint32_t gw[4] = {gv[c8].x, gv[c8].y, gv[c8].z, gv[c8].w};
-                            uint32_t ow[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float s0 = 1.0f / (1.0f + ex2(-bf16_lo(gw[e]) * LOG2E));
-                                const float s1 = 1.0f / (1.0f + ex2(-bf16_hi(gw[e]) * LOG2E));
-                                ow[e] = pack_bf16(outv[c8l * 8 + 2 * e] * s0, outv[c8l * 8 + 2 * e + 1] * s1);
-                            }
-                            *reinterpret_cast<uint4*>(p.o_gated + act_off + c8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                        }
-                    }
-                }
-            }
-            if (wg == 0 && qrow < p.N) p.lse[(static_cast<size_t>(pbs) * p.H + ph) * p.N + qrow] = ms * LN2 + __logf(lt);
-            fence_async_smem();
-            if (!group_sync()) return false;
-            if (row == 0 && wg * HD < p.Dt) {
-                tma_store_4d(&tm_o, smem + C::OFF_O + wg * C::O_SLICE, wg * HD, ph, pqt * TILE, pbs);
-                tma_commit_group();
-            }
-            // the other groups have read this group's accumulator: the next item's first PV may overwrite it
-#pragma unroll
-            for (int og = 0; og < NG; ++og)
-                if (og != wg && !warp_all(mbar_wait(&o_read[og], k & 1, wc, 0x36))) return false;
-            EVO_TE(t_epi, p.status, 0x79);
-            return true;
-        };
-
-        bool have_prev = false;
-        int pbs = 0, pqt = 0, ph = 0;
-        float pm = 0.f, pl = 0.f;
 
         for (int it = 0; it < n_items && ok; ++it) {
             int bs, qt, h;
@@ -611,18 +606,13 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
 
-                // The P columns in tensor memory are free once the previous tile's PV MMA is done.
-                // On the first tile of an item that previous tile belongs to the previous item, whose
-                // epilogue runs now (its last PV has had the whole softmax above to finish).
+                // The P columns in tensor memory are free, and the accumulator may be rescaled, once
+                // the previous tile's PV MMA is done.
                 if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 3);
-                if (j > 0 || have_prev) {
+                if (g > 0) {
                     ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x33));
                     if (!ok) break;
                     tc_fence_after();
-                }
-                if (j == 0 && have_prev) {
-                    ok = epilogue(it - 1, pbs, pqt, ph, pm, pl);
-                    if (!ok) break;
                 }
                 if ((warp & 3) == 0 && wg < 3) EVO_TL(p.status, 5 + wg, g, 4);
                 if (__any_sync(0xffffffffu, need)) {
@@ -661,19 +651,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                          "f"(m_used), "f"(l) : "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&xch_ready[(it & 1) * NG + wg]);
-            have_prev = true;
-            pbs = bs; pqt = qt; ph = h;
-            pm = m_used; pl = l;
         }
-        if (ok && have_prev) {
-            // last item: its final PV and epilogue
-            ok = warp_all(mbar_wait(&pv_full[wg], (g - 1) & 1, wc, 0x34));
-            if (ok) {
-                tc_fence_after();
-                ok = epilogue(n_items - 1, pbs, pqt, ph, pm, pl);
-            }
-        }
-        if (row == 0) tma_wait_group<0>();
     }
 
     if (tid == 0) EVO_TE(t_kernel, p.status, 0x7e);
@@ -702,7 +680,7 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
     if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
-    if ((rc = make_tmap_qkv_cols(&to, o, BS, d->N, d->H, Dt, TILE, C::HD, lay))) return rc;   // one slice per group
+    if ((rc = make_tmap_qkv(&to, o, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
 
     FwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
