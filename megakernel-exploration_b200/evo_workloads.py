@@ -21,9 +21,13 @@ WORKLOADS = {
     "cfg3_triangle":      (1, 384, 384, 4, 32, 0.5, 1.0, "valid"),
     "cfg4_large_msa":     (1, 1024, 768, 8, 32, 0.5, 2.0, "tail10pct"),
     "cfg5_long_triangle": (1, 1024, 1024, 4, 64, 0.5, 1.0, "bernoulli0.95"),
+    # not benchmark configurations: the two wide head dims of the reference's kernels and test grids
+    # (evo_h100/test_tk_evoattention.py:89-95) at a size that fills the GPU, for timing them
+    "wide_d128":          (1, 128, 768, 4, 128, 0.5, 1.0, "tail10pct"),
+    "wide_d96":           (1, 128, 768, 4, 96, 0.5, 1.0, "tail10pct"),
 }
 WORKLOAD_SEEDS = {"cfg1_cpu_fp32": 1001, "cfg2_msa_row": 1002, "cfg3_triangle": 1003,
-                  "cfg4_large_msa": 1004, "cfg5_long_triangle": 1005}
+                  "cfg4_large_msa": 1004, "cfg5_long_triangle": 1005, "wide_d128": 1006, "wide_d96": 1007}
 
 
 def make_mask(kind: str, B: int, S: int, N: int, gen: torch.Generator) -> torch.Tensor:
