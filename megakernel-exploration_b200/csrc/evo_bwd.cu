@@ -115,6 +115,7 @@ struct BwdCfg {
 struct BwdParams {
     int B, S, N, H;
     int Dt;          // true head dim (16 runs on the D = 32 kernel: loads zero-filled, stores clipped)
+    int KB;          // contraction blocks of 16 head-dim columns that hold data: ceil(Dt / 16)
     int NT;          // tiles per row: ceil(N / 128)
     int NTP;         // NT * 128
     int CPB;         // chunks per batch: ceil(S / RC)
@@ -295,8 +296,9 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // dQ = dS K.  Each warp runs its loop with all lanes (uniform control flow: operand
             // descriptors stay in uniform registers) and elects one lane to issue.
             constexpr uint32_t IDESC_SDP = make_idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t IDESC_DKV = make_idesc_bf16(128, DH, 1, 1);
-            constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, DH, 0, 1);
+            // N = the head-dim columns that hold data (the rest of a wider kernel's tile is zero fill)
+            const uint32_t IDESC_DKV = make_idesc_bf16(128, 16 * p.KB, 1, 1);
+            const uint32_t IDESC_DQ = make_idesc_bf16(128, 16 * p.KB, 0, 1);
             const uint32_t aSt = smem_u32(smem + C::OFF_STAGE), aKV = smem_u32(smem + C::OFF_KV);
             const uint32_t aZero = smem_u32(smem + C::OFF_ZERO);
             const int role = warp - BWD_WARP_MMA;          // 0: S/dP, 1: dV/dK, 2: dQ
@@ -324,6 +326,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             const uint32_t k_lo = RD::kmajor_lo(k_tile), v_lo = RD::kmajor_lo(v_tile);
 #pragma unroll
                             for (int kk = 0; kk < RT::KBLOCKS; ++kk) {
+                                if (kk >= p.KB) continue;      // zero-filled blocks past the true head dim
                                 umma_ss(tmem + C::TMEM_S, RD::kmajor(q_lo, kk), RD::kmajor(k_lo, kk), IDESC_SDP, kk > 0);
                                 umma_ss(tmem + C::TMEM_DP, RD::kmajor(do_lo, kk), RD::kmajor(v_lo, kk), IDESC_SDP, kk > 0);
                             }
@@ -406,7 +409,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&dq_free[b]);
                         }
-                        if (i * TILE + wrow0 < p.N) {     // warp-uniform
+                        if (i * TILE + wrow0 < p.N && rd * 32 < p.Dt) {     // warp-uniform
                             // the slot is free once lane 0's earlier bulk operations have read it
                             if (lane == 0) tma_wait_group_read<0>();
                             __syncwarp();
@@ -778,6 +781,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.total_items = d->B * p.CPB * d->H * NT;
     p.scale = (scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(Dt));
     p.Dt = Dt;
+    p.KB = (Dt + 15) / 16;
     p.c1 = p.scale * LOG2E;
     p.xq = reinterpret_cast<const __nv_bfloat16*>(xq);
     p.xk = reinterpret_cast<const __nv_bfloat16*>(xk);

@@ -74,6 +74,7 @@ struct DbCfg {
 struct DbParams {
     int B, S, N, H;
     int NT, NTP;
+    int KB;               // contraction blocks of 16 head-dim columns that hold data: ceil(D / 16)
     int Z, SL;            // S slices, rows per slice
     int total_items;      // Z * B * H * NT * NT
     float c1;             // scale * log2(e)
@@ -240,7 +241,8 @@ evo_dbias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         const uint32_t b_lo = RD::kmajor_lo(sb + (is_dp ? C::ST_V : C::ST_K));
 #pragma unroll
                         for (int kk = 0; kk < RT::KBLOCKS; ++kk)
-                            umma_ss(t0, RD::kmajor(a_lo, kk), RD::kmajor(b_lo, kk), IDESC, kk > 0);
+                            if (kk < p.KB)      // blocks past the true head dim are zero-filled: skipped
+                                umma_ss(t0, RD::kmajor(a_lo, kk), RD::kmajor(b_lo, kk), IDESC, kk > 0);
                         // + (mask - LSE) / scale on S, - delta on dP: the extra contraction block
                         umma_ss(t0, xt_desc(sb + C::ST_XQ, aZero),
                                 xt_desc(is_dp ? aSt + C::OFF_XDP : sb + C::ST_XK, aZero), IDESC, 1u);
@@ -395,6 +397,7 @@ static int launch_dbias_t(const EvoDims* d, const ActLayout& lay, const ActLayou
     DbParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
     p.NT = NT; p.NTP = NT * TILE;
+    p.KB = (d->D + 15) / 16;
     p.SL = (d->S + best_z - 1) / best_z;
     p.Z = (d->S + p.SL - 1) / p.SL;
     p.total_items = static_cast<int>(base * p.Z);

@@ -106,6 +106,7 @@ struct FwdCfg {
 struct FwdParams {
     int B, S, N, H;
     int Dt;            // true head dim (16 runs on the D = 32 kernel: loads zero-filled, stores clipped)
+    int KB;            // contraction blocks of 16 head-dim columns that hold data: ceil(Dt / 16)
     int QT;            // q tiles (= kv tiles) per row: ceil(N / 128)
     int total_items;   // B*S*QT*H
     float c1;          // scale * log2(e)
@@ -268,8 +269,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             const uint32_t kt = aSt + st * C::STAGE_STRIDE + C::ST_K + w * CW * RT::ROW_BYTES;
 #pragma unroll
                             for (int kb = 0; kb < RT::KBLOCKS; ++kb)
-                                umma_ss(tmem + C::TMEM_S + (g & 1) * 128 + CW * w, RT::kmajor(aQ + qb * C::ROWT, kb),
-                                        RT::kmajor(kt, kb), IDESC_S, kb > 0);
+                                if (kb < p.KB)      // blocks past the true head dim are zero-filled: skipped
+                                    umma_ss(tmem + C::TMEM_S + (g & 1) * 128 + CW * w, RT::kmajor(aQ + qb * C::ROWT, kb),
+                                            RT::kmajor(kt, kb), IDESC_S, kb > 0);
                             umma_commit(&s_full[sb]);
                             // Q is free once every group's S of the item's last tile is issued
                             if (w == NG - 1 && j == NT - 1) umma_commit(&q_empty[qb]);
@@ -282,7 +284,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // ------------------------------ PV issuer ------------------------------
             // PV_w (+)= P_w V[CW w : CW w + CW, :] with P_w read from tensor memory; the accumulator of a
             // group stays in tensor memory for the whole item (the first tile overwrites it).
-            constexpr uint32_t IDESC_PV = make_idesc_bf16(128, DH, 0, 1);
+            const uint32_t IDESC_PV = make_idesc_bf16(128, 16 * p.KB, 0, 1);   // N = the head-dim columns that hold data
             const uint32_t aSt = smem_u32(smem + C::OFF_STAGE);
             bool ok = true;
             int g = 0;
@@ -685,6 +687,7 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     FwdParams p;
     p.B = d->B; p.S = d->S; p.N = d->N; p.H = d->H;
     p.Dt = Dt;
+    p.KB = (Dt + 15) / 16;
     p.QT = QT;
     p.total_items = BS * QT * d->H;
     p.c1 = ((scale > 0.f) ? scale : 1.0f / sqrtf(static_cast<float>(Dt))) * LOG2E;
