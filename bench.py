@@ -4,7 +4,7 @@
                     [--workload cfg2_msa_row] [--scaling weak|strong]
 
 A step is one forward + backward of the workload through
-TKEvoAttention.apply on seeded synthetic inputs.  N=1 runs BASELINE config 2
+TKEvoAttention.apply on seeded synthetic inputs.  N=1 runs benchmark config 2
 (B=1, S=512, N=384, H=8, D=32, bf16).  N>1 (under torchrun, one rank per GPU)
 shards the independent S axis over ranks with the pair bias replicated and an
 NCCL all-reduce of dBias in backward: "weak" keeps S rows per GPU fixed,

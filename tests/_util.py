@@ -38,7 +38,7 @@ def abs_tol(name, ref, strict=False):
     spacing at magnitude x is 2^-8 x .. 2^-7 x: no bf16 result can be guaranteed
     closer than half of that, so where the reference exceeds ~5 in magnitude the
     bound is one bf16 step at the largest reference value.  dBias is fp32 and
-    always held to 2e-2.  strict=True (the BASELINE configs) holds every tensor to
+    always held to 2e-2.  strict=True (the benchmark configs) holds every tensor to
     the flat 2e-2."""
     if name in BF16_OUTPUTS and not strict:
         return max(evo_ref.MAX_ABS_TOL, 2.0 ** -8 * ref.abs().max().item())

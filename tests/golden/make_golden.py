@@ -1,4 +1,4 @@
-"""Generates tests/golden/cfg1_golden.npz: the fp32 CPU oracle on BASELINE
+"""Generates tests/golden/cfg1_golden.npz: the fp32 CPU oracle on benchmark
 config 1 (B=1, S=32, N=64, H=4, D=32; q,k,v,bias,dO ~ N(0,1); Bernoulli(0.9)
 additive mask with residue 0 forced valid; seed 1001).
 

@@ -38,7 +38,7 @@ def test_reference_grid(B, S, H, N, D):
 # edge cases the reference never tested: ragged N (not a multiple of 128), a
 # single partial tile, S that does not divide the row chunk, B > 1 with S > 1
 EDGE_CASES = [
-    (1, 32, 4, 64, 32, "bernoulli0.9"),     # BASELINE config 1's shape, bf16
+    (1, 32, 4, 64, 32, "bernoulli0.9"),     # benchmark config 1's shape, bf16
     (1, 3, 2, 8, 32, "valid"),              # smallest N
     (1, 5, 2, 200, 32, "tail0to32"),        # ragged N, odd S
     (2, 3, 3, 136, 64, "bernoulli0.95"),    # ragged N, D=64, odd H
@@ -59,7 +59,7 @@ def test_edge_cases(B, S, H, N, D, mk):
 
 
 def test_golden_config1():
-    """BASELINE config 1 against the committed fixture (tests/golden/)."""
+    """benchmark config 1 against the committed fixture (tests/golden/)."""
     import os
     import numpy as np
     g = np.load(os.path.join(os.path.dirname(__file__), "golden", "cfg1_golden.npz"))
