@@ -179,6 +179,26 @@ int evo_bwd_gated(const EvoDims* dims, const EvoStrides* strides, const void* q,
                   void* dk, void* dv, void* d_gate, float* dbias, void* workspace, size_t workspace_bytes,
                   float scale, unsigned phases, int reserved_sms, void* stream);
 
+/* The same two calls with separate views for the three families of activation tensors
+ * (no counterpart in the reference, whose wrapper copies every tensor into one layout,
+ * evo_h100/tk_evo_attention_layer.py:81-102):
+ *   s_qkv   q, k, v                                   (read)
+ *   s_out   o, o_resid, o_gated, gate, d_out, d_gate  (the output side)
+ *   s_grad  dq, dk, dv                                (written by the backward)
+ * Each is an EvoStrides as in evo_fwd_strided, or NULL for contiguous.  A view need not be
+ * dense: q, k and v sliced out of one fused projection [B][S][N][3][H][D] are read where
+ * they lie, while O and the gradients are written contiguously. */
+int evo_fwd_views(const EvoDims* dims, const EvoStrides* s_qkv, const EvoStrides* s_out, const void* q,
+                  const void* k, const void* v, const void* pair_bias, const void* res_mask,
+                  const void* gate, void* o, void* o_gated, void* o_resid, float* lse, float scale,
+                  void* stream);
+int evo_bwd_views(const EvoDims* dims, const EvoStrides* s_qkv, const EvoStrides* s_out,
+                  const EvoStrides* s_grad, const void* q, const void* k, const void* v,
+                  const void* pair_bias, const void* res_mask, const void* gate, const void* o,
+                  const void* o_resid, const float* lse, const void* d_out, void* dq, void* dk, void* dv,
+                  void* d_gate, float* dbias, void* workspace, size_t workspace_bytes, float scale,
+                  unsigned phases, int reserved_sms, void* stream);
+
 /* Reads (and clears) the device status word that kernels set when a bounded
  * wait gives up.  Synchronises the device.  Returns EVO_OK, EVO_ERR_DEVICE_WAIT
  * (raw word in *raw if non-NULL) or EVO_ERR_CUDA.  The reference has no

@@ -44,6 +44,10 @@ SYMBOLS = {
     "evo_bwd_phased": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 14
                        + [C.c_size_t, C.c_float, C.c_uint, C.c_int, C.c_void_p]),
     "evo_fwd_gated": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 10 + [C.c_float, C.c_void_p]),
+    "evo_fwd_views": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides), C.POINTER(EvoStrides)] + [C.c_void_p] * 10
+                      + [C.c_float, C.c_void_p]),
+    "evo_bwd_views": (C.c_int, [C.POINTER(EvoDims)] + [C.POINTER(EvoStrides)] * 3 + [C.c_void_p] * 16
+                      + [C.c_size_t, C.c_float, C.c_uint, C.c_int, C.c_void_p]),
     "evo_bwd_gated": (C.c_int, [C.POINTER(EvoDims), C.POINTER(EvoStrides)] + [C.c_void_p] * 16
                       + [C.c_size_t, C.c_float, C.c_uint, C.c_int, C.c_void_p]),
     "evo_bwd_gated_workspace_bytes": (C.c_size_t, [C.POINTER(EvoDims)]),
@@ -158,6 +162,28 @@ def bwd_gated(dims: EvoDims, strides, q, k, v, bias, mask, gate, o, o_resid, lse
                               _ptr(lse), _ptr(d_out), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(d_gate), _ptr(dbias),
                               _ptr(workspace), workspace.numel() * workspace.element_size(), float(scale),
                               int(phases), int(reserved_sms), stream), "evo_bwd_gated")
+
+
+def _sref(strides):
+    return C.byref(strides) if strides is not None else None
+
+
+def fwd_views(dims: EvoDims, s_qkv, s_out, q, k, v, bias, mask, gate, o, o_gated, o_resid, lse, scale: float,
+              stream: int) -> None:
+    """evo_fwd_gated with separate views for q/k/v (s_qkv) and the output side (s_out); None = contiguous."""
+    check(lib().evo_fwd_views(C.byref(dims), _sref(s_qkv), _sref(s_out), _ptr(q), _ptr(k), _ptr(v), _ptr(bias),
+                              _ptr(mask), _ptr(gate), _ptr(o), _ptr(o_gated), _ptr(o_resid), _ptr(lse), float(scale),
+                              stream), "evo_fwd_views")
+
+
+def bwd_views(dims: EvoDims, s_qkv, s_out, s_grad, q, k, v, bias, mask, gate, o, o_resid, lse, d_out, dq, dk, dv,
+              d_gate, dbias, workspace, scale: float, phases: int, reserved_sms: int, stream: int) -> None:
+    """evo_bwd_gated with separate views for q/k/v (s_qkv), o/d_out/gate/d_gate (s_out) and dq/dk/dv (s_grad)."""
+    check(lib().evo_bwd_views(C.byref(dims), _sref(s_qkv), _sref(s_out), _sref(s_grad), _ptr(q), _ptr(k), _ptr(v),
+                              _ptr(bias), _ptr(mask), _ptr(gate), _ptr(o), _ptr(o_resid), _ptr(lse), _ptr(d_out),
+                              _ptr(dq), _ptr(dk), _ptr(dv), _ptr(d_gate), _ptr(dbias), _ptr(workspace),
+                              workspace.numel() * workspace.element_size(), float(scale), int(phases),
+                              int(reserved_sms), stream), "evo_bwd_views")
 
 
 def bwd_workspace_bytes(dims: EvoDims) -> int:

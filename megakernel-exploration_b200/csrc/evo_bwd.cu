@@ -748,7 +748,9 @@ static BwdWorkspace bwd_workspace(const EvoDims* d, bool gated = false) {
 }
 
 template <int DH>
-static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v, const void* bias,
+// lay_in: q, k, v; lay_out: o, o_resid, d_o, gate, d_gate; lay_grad: dq, dk, dv
+static int launch_bwd(const EvoDims* d, const ActLayout& lay_in, const ActLayout& lay_out, const ActLayout& lay_grad,
+                      const void* q, const void* k, const void* v, const void* bias,
                       const void* mask, const void* o, const void* o_resid, const float* lse, const void* d_o_in,
                       void* dq, void* dk, void* dv, float* dbias, uint8_t* ws, float scale, unsigned phases,
                       int reserved_sms, cudaStream_t st, const void* gate = nullptr, void* d_gate = nullptr) {
@@ -758,7 +760,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     const BwdWorkspace w = bwd_workspace(d, gate != nullptr);
     // with a gate the kernels read the gradient entering the attention from the workspace (contiguous)
     const void* d_o = gate ? static_cast<const void*>(ws + w.off_do) : d_o_in;
-    const ActLayout lay_do = gate ? contiguous_layout(d->N, d->H, d->D) : lay;
+    const ActLayout lay_do = gate ? contiguous_layout(d->N, d->H, d->D) : lay_out;
     uint4* xq = reinterpret_cast<uint4*>(ws + w.off_xq);
     uint4* xk = reinterpret_cast<uint4*>(ws + w.off_xk);
     float* dq_acc = reinterpret_cast<float*>(ws + w.off_dq);
@@ -766,9 +768,9 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     CUtensorMap tq, tk, tv, tdo, tb, tdq;
     int rc;
     const int Dt = d->D;          // 16 on the D = 32 kernel: boxes of 32 columns over tensors of 16
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay_in, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay_in, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay_in, RowTile<DH>::BOX_D))) return rc;
     if ((rc = make_tmap_qkv(&tdo, d_o, BS, d->N, d->H, Dt, TILE, lay_do, RowTile<DH>::BOX_D))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
     if ((rc = make_tmap_rows_box(&tdq, dq_acc, 4, BS, d->N, d->H, DH, 32, 32))) return rc;
@@ -787,7 +789,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     p.xk = reinterpret_cast<const __nv_bfloat16*>(xk);
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
-    p.lay = lay;
+    p.lay = lay_grad;          // the kernel's own stores are dK and dV
     p.status = status_word();
     if (!p.status) return EVO_ERR_CUDA;
 
@@ -805,10 +807,10 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
         bwd_prep_kernel<DH><<<sms * 8, 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(o_resid),
             static_cast<const __nv_bfloat16*>(d_o_in), lse, static_cast<const __nv_bfloat16*>(mask), xq, xk,
-            1.0f / p.scale, BS, d->N, d->H, p.NTP, lay, Dt, static_cast<const __nv_bfloat16*>(gate),
+            1.0f / p.scale, BS, d->N, d->H, p.NTP, lay_out, Dt, static_cast<const __nv_bfloat16*>(gate),
             reinterpret_cast<__nv_bfloat16*>(ws + w.off_do), static_cast<__nv_bfloat16*>(d_gate));
         if ((rc = cuda_err(cudaGetLastError()))) return rc;
-        if (!dbias_here && (rc = launch_dbias(d, lay, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st)))
+        if (!dbias_here && (rc = launch_dbias(d, lay_in, lay_do, q, k, v, bias, d_o, xq, xk, dbias, scale, sms, st)))
             return rc;
     }
     if (!(phases & EVO_BWD_PHASE_DQKV)) return EVO_OK;
@@ -826,7 +828,7 @@ static int launch_bwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     prof_end(1, st);
     if ((rc = cuda_err(cudaGetLastError()))) return rc;
 
-    cvt_dq_kernel<DH><<<sms * 8, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), dq_bytes / 32, d->N, d->H, lay, Dt);
+    cvt_dq_kernel<DH><<<sms * 8, 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), dq_bytes / 32, d->N, d->H, lay_grad, Dt);
     return cuda_err(cudaGetLastError());
 }
 
@@ -921,11 +923,23 @@ extern "C" int evo_bwd_gated(const EvoDims* dims, const EvoStrides* strides, con
                              void* dk, void* dv, void* d_gate, float* dbias, void* workspace,
                              size_t workspace_bytes, float scale, unsigned phases, int reserved_sms,
                              void* stream) {
+    return evo_bwd_views(dims, strides, strides, strides, q, k, v, pair_bias, res_mask, gate, o, o_resid, lse, d_o, dq,
+                         dk, dv, d_gate, dbias, workspace, workspace_bytes, scale, phases, reserved_sms, stream);
+}
+
+extern "C" int evo_bwd_views(const EvoDims* dims, const EvoStrides* s_qkv, const EvoStrides* s_out,
+                             const EvoStrides* s_grad, const void* q, const void* k, const void* v,
+                             const void* pair_bias, const void* res_mask, const void* gate, const void* o,
+                             const void* o_resid, const float* lse, const void* d_o, void* dq, void* dk, void* dv,
+                             void* d_gate, float* dbias, void* workspace, size_t workspace_bytes, float scale,
+                             unsigned phases, int reserved_sms, void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
     if (!(phases & (EVO_BWD_PHASE_DBIAS | EVO_BWD_PHASE_DQKV))) return EVO_ERR_BAD_DIMS;
-    evo::ActLayout lay;
-    if ((rc = evo::layout_from_strides(dims, strides, &lay))) return rc;
+    evo::ActLayout lay, lay_out, lay_grad;
+    if ((rc = evo::layout_from_strides(dims, s_qkv, &lay))) return rc;
+    if ((rc = evo::layout_from_strides(dims, s_out, &lay_out))) return rc;
+    if ((rc = evo::layout_from_strides(dims, s_grad, &lay_grad))) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse || !d_o || !dq || !dk || !dv || !dbias ||
         !workspace)
         return EVO_ERR_NULL_PTR;
@@ -945,11 +959,11 @@ extern "C" int evo_bwd_gated(const EvoDims* dims, const EvoStrides* strides, con
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     if (dims->D <= 32)
-        return evo::launch_bwd<32>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+        return evo::launch_bwd<32>(dims, lay, lay_out, lay_grad, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
                                    ws, scale, phases, reserved_sms, st, gate, d_gate);
     if (dims->D <= 64)
-        return evo::launch_bwd<64>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
+        return evo::launch_bwd<64>(dims, lay, lay_out, lay_grad, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias,
                                    ws, scale, phases, reserved_sms, st, gate, d_gate);
-    return evo::launch_bwd<128>(dims, lay, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
+    return evo::launch_bwd<128>(dims, lay, lay_out, lay_grad, q, k, v, pair_bias, res_mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws,
                                 scale, phases, reserved_sms, st, gate, d_gate);
 }

@@ -667,8 +667,9 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #define EVO_FWD_NG32 2
 #endif
 
+// lay_in: q, k, v; lay: the output side (o, o_resid, gate, o_gated)
 template <int DH, int NG>
-static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, const void* k, const void* v,
+static int launch_fwd(const EvoDims* d, const ActLayout& lay_in, const ActLayout& lay, const void* q, const void* k, const void* v,
                       const void* bias, const void* mask, const void* gate, void* o, void* o_gated, void* o_resid,
                       float* lse, float scale, cudaStream_t st) {
     using C = FwdCfg<DH, NG>;
@@ -678,9 +679,9 @@ static int launch_fwd(const EvoDims* d, const ActLayout& lay, const void* q, con
     CUtensorMap tq, tk, tv, tb, to;
     int rc;
     const int Dt = d->D;          // 16 on the D = 32 kernel: boxes of 32 columns over tensors of 16
-    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
-    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
-    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tq, q, BS, d->N, d->H, Dt, TILE, lay_in, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tk, k, BS, d->N, d->H, Dt, TILE, lay_in, RowTile<DH>::BOX_D))) return rc;
+    if ((rc = make_tmap_qkv(&tv, v, BS, d->N, d->H, Dt, TILE, lay_in, RowTile<DH>::BOX_D))) return rc;
     if ((rc = make_tmap_bias(&tb, bias, d->B, d->H, d->N))) return rc;
     if ((rc = make_tmap_qkv(&to, o, BS, d->N, d->H, Dt, TILE, lay, RowTile<DH>::BOX_D))) return rc;
 
@@ -733,10 +734,19 @@ extern "C" int evo_fwd_strided(const EvoDims* dims, const EvoStrides* strides, c
 extern "C" int evo_fwd_gated(const EvoDims* dims, const EvoStrides* strides, const void* q, const void* k,
                              const void* v, const void* pair_bias, const void* res_mask, const void* gate,
                              void* o, void* o_gated, void* o_resid, float* lse, float scale, void* stream) {
+    return evo_fwd_views(dims, strides, strides, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse, scale,
+                         stream);
+}
+
+extern "C" int evo_fwd_views(const EvoDims* dims, const EvoStrides* s_qkv, const EvoStrides* s_out, const void* q,
+                             const void* k, const void* v, const void* pair_bias, const void* res_mask,
+                             const void* gate, void* o, void* o_gated, void* o_resid, float* lse, float scale,
+                             void* stream) {
     int rc = evo::check_dims(dims);
     if (rc) return rc;
-    evo::ActLayout lay;
-    if ((rc = evo::layout_from_strides(dims, strides, &lay))) return rc;
+    evo::ActLayout lay, lay_in;
+    if ((rc = evo::layout_from_strides(dims, s_qkv, &lay_in))) return rc;
+    if ((rc = evo::layout_from_strides(dims, s_out, &lay))) return rc;
     if (!q || !k || !v || !pair_bias || !res_mask || !o || !lse) return EVO_ERR_NULL_PTR;
     if ((gate == nullptr) != (o_gated == nullptr)) return EVO_ERR_NULL_PTR;
     const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
@@ -748,9 +758,11 @@ extern "C" int evo_fwd_gated(const EvoDims* dims, const EvoStrides* strides, con
     if ((rc = evo::ensure_context())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dims->D <= 32)
-        return evo::launch_fwd<32, EVO_FWD_NG32>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid,
-                                                 lse, scale, st);
+        return evo::launch_fwd<32, EVO_FWD_NG32>(dims, lay_in, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated,
+                                                 o_resid, lse, scale, st);
     if (dims->D <= 64)
-        return evo::launch_fwd<64, 2>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse, scale, st);
-    return evo::launch_fwd<128, 2>(dims, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse, scale, st);
+        return evo::launch_fwd<64, 2>(dims, lay_in, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse,
+                                      scale, st);
+    return evo::launch_fwd<128, 2>(dims, lay_in, lay, q, k, v, pair_bias, res_mask, gate, o, o_gated, o_resid, lse,
+                                   scale, st);
 }

@@ -154,6 +154,33 @@ def _shared_view_strides(Q, K, V):
     return tuple(st)
 
 
+def _inplace_view_strides(Q, K, V):
+    """Strides (elements) if Q, K, V are bf16 views that the kernels can READ in place: identical
+    strides, contiguous head dim, 16-byte-aligned steps, (B, N_SEQ) flattenable, no overlap inside a
+    tensor.  Holes are fine: q, k, v sliced out of one fused projection [B, N_SEQ, N_CTX, 3, H, D]
+    qualify, and are read where they lie while O and the gradients are written contiguously (the
+    reference copies each of them twice, transpose and pad, layer.py:81-102).  None otherwise."""
+    if any(t.dtype != torch.bfloat16 for t in (Q, K, V)):
+        return None
+    st = Q.stride()
+    if K.stride() != st or V.stride() != st or st[4] != 1:
+        return None
+    B, S = Q.shape[0], Q.shape[1]
+    for ext, s_ in zip(Q.shape[:4], st[:4]):
+        if ext > 1 and (s_ <= 0 or s_ % 8 != 0):
+            return None
+    if B > 1 and S > 1 and st[0] != S * st[1]:
+        return None
+    span = 1
+    for s_, ext in sorted((s_, ext) for s_, ext in zip(st, Q.shape) if ext > 1):
+        if s_ < span:
+            return None
+        span = s_ * ext
+    if any(t.data_ptr() % 16 for t in (Q, K, V)):
+        return None
+    return tuple(st)
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -193,7 +220,12 @@ class TKEvoAttention(torch.autograd.Function):
         # Views such as the "ending node" triangle attention (N_SEQ and N_CTX swapped in memory) are
         # read and written in place; the reference transposes and copies (layer.py:81-102).
         strides = _shared_view_strides(Q, K, V) if padded_D == D else None
-        q, k, v = (Q, K, V) if strides is not None else (_bf16c(Q), _bf16c(K), _bf16c(V))
+        # Views with holes (q, k, v sliced out of a fused projection) are read in place as well; only
+        # the tensors this call allocates are then contiguous.
+        in_strides = strides
+        if strides is None and padded_D == D and not Q.is_contiguous():
+            in_strides = _inplace_view_strides(Q, K, V)
+        q, k, v = (Q, K, V) if in_strides is not None else (_bf16c(Q), _bf16c(K), _bf16c(V))
         if padded_D != D:
             pad = padded_D - D
             q = F.pad(q, (0, pad)).contiguous()
@@ -206,13 +238,13 @@ class TKEvoAttention(torch.autograd.Function):
         softmax_scale = 1.0 / (D ** 0.5)
 
         like = (lambda: torch.empty_strided(q.shape, strides, dtype=q.dtype, device=q.device)) \
-            if strides is not None else (lambda: torch.empty_like(q))
+            if strides is not None else (lambda: torch.empty(q.shape, dtype=q.dtype, device=q.device))
         o = like()
         g = o_gated = None
         if gate is not None:
             # the gate travels in the layout of q
-            if strides is not None and gate.dtype == torch.bfloat16 and tuple(gate.stride()) == strides \
-                    and gate.data_ptr() % 16 == 0:
+            same_layout = (tuple(gate.stride()) == strides) if strides is not None else gate.is_contiguous()
+            if gate.dtype == torch.bfloat16 and same_layout and gate.data_ptr() % 16 == 0:
                 g = gate
             else:
                 g = like()
@@ -224,13 +256,17 @@ class TKEvoAttention(torch.autograd.Function):
         dims = _evoattn.EvoDims(B, N_SEQ, N_CTX, H, padded_D)
         with _device_ctx(q):
             st_ = _evoattn.EvoStrides(*strides[:4]) if strides is not None else None
-            if g is not None:
+            if in_strides != strides:
+                _evoattn.fwd_views(dims, _evoattn.EvoStrides(*in_strides[:4]), st_, q, k, v, bias, mask, g, o, o_gated,
+                                   o_resid, lse, softmax_scale, _stream())
+            elif g is not None:
                 _evoattn.fwd_gated(dims, st_, q, k, v, bias, mask, g, o, o_gated, o_resid, lse, softmax_scale, _stream())
             elif strides is not None:
                 _evoattn.fwd_strided(dims, st_, q, k, v, bias, mask, o, o_resid, lse, softmax_scale, _stream())
             else:
                 _evoattn.fwd(dims, q, k, v, bias, mask, o, o_resid, lse, softmax_scale, _stream())
         ctx.strides = strides
+        ctx.in_strides = in_strides
         ctx.gated = g is not None
 
         if g is not None:
@@ -267,7 +303,7 @@ class TKEvoAttention(torch.autograd.Function):
                 d_o = like()
                 d_o.copy_(dO)
         else:
-            like = lambda: torch.empty_like(q)
+            like = lambda: torch.empty(q.shape, dtype=q.dtype, device=q.device)
             d_o = _bf16c(dO)
             if padded_D != D:
                 d_o = F.pad(d_o, (0, padded_D - D)).contiguous()
@@ -281,7 +317,20 @@ class TKEvoAttention(torch.autograd.Function):
         st_ = _evoattn.EvoStrides(*strides[:4]) if strides is not None else None
         args = (dims, st_, q, k, v, bias, mask, o, o_resid, lse, d_o, dq, dk, dv, dbias, ws, ctx.softmax_scale)
         with _device_ctx(q):
-            if g is not None:
+            if ctx.in_strides != strides:
+                # q, k, v read through their own view; everything else in the layout of `strides`
+                import torch.distributed as dist
+                vargs = (dims, _evoattn.EvoStrides(*ctx.in_strides[:4]), st_, st_, q, k, v, bias, mask, g, o, o_resid,
+                         lse, d_o, dq, dk, dv, d_gate, dbias, ws, ctx.softmax_scale)
+                if ctx.process_group is None:
+                    _evoattn.bwd_views(*vargs, _evoattn.BWD_PHASE_DBIAS | _evoattn.BWD_PHASE_DQKV, 0, _stream())
+                else:
+                    _evoattn.bwd_views(*vargs, _evoattn.BWD_PHASE_DBIAS, 0, _stream())
+                    work = dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.process_group, async_op=True)
+                    reserve = ALLREDUCE_RESERVED_SMS if dist.get_world_size(ctx.process_group) >= ALLREDUCE_MIN_GROUP else 0
+                    _evoattn.bwd_views(*vargs, _evoattn.BWD_PHASE_DQKV, reserve, _stream())
+                    work.wait()
+            elif g is not None:
                 both = _evoattn.BWD_PHASE_DBIAS | _evoattn.BWD_PHASE_DQKV
                 gargs = (dims, st_, q, k, v, bias, mask, g, o, o_resid, lse, d_o, dq, dk, dv, d_gate, dbias, ws,
                          ctx.softmax_scale)

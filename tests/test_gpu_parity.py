@@ -320,26 +320,50 @@ def test_c_abi_direct():
     assert ei.value.code == -1
 
 
-def test_chunked_qkv_projection_views():
+@pytest.mark.parametrize("B,S,N,H,D,axis,gated", [
+    (1, 6, 136, 2, 32, -1, False),      # [B, S, N, H, 3*D] sliced along the head dim
+    (2, 3, 200, 4, 64, 3, False),       # [B, S, N, 3, H, D] sliced along the q/k/v axis
+    (1, 4, 136, 2, 128, 3, True),       # the same with D = 128 and the fused gate
+])
+def test_chunked_qkv_projection_views(B, S, N, H, D, axis, gated, monkeypatch):
     """q, k, v sliced out of one fused projection (equal strides, holes between the rows): the layer
-    copies them, O comes back contiguous as the reference's always is, and parity holds."""
-    from tk_evo_attention_layer import TKEvoAttention
-    B, S, N, H, D = 1, 6, 136, 2, 32
+    reads them where they lie (no copy of q, k or v is made), O comes back contiguous as the
+    reference's always is, and parity holds."""
+    import tk_evo_attention_layer as L
+    import _evoattn
     q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, 1.0, 1.0, "tail0to32", seed=33)
     dev, bf = "cuda", torch.bfloat16
-    qkv = torch.cat([q, k, v], dim=-1).to(dev, bf).requires_grad_(True)
-    Q, K, V = qkv.chunk(3, dim=-1)
-    assert not Q.is_contiguous() and Q.stride() == K.stride()
+    if axis == -1:
+        qkv = torch.cat([q, k, v], dim=-1).to(dev, bf).requires_grad_(True)
+        Q, K, V = qkv.chunk(3, dim=-1)
+    else:
+        qkv = torch.stack([q, k, v], dim=3).to(dev, bf).requires_grad_(True)      # [B, S, N, 3, H, D]
+        Q, K, V = qkv.unbind(dim=3)
+    assert not Q.is_contiguous() and Q.stride() == K.stride() and L._shared_view_strides(Q, K, V) is None
+    copies = []
+    real = L._bf16c
+    monkeypatch.setattr(L, "_bf16c", lambda t: (copies.append(t.dim()), real(t))[1])
     PB = bias.to(dev, torch.float32).requires_grad_(True)
-    O = TKEvoAttention.apply(Q, K, V, mask.to(dev), PB)
+    gate = torch.randn((B, S, N, H, D), generator=torch.Generator().manual_seed(5))
+    G = gate.to(dev, bf).requires_grad_(True) if gated else None
+    O = L.TKEvoAttention.apply(Q, K, V, mask.to(dev), PB, None, G) if gated else L.TKEvoAttention.apply(Q, K, V, mask.to(dev), PB)
     assert O.is_contiguous() and O.view(B, S, N, H * D).shape == (B, S, N, H * D)
     O.backward(d_o.to(dev, bf))
-    import _evoattn
     _evoattn.device_status()
+    assert 5 not in copies[:-1], "q, k or v was copied"       # the last entry is dO, passed through unchanged
     g = qkv.grad.float().cpu()
-    got = {"o": O.detach().float().cpu(), "dq": g[..., :D], "dk": g[..., D:2 * D], "dv": g[..., 2 * D:],
-           "dbias": PB.grad.float().cpu()}
-    assert_parity(oracle_on_rounded(q, k, v, mask, bias, d_o), got, tag="chunked qkv")
+    if axis == -1:
+        dq, dk, dv = g[..., :D], g[..., D:2 * D], g[..., 2 * D:]
+    else:
+        dq, dk, dv = g.unbind(dim=3)
+    got = {"o": O.detach().float().cpu(), "dq": dq, "dk": dk, "dv": dv, "dbias": PB.grad.float().cpu()}
+    if gated:
+        rq, rk, rv, rb, rm, rdo, rg = (t.to(bf).float() for t in (q, k, v, bias, mask, d_o, gate))
+        ref = evo_ref.evo_attention_fwd_bwd_ref(rq, rk, rv, rm, rb, rdo, gate=rg)
+        got["dgate"] = G.grad.float().cpu()
+        assert_parity(ref, got, names=("o", "dq", "dk", "dv", "dbias", "dgate"), tag="chunked qkv, gated")
+    else:
+        assert_parity(oracle_on_rounded(q, k, v, mask, bias, d_o), got, tag="chunked qkv")
 
 
 def test_head_dim_16_without_padding_copies():

@@ -82,3 +82,25 @@ def test_bias_cast_is_cached_per_version():
     assert c is not a and torch.equal(c, pb.reshape(B, H, N, N).to(torch.bfloat16))
     h = torch.randn((B, 1, H, N, N)).to(torch.bfloat16)
     assert L._bias_bf16(h, B, H, N).data_ptr() == h.data_ptr()   # bf16 input: no copy at all
+
+
+def test_views_with_holes_are_read_in_place():
+    """q, k, v sliced out of one fused projection are not dense, so outputs cannot mirror them, but the
+    kernels can read them where they lie: _inplace_view_strides accepts them, and rejects views whose
+    steps are not multiples of 8 elements, whose strides differ, or that overlap themselves."""
+    import tk_evo_attention_layer as L
+    bf = torch.bfloat16
+    B, S, N, H, D = 2, 3, 16, 2, 32
+    qkv = torch.zeros((B, S, N, 3, H, D), dtype=bf)
+    q, k, v = qkv.unbind(dim=3)
+    assert L._shared_view_strides(q, k, v) is None
+    assert L._inplace_view_strides(q, k, v) == (S * N * 3 * H * D, N * 3 * H * D, 3 * H * D, D, 1)
+    wide = torch.zeros((B, S, N, H, 3 * D), dtype=bf)
+    q2, k2, v2 = wide.chunk(3, dim=-1)
+    assert L._inplace_view_strides(q2, k2, v2) == (S * N * H * 3 * D, N * H * 3 * D, H * 3 * D, 3 * D, 1)
+    assert L._inplace_view_strides(q, k2, v) is None                          # different strides
+    assert L._inplace_view_strides(q.float(), k.float(), v.float()) is None   # not bf16
+    odd = torch.zeros((B, S, N, H, D + 4), dtype=bf)[..., :D]                 # steps of 36 elements
+    assert L._inplace_view_strides(odd, odd, odd) is None
+    ov = torch.zeros((N + 4, H, D), dtype=bf).as_strided((1, 1, N, H, D), (0, 0, D, D, 1))   # rows overlap heads
+    assert L._inplace_view_strides(ov, ov, ov) is None
