@@ -495,13 +495,37 @@ def run_reference_sweep(args):
             TKEvoAttention.apply(leaves[0], leaves[1], leaves[2], mask, leaves[3]).backward(d_o)
 
         ms_b, ms_a = bench(bwd_only), bench(full)
+        # the same full step captured once in a CUDA graph and replayed: what the kernels take without
+        # the Python wrapper and the launch latency (the reference's numbers have no such column)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            # leaves of their own, first used on this stream: autograd accumulates a leaf's gradient
+            # on the stream of its first use, which must not be the default stream during capture
+            gl = [t.detach().clone().requires_grad_(True) for t in leaves]
+
+            def full_g():
+                for t in gl:
+                    t.grad = None
+                TKEvoAttention.apply(gl[0], gl[1], gl[2], mask, gl[3]).backward(d_o)
+
+            for _ in range(3):
+                full_g()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            full_g()
+        ms_g = bench(graph.replay)
+        del graph, gl
         unit = B * S * H * N * N * D / 1e12
-        rows.append({"N_CTX": N, "fwd_ms": ms_f, "bwd_ms": ms_b, "full_ms": ms_a,
+        rows.append({"N_CTX": N, "fwd_ms": ms_f, "bwd_ms": ms_b, "full_ms": ms_a, "full_graph_ms": ms_g,
                      "fwd_tflops": 4 * unit / (ms_f * 1e-3), "bwd_tflops": 10 * unit / (ms_b * 1e-3),
-                     "full_tflops": 14 * unit / (ms_a * 1e-3)})
+                     "full_tflops": 14 * unit / (ms_a * 1e-3), "full_graph_tflops": 14 * unit / (ms_g * 1e-3)})
     _evoattn.device_status()
     print(json.dumps({"sweep": "reference benchmark shapes", "B": B, "H": H, "D": D, "N_SEQ": S, "dtype": "bf16",
-                      "timing": "median of 60 per-call CUDA-event times, L2 flushed before each, Python wrapper included",
+                      "timing": "median of 60 per-call CUDA-event times, L2 flushed before each, Python wrapper included "
+                                "(full_graph_*: the full step replayed from a CUDA graph)",
                       "rows": rows}), flush=True)
 
 
