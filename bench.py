@@ -326,12 +326,29 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
         return ms.item(), per
 
+    headline = step
+    if args.graph:
+        # the step captured once in a CUDA graph (its NCCL all-reduce included) and replayed: for
+        # workloads whose per-GPU share is launch-bound.  The leaves are first used on the capture's
+        # side stream: autograd accumulates a leaf's gradient on the stream of its first use.
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(args.warmup, 3)):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            step()
+        barrier()
+        headline = graph.replay
     for _ in range(max(args.warmup, 3)):
-        step()
+        headline()
     _evoattn.device_status()
     # headline: nothing but the steps inside the timed region
     with ClockSampler(local_rank) as cs:
-        ms_total, per_step = timed(step, args.steps)
+        ms_total, per_step = timed(headline, args.steps)
     _evoattn.device_status()
     # a second, short loop with the library's per-kernel events, for the roofline figures only
     prof_steps = max(3, min(args.steps, 20))
@@ -428,6 +445,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     "bytes_are": "per rank (the value is the whole job)",
                     "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps},
             "gpu_launches": 5 * args.steps,   # forward; backward: prep, dBias, dQ/dK/dV, dQ conversion
+            "graph_replay": bool(args.graph),
             "roofline": roofline,
         }
         if multi_gpu_check is not None:
@@ -437,7 +455,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         if cpu is not None:
             out["cpu_baseline"] = cpu
         print(json.dumps(out), flush=True)
+    if args.graph:
+        # a graph that holds collective kernels must be gone before its communicator is
+        headline = None
+        del graph
+        torch.cuda.synchronize()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -542,6 +566,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--cpu-rows", type=int, default=64, help="S rows per CPU pass (bounded sample)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the step in a CUDA graph and time its replay (launch-bound workloads)")
     ap.add_argument("--no-strong-cfg4", action="store_true",
                     help="N > 1: skip the strong-scaling record of config 4 that the default line carries")
     ap.add_argument("--rows", type=int, default=0,
