@@ -12,7 +12,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libevoattn.so")
 
-ABI_VERSION = 102
+ABI_VERSION = 103
 
 
 class EvoDims(C.Structure):

@@ -333,7 +333,7 @@ int check_dims(const EvoDims* d) {
 
 extern "C" {
 
-int evo_version(void) { return 102; }
+int evo_version(void) { return 103; }
 
 int evo_last_cuda_error(void) { return evo::t_last_cuda_error; }
 
