@@ -64,18 +64,21 @@ ALLREDUCE_RESERVED_SMS = int(os.environ.get("EVO_ALLREDUCE_RESERVED_SMS", "4"))
 ALLREDUCE_MIN_GROUP = int(os.environ.get("EVO_ALLREDUCE_MIN_GROUP", "2"))
 
 
-def new_dbias_group(ranks=None, ctas: int = 0):
+def new_dbias_group(ranks=None, ctas: int = 0, timeout=None):
     """A process group for the d_pair_bias all-reduce whose NCCL kernels use at most `ctas` CTAs
     (default ALLREDUCE_RESERVED_SMS), so that they fit beside the dQ/dK/dV kernel.  Collective over
-    all ranks of the default group, like torch.distributed.new_group."""
+    all ranks of the default group, like torch.distributed.new_group.  `timeout` (a timedelta) is the
+    group's limit for one collective: with it, a rank that never joins the backward's all-reduce ends
+    the others' wait with an error instead of holding them for the backend's default half hour."""
     import torch.distributed as dist
     ctas = ctas or max(ALLREDUCE_RESERVED_SMS, 1)
+    kw = {} if timeout is None else {"timeout": timeout}
     if dist.get_backend() == "nccl":
         opts = dist.ProcessGroupNCCL.Options()
         opts.config.max_ctas = ctas
         opts.config.min_ctas = 1
-        return dist.new_group(ranks=ranks, pg_options=opts)
-    return dist.new_group(ranks=ranks)
+        return dist.new_group(ranks=ranks, pg_options=opts, **kw)
+    return dist.new_group(ranks=ranks, **kw)
 
 # Head dims the library takes as they are; others below 128 are zero-padded up to the next one.
 TK_SUPPORTED_DIMS = (16, 32, 64, 96, 128)

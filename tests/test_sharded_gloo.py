@@ -115,3 +115,44 @@ def test_five_argument_call_returns_five_grads():
     bf = lambda t: t.to(torch.bfloat16).float()
     ref = evo_ref.evo_attention_fwd_bwd_ref(bf(q), bf(k), bf(v), bf(mask), bf(bias), bf(d_o))
     assert evo_ref.max_abs_err(ref["dq"], Q.grad.float()) < 2e-2
+
+
+def _worker_missing_rank(rank, world, port, out_dir):
+    """Rank 1 runs the forward and then never joins the backward's all-reduce (a rank that died or fell
+    behind between steps).  Rank 0 must get an error from the collective within the group's time limit,
+    not wait for ever."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    L, evo_ref = _install_cpu_doubles()
+    B, S, N, H, D = 1, 4, 16, 2, 32
+    rows = S // world
+    q, k, v, mask, bias, d_o = evo_ref.make_inputs(B, S, N, H, D, seed=5, s_lo=rank * rows, s_hi=(rank + 1) * rows)
+    Q, K, V = (t.to(torch.bfloat16).requires_grad_(True) for t in (q, k, v))
+    PB = bias.clone().requires_grad_(True)
+    O = L.EvoAttention(process_group=L.new_dbias_group(timeout=datetime.timedelta(seconds=4)))(Q, K, V, mask, PB)
+    if rank == 0:
+        t0 = time.time()
+        try:
+            O.backward(d_o.to(torch.bfloat16))
+            verdict = "no error"
+        except Exception as e:                      # the collective's time limit, surfaced by work.wait()
+            verdict = f"raised {type(e).__name__} after {time.time() - t0:.1f}s"
+        with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+            f.write(verdict)
+    else:
+        deadline = time.time() + 30                 # absent from the all-reduce until rank 0 has given up
+        while not os.path.exists(os.path.join(out_dir, "rank0.txt")) and time.time() < deadline:
+            time.sleep(0.2)
+    # no barrier, no orderly shutdown of a group with a failed collective
+    os._exit(0)
+
+
+def test_missing_rank_ends_the_all_reduce_with_an_error(tmp_path):
+    world = 2
+    mp.spawn(_worker_missing_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    verdict = (tmp_path / "rank0.txt").read_text()
+    assert verdict.startswith("raised"), verdict
+    seconds = float(verdict.split("after ")[1].rstrip("s"))
+    assert seconds < 20, verdict
