@@ -56,11 +56,14 @@ namespace evo {
 constexpr int BWD_THREADS = 512;
 constexpr int BWD_WARP_DRAIN = 8, BWD_WARP_PRODUCER = 12, BWD_WARP_MMA = 13;   // 13, 14, 15: mma issuers
 constexpr uint32_t BWD_TMEM_COLS = 512;
-constexpr int BWD_REGS_COMPUTE = 176;
-constexpr int BWD_REGS_OTHER = 80;
+// setmaxnreg budgets of the compute warpgroups and of the others, by head dim.  Measured (dQ/dK/dV
+// kernel): D=32 (B=1, S=512, N=384, H=8) 168/88 0.474 ms, 176/80 0.471, 184/72 0.483, 160/96 0.478;
+// D=64 (B=1, S=256, N=1024, H=4) 168/88 1.297 ms, 176/80 1.321, 184/72 1.288, 160/96 1.353.
+template <int DH> constexpr int BWD_REGS_COMPUTE = (DH == 64) ? 184 : 176;
+template <int DH> constexpr int BWD_REGS_OTHER = 256 - BWD_REGS_COMPUTE<DH>;
 // the CTA's register pool is the launch count (cap for 512 threads: 128) times the threads;
 // a setmaxnreg increase that the pool cannot satisfy blocks for ever
-static_assert(BWD_REGS_COMPUTE * 256 + BWD_REGS_OTHER * 256 <= 128 * BWD_THREADS, "register pool");
+static_assert(BWD_REGS_COMPUTE<32> * 256 + BWD_REGS_OTHER<32> * 256 <= 128 * BWD_THREADS, "register pool");
 
 template <int DH>
 struct BwdCfg {
@@ -234,7 +237,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     };
 
     if (warp >= BWD_WARP_DRAIN) {
-        reg_dec<BWD_REGS_OTHER>();
+        reg_dec<BWD_REGS_OTHER<DH>>();
         if (warp == BWD_WARP_PRODUCER && lane == 0) {
             // ------------------------------ producer ------------------------------
             bool ok = true;
@@ -471,7 +474,7 @@ evo_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (lane == 0) tma_wait_group<0>();
         }
     } else {
-        reg_inc<BWD_REGS_COMPUTE>();
+        reg_inc<BWD_REGS_COMPUTE<DH>>();
         // ------------------------------ compute groups ------------------------------
         const int wg = warp >> 2;            // kv columns 64*wg .. 64*wg+63 of the tile
         const int row = tid & 127;           // q row within the tile == TMEM lane

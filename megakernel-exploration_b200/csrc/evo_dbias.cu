@@ -45,8 +45,10 @@ struct DbCfg {
     // (the per-thread cap ptxas derives from the launch bound, times THREADS); an
     // increase blocks until the pool has room, for ever if it never can.
     static constexpr int REGS_LAUNCH = (65536 / THREADS) & ~7;
-    static constexpr int REGS_COMPUTE = (NG == 2) ? 224 : 112;
-    static constexpr int REGS_OTHER = (NG == 2) ? 56 : 32;
+    // measured (B=1, S=512, N=384, H=8, D=32 / B=1, S=256, N=1024, H=4, D=64): 224/56 0.200 / 0.394 ms,
+    // 216/72 0.195 / 0.380, 208/88 0.213 / 0.409
+    static constexpr int REGS_COMPUTE = (NG == 2) ? 216 : 112;
+    static constexpr int REGS_OTHER = (NG == 2) ? 72 : 32;
     static_assert(REGS_COMPUTE * NCW * 32 + REGS_OTHER * 128 <= REGS_LAUNCH * THREADS, "register pool");
     // D <= 64: a stage holds the four operand tiles of a step.  D = 128 (four tiles are 128 KB):
     // a stage holds ONE operand pair, (Q, K) of a step or (dO, V) of a step, alternately; each of

@@ -64,9 +64,16 @@ struct FwdCfg {
     // cap ptxas derives from the launch bound) times the threads; an increase that the pool cannot
     // satisfy blocks for ever
     static constexpr int REGS_LAUNCH = (65536 / THREADS) & ~7;
-    static constexpr int REGS_SOFTMAX = (NG == 2) ? 200 : 96;
-    static constexpr int REGS_EPI = (NG == 2) ? 56 : 40;
-    static constexpr int REGS_OTHER = (NG == 2) ? 56 : 40;
+    // Measured at B=1, S=512, N=384, H=8, D=32 (forward kernel): 208/40/40 0.392 ms, 200/56/56 0.393,
+    // 200/72/40 0.383, 192/72/56 0.376, 192/64/64 0.370, 184/72/72 0.383, 176/80/80 0.378.
+#ifndef EVO_FWD_RS
+#define EVO_FWD_RS 192
+#define EVO_FWD_RE 64
+#define EVO_FWD_RO 64
+#endif
+    static constexpr int REGS_SOFTMAX = (NG == 2) ? EVO_FWD_RS : 96;
+    static constexpr int REGS_EPI = (NG == 2) ? EVO_FWD_RE : 40;
+    static constexpr int REGS_OTHER = (NG == 2) ? EVO_FWD_RO : 40;
     static_assert((REGS_SOFTMAX * NSW + REGS_EPI * 4 + REGS_OTHER * 4) * 32 <= REGS_LAUNCH * THREADS, "register pool");
     static constexpr int STAGES = (DH == 32) ? 3 : 2;
     static constexpr uint32_t ROWT = RowTile<DH>::BYTES;          // one [128][DH] bf16 tile
