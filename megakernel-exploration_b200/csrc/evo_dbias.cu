@@ -34,7 +34,10 @@
 namespace evo {
 
 // every fourth column pair takes its exp2 on the fused-multiply-add pipe (see ex2_poly2)
-constexpr int DBIAS_POLY_EVERY = 4;
+#ifndef EVO_DBIAS_POLY_EVERY
+#define EVO_DBIAS_POLY_EVERY 4
+#endif
+constexpr int DBIAS_POLY_EVERY = EVO_DBIAS_POLY_EVERY;
 
 template <int DH, int NG>
 struct DbCfg {

@@ -580,7 +580,7 @@ evo_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // pass of tile g, then the second half runs its own, while the other half is in the
                 // fused-multiply-add pass of its next tile or in its epilogue.  The first half waits
                 // for the second half's pass of the previous tile, the second for the first's pass of
-                // this tile.  (At D = 64, with its longer epilogue, taking turns measured 2 % slower.)
+                // this tile.  (At D = 64 taking turns measured 7 % slower: 0.736 against 0.686 ms at B=1, S=256, N=1024, H=4.)
 #ifdef EVO_FWD_NO_PINGPONG
                 constexpr bool PINGPONG = false;
 #else
