@@ -39,8 +39,8 @@ for _p in (ROOT, PKG):
 import evo_workloads as wl  # noqa: E402
 
 # DRAM bytes per S row of one evo_bwd_kernel launch, from the ncu capture summarised under profiles/
-# (160.79 MB read + 54.46 MB written at 128 rows of cfg2).
-NCU_DRAM_BYTES_PER_ROW = {"cfg2_msa_row": (160.79e6 + 54.46e6) / 128}
+# (160.77 MB read + 53.59 MB written at 128 rows of cfg2).
+NCU_DRAM_BYTES_PER_ROW = {"cfg2_msa_row": (160.77e6 + 53.59e6) / 128}
 
 METRIC = "EvoAttention fwd+bwd TFLOP/s"
 UNIT = "TFLOP/s"
